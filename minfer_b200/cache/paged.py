@@ -1,0 +1,254 @@
+"""The cache: a slot per sequence, keys and values per cache entry in pages of 64
+positions, and per-sequence state of fixed size beside it.
+
+The reference keeps, per layer, two persistent regions K and V of ``n_ctx`` positions
+addressed by position (src/graph/alloc.rs:260-268, src/cache.rs:1-85), one whole set per
+server slot (src/server/slot.rs:15-32), and has one kind of layer only.  Here:
+
+* Storage is sized by the number of tokens that live sequences may hold together
+  (``max_tokens``), in pages of 64 positions; a sequence takes pages as it grows and gives
+  them all back when its slot is released, so later batches use them again.
+* Cache entries with the same needs form a *group* with storage, pages and page tables of
+  its own.  A group is either linear (every position is kept) or a ring of
+  ``ceil(window / 64) * 64`` positions (a windowed mixer never reads further back).
+* Validity is a sequence's length, never a memset: a reused page still holds the last
+  owner's values and nothing reads them.
+* ``StatePool`` holds fixed-size state per slot (zeroed when the slot is handed out) for
+  parts that ask for it, and for the sampler.
+
+Layout of a group's storage: ``[entry][page][kv_head][64][head_dim]`` for K and for V.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+PAGE = 64
+
+
+class CacheError(RuntimeError):
+    pass
+
+
+class OutOfPages(CacheError):
+    pass
+
+
+def pages_for(n_positions: int) -> int:
+    return (n_positions + PAGE - 1) // PAGE
+
+
+class SlotTable:
+    """Hands out slot numbers; a slot is held by at most one sequence at a time."""
+
+    def __init__(self, n_slots: int):
+        if n_slots <= 0:
+            raise CacheError("the cache needs at least one slot")
+        self.n_slots = n_slots
+        self._free: List[int] = list(range(n_slots - 1, -1, -1))
+        self._held = [False] * n_slots
+        self.length = [0] * n_slots
+
+    def acquire(self) -> int:
+        if not self._free:
+            raise CacheError(f"all {self.n_slots} sequence slots are in use")
+        s = self._free.pop()
+        self._held[s] = True
+        self.length[s] = 0
+        return s
+
+    def release(self, slot: int) -> None:
+        self.check(slot)
+        self._held[slot] = False
+        self.length[slot] = 0
+        self._free.append(slot)
+
+    def check(self, slot: int) -> None:
+        if not isinstance(slot, int) or not 0 <= slot < self.n_slots:
+            raise CacheError(f"slot {slot!r} is out of range (0..{self.n_slots - 1})")
+        if not self._held[slot]:
+            raise CacheError(f"slot {slot} is not held by any sequence (released twice?)")
+
+    def held(self) -> List[int]:
+        return [s for s in range(self.n_slots) if self._held[s]]
+
+    def n_free(self) -> int:
+        return len(self._free)
+
+
+class PagePool:
+    """Free list of a group's pages."""
+
+    def __init__(self, n_pages: int):
+        self.n_pages = n_pages
+        self._free: List[int] = list(range(n_pages - 1, -1, -1))
+        self._owner: List[int] = [-1] * n_pages       # slot that holds the page, or -1
+
+    def take(self, slot: int) -> int:
+        if not self._free:
+            raise OutOfPages(
+                f"the cache has no free page left ({self.n_pages} pages of {PAGE} positions); "
+                f"it was sized for fewer tokens than the live sequences now hold")
+        p = self._free.pop()
+        self._owner[p] = slot
+        return p
+
+    def give_back(self, page: int, slot: int) -> None:
+        if not 0 <= page < self.n_pages:
+            raise CacheError(f"page {page} is out of range")
+        if self._owner[page] != slot:
+            raise CacheError(
+                f"page {page} is returned by slot {slot} but is held by {self._owner[page]}")
+        self._owner[page] = -1
+        self._free.append(page)
+
+    def n_free(self) -> int:
+        return len(self._free)
+
+    def owner(self, page: int) -> int:
+        return self._owner[page]
+
+
+@dataclass(frozen=True)
+class GroupKey:
+    n_kv_heads: int
+    head_dim: int
+    window: int          # 0: linear
+
+
+class CacheGroup:
+    """Storage, pages and page tables of the cache entries that share one ``GroupKey``."""
+
+    def __init__(self, key: GroupKey, entries: Sequence[int], n_pages: int, n_slots: int,
+                 dtype: torch.dtype, device: torch.device | str):
+        self.key = key
+        self.entries = list(entries)
+        self.ring = pages_for(key.window) * PAGE if key.window > 0 else 0
+        self.n_pages = n_pages
+        self.pool = PagePool(n_pages)
+        self.pages: List[List[int]] = [[] for _ in range(n_slots)]
+        shape = (len(self.entries), n_pages, key.n_kv_heads, PAGE, key.head_dim)
+        self.k = torch.empty(shape, dtype=dtype, device=device)
+        self.v = torch.empty(shape, dtype=dtype, device=device)
+        self._index = {e: i for i, e in enumerate(self.entries)}
+
+    def pages_needed(self, length: int) -> int:
+        need = pages_for(length)
+        if self.ring:
+            need = min(need, self.ring // PAGE)
+        return need
+
+    def ensure(self, slot: int, length: int) -> None:
+        """Pages so that a sequence of ``length`` positions can be written."""
+        have = self.pages[slot]
+        need = self.pages_needed(length)
+        while len(have) < need:
+            have.append(self.pool.take(slot))
+
+    def release(self, slot: int) -> None:
+        for p in self.pages[slot]:
+            self.pool.give_back(p, slot)
+        self.pages[slot] = []
+
+    def entry_tensors(self, entry: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        i = self._index[entry]
+        return self.k[i], self.v[i]
+
+    def table_rows(self, slots: Sequence[int], width: int) -> List[List[int]]:
+        rows = []
+        for s in slots:
+            pg = self.pages[s]
+            if len(pg) > width:
+                raise CacheError("the page table is narrower than a sequence's pages")
+            rows.append(pg + [-1] * (width - len(pg)))
+        return rows
+
+    def max_pages_of(self, slots: Sequence[int]) -> int:
+        return max((len(self.pages[s]) for s in slots), default=0)
+
+
+class StatePool:
+    """Fixed-size state per slot: one tensor ``[n_slots, *shape]`` per name."""
+
+    def __init__(self, n_slots: int, device: torch.device | str):
+        self.n_slots = n_slots
+        self.device = device
+        self.tensors: Dict[str, torch.Tensor] = {}
+
+    def add(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        if name in self.tensors:
+            raise CacheError(f"state '{name}' is already defined")
+        t = torch.zeros((self.n_slots, *shape), dtype=dtype, device=self.device)
+        self.tensors[name] = t
+        return t
+
+    def reset(self, slot: int) -> None:
+        for t in self.tensors.values():
+            t[slot].zero_()
+
+    def bytes_per_slot(self) -> int:
+        return sum(t[0].numel() * t.element_size() for t in self.tensors.values())
+
+
+class Cache:
+    """Slots, groups and state together.  ``requests`` maps a cache entry to the
+    ``GroupKey`` of the mixer that writes it."""
+
+    def __init__(self, requests: Dict[int, GroupKey], max_tokens: int, max_seqs: int,
+                 dtype: torch.dtype, device: torch.device | str):
+        if max_tokens <= 0 or max_tokens % PAGE != 0:
+            raise CacheError(f"max_tokens must be a positive multiple of {PAGE}, got {max_tokens}")
+        self.max_tokens = max_tokens
+        self.max_seqs = max_seqs
+        self.dtype = dtype
+        self.device = device
+        self.slots = SlotTable(max_seqs)
+        self.state = StatePool(max_seqs, device)
+        by_key: Dict[GroupKey, List[int]] = {}
+        for entry in sorted(requests):
+            by_key.setdefault(requests[entry], []).append(entry)
+        self.groups: List[CacheGroup] = []
+        self.group_of: Dict[int, CacheGroup] = {}
+        total_pages = max_tokens // PAGE
+        for key, entries in by_key.items():
+            n_pages = total_pages
+            if key.window > 0:
+                n_pages = min(total_pages, max_seqs * pages_for(key.window))
+            g = CacheGroup(key, entries, n_pages, max_seqs, dtype, device)
+            self.groups.append(g)
+            for e in entries:
+                self.group_of[e] = g
+
+    # ---- slots --------------------------------------------------------------------------
+    def acquire(self) -> int:
+        s = self.slots.acquire()
+        self.state.reset(s)
+        return s
+
+    def release(self, slot: int) -> None:
+        self.slots.check(slot)
+        for g in self.groups:
+            g.release(slot)
+        self.slots.release(slot)
+
+    def length(self, slot: int) -> int:
+        self.slots.check(slot)
+        return self.slots.length[slot]
+
+    def reserve(self, slot: int, new_length: int) -> None:
+        """Pages in every group for a sequence that grows to ``new_length``."""
+        self.slots.check(slot)
+        for g in self.groups:
+            g.ensure(slot, new_length)
+
+    def set_length(self, slot: int, length: int) -> None:
+        self.slots.check(slot)
+        self.slots.length[slot] = length
+
+    def bytes(self) -> int:
+        return sum(2 * g.k.numel() * g.k.element_size() for g in self.groups)
+
+    def free_pages(self) -> List[int]:
+        return [g.pool.n_free() for g in self.groups]

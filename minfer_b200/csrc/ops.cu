@@ -1,0 +1,304 @@
+// Row-wise and element-wise kernels of the step: embedding lookup, RMSNorm, the fused
+// rotary + cache write, SwiGLU, row gather, casts.  All reductions are in float32.
+//
+// Formulas follow the reference's CPU backend: get_rows src/graph/cpu_backend.rs:249-291,
+// rms_norm src/vec_ops.rs:500-522 (x * 1/sqrt(mean(x^2)+eps) * w), rotary
+// src/graph/cpu_backend.rs:403-434, KV store src/graph/cpu_backend.rs:118-149, silu
+// src/vec_ops.rs:131-146.  Its CUDA versions (src/cuda_kernels.cu:531-668) launch one
+// kernel per op and one thread per block for the KV store; here bias, rotation and both
+// cache writes are one pass over the projection's output.
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------
+// embedding: out[t][:] = table[ids[t]][:]  (float32 out: the residual stream is float32)
+// ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ out, int width, int vocab,
+                             unsigned* __restrict__ status) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * width;
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicOr(status, MF_STATUS_BAD_TOKEN);
+        for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = 0.0f;
+        return;
+    }
+    const T* row = table + (size_t)id * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+extern "C" int mf_embed(const void* table, int table_dtype, const int* ids, float* out,
+                        int n_tokens, int width, int vocab, unsigned* status,
+                        cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (table_dtype == MF_DTYPE_F32)
+        embed_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, width,
+                                                             vocab, status);
+    else if (table_dtype == MF_DTYPE_BF16)
+        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+            (const __nv_bfloat16*)table, ids, out, width, vocab, status);
+    else
+        return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// RMSNorm over rows of the float32 residual stream; optional row gather (rows[r] names the
+// input row of output row r).  y = x * rsqrt(mean(x^2) + eps) * w
+// ------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                               const int* __restrict__ rows, TO* __restrict__ y, int width,
+                               float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = xr[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    TO* yr = y + (size_t)r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) yr[i] = from_f32<TO>(xr[i] * scale * w[i]);
+}
+
+extern "C" int mf_rmsnorm(const float* x, const float* w, const int* rows, void* y, int out_dtype,
+                          int n_rows, int width, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    // the block size is a function of the width only, so a row's sum never depends on the batch
+    int threads = 32;
+    while (threads < 512 && threads * 4 < width) threads <<= 1;
+    if (out_dtype == MF_DTYPE_F32)
+        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, rows, (float*)y, width, eps);
+    else if (out_dtype == MF_DTYPE_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, w, rows, (__nv_bfloat16*)y,
+                                                                      width, eps);
+    else
+        return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// rotary + cache write.  Input: the fused projection's float32 output qkv[t] =
+// [q (n_heads*hd) | k (n_kv*hd) | v (n_kv*hd)], bias already added.  Rotates q and k by
+// the token's position (angles in float32: pos * inv_freq[i]), writes
+//   q_out[t][h][:]              (activation type)
+//   k_out[t][hk][:], v_out[..]  (activation type; the step's own keys and values, which
+//                                prefill attention reads; may be null)
+//   cache pages                 (if k_cache is not null): position p of batch row b lies in
+//                                page page_table[b*table_stride + (p' / 64)], p' = p % ring
+//                                for a ring of `ring` positions, else p; inside the page at
+//                                [kv_head][p % 64][:].
+// A ring holds only the last `ring` positions: a prompt longer than the ring writes just
+// those (seq_end[b] is the sequence's length after this step).
+// style: 0 = pairs (i, i + R/2) ("NeoX", the reference's NonInterleaved), 1 = pairs
+// (2i, 2i+1); R = rotary_dim <= hd, dimensions beyond R pass through; inv_freq null = no
+// rotation at all.
+// ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_kvstore_kernel(const float* __restrict__ qkv, const int* __restrict__ positions,
+                                    const int* __restrict__ token_row,
+                                    const int* __restrict__ seq_end,
+                                    const float* __restrict__ inv_freq, T* __restrict__ q_out,
+                                    T* __restrict__ k_out, T* __restrict__ v_out,
+                                    T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                    const int* __restrict__ page_table, int table_stride, int ring,
+                                    int n_heads, int n_kv, int hd, int rotary_dim, int style,
+                                    unsigned* __restrict__ status) {
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int b = token_row[t];
+    const int half = hd >> 1;
+    const int rhalf = rotary_dim >> 1;
+    const int n_slots = (n_heads + 2 * n_kv) * half;
+    const size_t in_width = (size_t)(n_heads + 2 * n_kv) * hd;
+    const float* in = qkv + (size_t)t * in_width;
+
+    // where this token's keys and values go in the cache
+    long long cache_row = -1;     // element offset of [kv_head 0][pos%64][0] in the page, or -1
+    if (k_cache != nullptr) {
+        bool keep = true;
+        int p_eff = pos;
+        if (ring > 0) {
+            keep = pos >= seq_end[b] - ring;
+            p_eff = pos % ring;
+        }
+        if (keep) {
+            const int page = page_table[(size_t)b * table_stride + (p_eff >> 6)];
+            if (page < 0) {
+                if (threadIdx.x == 0) atomicOr(status, MF_STATUS_BAD_POSITION);
+            } else {
+                cache_row = ((long long)page * n_kv * MF_PAGE + (pos & (MF_PAGE - 1))) * hd;
+            }
+        }
+    }
+
+    for (int s = threadIdx.x; s < n_slots; s += blockDim.x) {
+        const int head = s / half;      // 0..n_heads-1: q, then k heads, then v heads
+        const int i = s - head * half;
+        const float* hin = in + (size_t)head * hd;
+        int d0, d1;
+        float x0, x1;
+        const bool is_v = head >= n_heads + n_kv;
+        if (!is_v && inv_freq != nullptr && i < rhalf) {
+            if (style == 0) { d0 = i; d1 = i + rhalf; } else { d0 = 2 * i; d1 = 2 * i + 1; }
+            const float a = hin[d0], c = hin[d1];
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            x0 = a * cs - c * sn;
+            x1 = a * sn + c * cs;
+        } else {
+            // pass-through pair: for rotated heads the dimensions beyond R, else (2i, 2i+1)
+            const int j = (!is_v && inv_freq != nullptr) ? rotary_dim + 2 * (i - rhalf) : 2 * i;
+            d0 = j; d1 = j + 1;
+            x0 = hin[d0];
+            x1 = hin[d1];
+        }
+        const T y0 = from_f32<T>(x0), y1 = from_f32<T>(x1);
+        if (head < n_heads) {
+            T* o = q_out + ((size_t)t * n_heads + head) * hd;
+            o[d0] = y0; o[d1] = y1;
+        } else {
+            const int hk = is_v ? head - n_heads - n_kv : head - n_heads;
+            T* step_out = is_v ? v_out : k_out;
+            if (step_out != nullptr) {
+                T* o = step_out + ((size_t)t * n_kv + hk) * hd;
+                o[d0] = y0; o[d1] = y1;
+            }
+            if (cache_row >= 0) {
+                T* c = (is_v ? v_cache : k_cache) + cache_row + (long long)hk * MF_PAGE * hd;
+                c[d0] = y0; c[d1] = y1;
+            }
+        }
+    }
+}
+
+extern "C" int mf_rope_kvstore(const float* qkv, const int* positions, const int* token_row,
+                               const int* seq_end, const float* inv_freq, void* q_out, void* k_out,
+                               void* v_out, void* k_cache, void* v_cache, const int* page_table,
+                               int table_stride, int ring, int n_tokens, int n_heads, int n_kv,
+                               int hd, int rotary_dim, int style, int dtype, unsigned* status,
+                               cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (hd % 2 != 0 || rotary_dim % 2 != 0 || rotary_dim > hd || rotary_dim < 0)
+        return MF_ERR_UNSUPPORTED;
+    if (ring % MF_PAGE != 0) return MF_ERR_ARGUMENT;
+    const int n_slots = (n_heads + 2 * n_kv) * (hd / 2);
+    int threads = 64;
+    while (threads < 256 && threads < n_slots) threads <<= 1;
+    if (dtype == MF_DTYPE_F32)
+        rope_kvstore_kernel<float><<<n_tokens, threads, 0, stream>>>(
+            qkv, positions, token_row, seq_end, inv_freq, (float*)q_out, (float*)k_out,
+            (float*)v_out, (float*)k_cache, (float*)v_cache, page_table, table_stride, ring,
+            n_heads, n_kv, hd, rotary_dim, style, status);
+    else if (dtype == MF_DTYPE_BF16)
+        rope_kvstore_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+            qkv, positions, token_row, seq_end, inv_freq, (__nv_bfloat16*)q_out,
+            (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, (__nv_bfloat16*)k_cache,
+            (__nv_bfloat16*)v_cache, page_table, table_stride, ring, n_heads, n_kv, hd,
+            rotary_dim, style, status);
+    else
+        return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// SwiGLU over the fused gate|up projection: out[t][j] = silu(gu[t][j]) * gu[t][nf + j],
+// silu(z) = z / (1 + exp(-z)), in float32.
+// ------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void swiglu_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int nf,
+                              long long total) {
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long t = idx / nf;
+        const int j = (int)(idx - t * nf);
+        const float g = to_f32(gu[t * 2 * nf + j]);
+        const float u = to_f32(gu[t * 2 * nf + nf + j]);
+        out[idx] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+extern "C" int mf_swiglu(const void* gu, int in_dtype, void* out, int out_dtype, int n_rows, int nf,
+                         cudaStream_t stream) {
+    const long long total = (long long)n_rows * nf;
+    if (total <= 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16
+                                 ? (total + threads - 1) / threads : 148 * 16);
+#define MF_SWIGLU(TI, TO) \
+    swiglu_kernel<TI, TO><<<blocks, threads, 0, stream>>>((const TI*)gu, (TO*)out, nf, total)
+    if (in_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_F32) MF_SWIGLU(float, float);
+    else if (in_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_BF16) MF_SWIGLU(float, __nv_bfloat16);
+    else if (in_dtype == MF_DTYPE_BF16 && out_dtype == MF_DTYPE_BF16)
+        MF_SWIGLU(__nv_bfloat16, __nv_bfloat16);
+    else return MF_ERR_UNSUPPORTED;
+#undef MF_SWIGLU
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// row gather of the float32 residual stream: out[r][:] = x[rows[r]][:]
+// ------------------------------------------------------------------------------------
+__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                   float* __restrict__ out, int width) {
+    const float* xr = x + (size_t)rows[blockIdx.x] * width;
+    float* o = out + (size_t)blockIdx.x * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = xr[i];
+}
+
+extern "C" int mf_gather_rows(const float* x, const int* rows, float* out, int n_rows, int width,
+                              cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    gather_rows_kernel<<<n_rows, 256, 0, stream>>>(x, rows, out, width);
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// cast between float32 and bfloat16 (round to nearest even)
+// ------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, long long n) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_f32<TO>(to_f32(in[i]));
+}
+
+extern "C" int mf_cast(const void* in, int in_dtype, void* out, int out_dtype, long long n,
+                       cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const int threads = 256;
+    const long long want = (n + threads - 1) / threads;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (in_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_BF16)
+        cast_kernel<float, __nv_bfloat16><<<blocks, threads, 0, stream>>>(
+            (const float*)in, (__nv_bfloat16*)out, n);
+    else if (in_dtype == MF_DTYPE_BF16 && out_dtype == MF_DTYPE_F32)
+        cast_kernel<__nv_bfloat16, float><<<blocks, threads, 0, stream>>>(
+            (const __nv_bfloat16*)in, (float*)out, n);
+    else
+        return MF_ERR_UNSUPPORTED;
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// decode bookkeeping on the device, so that a captured decode step can be replayed:
+// positions[b] += 1 and seq_end[b] += 1 for live rows.
+// ------------------------------------------------------------------------------------
+__global__ void advance_kernel(int* __restrict__ positions, int* __restrict__ seq_end, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        positions[i] += 1;
+        seq_end[i] += 1;
+    }
+}
+
+extern "C" int mf_advance_positions(int* positions, int* seq_end, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, seq_end, n);
+    return MF_LAUNCH_CHECK();
+}

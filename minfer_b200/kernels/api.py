@@ -1,0 +1,277 @@
+"""Python face of the CUDA launchers: each function checks its tensors, passes raw device
+pointers and the current stream to an ``extern "C"`` launcher, and raises on any error.
+
+There is no CPU path: a tensor that is not on a CUDA device is an error, and so is a
+library that cannot be built or loaded.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+F32, BF16 = 0, 1
+PAGE = 64
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+_ERRORS = {2001: "a size or dtype this kernel does not take", 2002: "inconsistent arguments",
+           2003: "the tensor-map encoder of the CUDA driver is not available",
+           2004: "the CUDA driver refused a tensor map"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _CODES[dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        why = _ERRORS.get(code, f"CUDA error {code}")
+        raise KernelError(f"{what}: {why}")
+
+
+def _ptr(t: Optional[torch.Tensor], what: str = "tensor") -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError(f"{what} must live on a CUDA device (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _i32(t: Optional[torch.Tensor], what: str) -> Optional[int]:
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{what} must be int32, got {t.dtype}")
+    return _ptr(t, what)
+
+
+def _f32(t: Optional[torch.Tensor], what: str) -> Optional[int]:
+    if t is not None and t.dtype != torch.float32:
+        raise KernelError(f"{what} must be float32, got {t.dtype}")
+    return _ptr(t, what)
+
+
+_configured: set[str] = set()
+
+
+def _lib(name: str) -> ctypes.CDLL:
+    lib = load_library(name)
+    if name not in _configured:
+        _SIGNATURES[name](lib)
+        _configured.add(name)
+    return lib
+
+
+def _sig_ops(lib: ctypes.CDLL) -> None:
+    lib.mf_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                             c_void_p]
+    lib.mf_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                               c_void_p]
+    lib.mf_rope_kvstore.argtypes = [c_void_p] * 11 + [c_int] * 9 + [c_void_p, c_void_p]
+    lib.mf_swiglu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.mf_gather_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
+    lib.mf_cast.argtypes = [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p]
+    lib.mf_advance_positions.argtypes = [c_void_p, c_void_p, c_int, c_void_p]
+
+
+def _sig_gemm_simt(lib: ctypes.CDLL) -> None:
+    lib.mf_gemm_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                 c_int, c_int, c_int, c_longlong, c_longlong, c_longlong, c_int,
+                                 c_void_p]
+
+
+def _sig_attention(lib: ctypes.CDLL) -> None:
+    lib.mf_attention_packed.argtypes = [c_void_p] * 7 + [c_int] * 5 + [c_float, c_int, c_void_p]
+    lib.mf_attention_paged.argtypes = ([c_void_p] * 6 + [c_int, c_int, c_void_p, c_void_p] +
+                                       [c_int] * 7 + [c_float, c_int, c_void_p])
+
+
+def _sig_sampling(lib: ctypes.CDLL) -> None:
+    lib.mf_sample.argtypes = [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_float, c_int, c_float, c_float, c_float, c_float,
+                              c_ulonglong, c_int, c_void_p]
+    lib.mf_sampler_state_ints.argtypes = []
+
+
+_SIGNATURES = {"ops": _sig_ops, "gemm_simt": _sig_gemm_simt, "attention": _sig_attention,
+               "sampling": _sig_sampling}
+
+
+# ---------------------------------------------------------------------------------------
+# row-wise ops
+# ---------------------------------------------------------------------------------------
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    n, width = out.shape
+    vocab = table.shape[0]
+    if table.shape[1] != width or ids.numel() != n:
+        raise KernelError("embed: shapes do not fit")
+    _check(_lib("ops").mf_embed(_ptr(table, "table"), dtype_code(table.dtype), _i32(ids, "ids"),
+                                _f32(out, "out"), n, width, vocab, _i32(status, "status"),
+                                _stream()), "embed")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> None:
+    n, width = out.shape
+    if x.shape[1] != width or weight.numel() != width:
+        raise KernelError("rmsnorm: shapes do not fit")
+    if rows is None and x.shape[0] != n:
+        raise KernelError("rmsnorm: row counts do not fit")
+    _check(_lib("ops").mf_rmsnorm(_f32(x, "x"), _f32(weight, "weight"), _i32(rows, "rows"),
+                                  _ptr(out, "out"), dtype_code(out.dtype), n, width, float(eps),
+                                  _stream()), "rmsnorm")
+
+
+def rope_kvstore(qkv: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor,
+                 seq_end: torch.Tensor, inv_freq: Optional[torch.Tensor], q_out: torch.Tensor,
+                 k_out: Optional[torch.Tensor], v_out: Optional[torch.Tensor],
+                 k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                 page_table: Optional[torch.Tensor], table_stride: int, ring: int,
+                 n_heads: int, n_kv: int, head_dim: int, rotary_dim: int, style: int,
+                 status: torch.Tensor) -> None:
+    n = qkv.shape[0]
+    if qkv.shape[1] != (n_heads + 2 * n_kv) * head_dim:
+        raise KernelError("rope_kvstore: qkv has the wrong width")
+    dt = q_out.dtype
+    for t in (k_out, v_out, k_cache, v_cache):
+        if t is not None and t.dtype != dt:
+            raise KernelError("rope_kvstore: q, k, v and the cache must share one dtype")
+    if (k_cache is None) != (v_cache is None) or (k_cache is not None and page_table is None):
+        raise KernelError("rope_kvstore: the cache needs keys, values and a page table")
+    _check(_lib("ops").mf_rope_kvstore(
+        _f32(qkv, "qkv"), _i32(positions, "positions"), _i32(token_row, "token_row"),
+        _i32(seq_end, "seq_end"), _f32(inv_freq, "inv_freq"), _ptr(q_out, "q_out"),
+        _ptr(k_out, "k_out"), _ptr(v_out, "v_out"), _ptr(k_cache, "k_cache"),
+        _ptr(v_cache, "v_cache"), _i32(page_table, "page_table"), int(table_stride), int(ring),
+        n, n_heads, n_kv, head_dim, rotary_dim, style, dtype_code(dt), _i32(status, "status"),
+        _stream()), "rope_kvstore")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    n, nf = out.shape
+    if gate_up.shape != (n, 2 * nf):
+        raise KernelError("swiglu: shapes do not fit")
+    _check(_lib("ops").mf_swiglu(_ptr(gate_up, "gate_up"), dtype_code(gate_up.dtype),
+                                 _ptr(out, "out"), dtype_code(out.dtype), n, nf, _stream()),
+           "swiglu")
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    n, width = out.shape
+    if x.shape[1] != width or rows.numel() != n:
+        raise KernelError("gather_rows: shapes do not fit")
+    _check(_lib("ops").mf_gather_rows(_f32(x, "x"), _i32(rows, "rows"), _f32(out, "out"), n, width,
+                                      _stream()), "gather_rows")
+
+
+def cast(src: torch.Tensor, out: torch.Tensor) -> None:
+    if src.numel() != out.numel():
+        raise KernelError("cast: sizes differ")
+    _check(_lib("ops").mf_cast(_ptr(src, "src"), dtype_code(src.dtype), _ptr(out, "out"),
+                               dtype_code(out.dtype), src.numel(), _stream()), "cast")
+
+
+def advance_positions(positions: torch.Tensor, seq_end: torch.Tensor, n: int) -> None:
+    _check(_lib("ops").mf_advance_positions(_i32(positions, "positions"), _i32(seq_end, "seq_end"),
+                                            n, _stream()), "advance_positions")
+
+
+# ---------------------------------------------------------------------------------------
+# matrix product on the FP32 pipe
+# ---------------------------------------------------------------------------------------
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+              accumulate: bool = False) -> None:
+    """out[M,N] (+)= a[M,K] @ w[N,K]^T + bias.  Rows may be strided (last dim contiguous)."""
+    m, k = a.shape
+    n = w.shape[0]
+    if w.shape[1] != k or out.shape != (m, n):
+        raise KernelError(f"gemm: shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, "
+                          f"out {tuple(out.shape)}")
+    for t, what in ((a, "a"), (w, "w"), (out, "out")):
+        if not t.is_cuda:
+            raise KernelError(f"gemm: {what} must live on a CUDA device (there is no CPU path)")
+        if t.stride(1) != 1:
+            raise KernelError(f"gemm: {what} must be contiguous along its last dimension")
+    if bias is not None and bias.numel() != n:
+        raise KernelError("gemm: bias has the wrong length")
+    _check(_lib("gemm_simt").mf_gemm_simt(
+        a.data_ptr(), dtype_code(a.dtype), w.data_ptr(), dtype_code(w.dtype), _f32(bias, "bias"),
+        out.data_ptr(), dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(0), out.stride(0),
+        1 if accumulate else 0, _stream()), "gemm_simt")
+
+
+# ---------------------------------------------------------------------------------------
+# attention
+# ---------------------------------------------------------------------------------------
+def attention_packed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_seq: torch.Tensor,
+                     row_pos: torch.Tensor, cu_seqlens: torch.Tensor, out: torch.Tensor,
+                     n_heads: int, n_kv: int, head_dim: int, window: int, scale: float) -> None:
+    rows = q.shape[0]
+    if q.dtype != k.dtype or q.dtype != v.dtype or q.dtype != out.dtype:
+        raise KernelError("attention: q, k, v and out must share one dtype")
+    _check(_lib("attention").mf_attention_packed(
+        _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v"), _i32(row_seq, "row_seq"), _i32(row_pos, "row_pos"),
+        _i32(cu_seqlens, "cu_seqlens"), _ptr(out, "out"), rows, n_heads, n_kv, head_dim,
+        int(window), float(scale), dtype_code(q.dtype), _stream()), "attention_packed")
+
+
+def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    row_seq: torch.Tensor, row_pos: torch.Tensor, page_table: torch.Tensor,
+                    table_stride: int, ring: int, out: torch.Tensor,
+                    partial: Optional[torch.Tensor], n_heads: int, n_kv: int, head_dim: int,
+                    window: int, chunk: int, n_chunks: int, scale: float) -> None:
+    rows = q.shape[0]
+    if q.dtype != k_cache.dtype or q.dtype != v_cache.dtype or q.dtype != out.dtype:
+        raise KernelError("attention: q, the cache and out must share one dtype")
+    if n_chunks > 1:
+        need = rows * n_heads * n_chunks * (head_dim + 2)
+        if partial is None or partial.numel() < need:
+            raise KernelError("attention: the scratch for key chunks is too small")
+    _check(_lib("attention").mf_attention_paged(
+        _ptr(q, "q"), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"), _i32(row_seq, "row_seq"),
+        _i32(row_pos, "row_pos"), _i32(page_table, "page_table"), int(table_stride), int(ring),
+        _ptr(out, "out"), _f32(partial, "partial"), rows, n_heads, n_kv, head_dim, int(window),
+        int(chunk), int(n_chunks), float(scale), dtype_code(q.dtype), _stream()),
+        "attention_paged")
+
+
+# ---------------------------------------------------------------------------------------
+# sampling
+# ---------------------------------------------------------------------------------------
+def sampler_state_ints() -> int:
+    return int(_lib("sampling").mf_sampler_state_ints())
+
+
+def sample(logits: torch.Tensor, out: torch.Tensor, *, temperature: float, top_k: int,
+           top_p: float, repeat_penalty: float, frequency_penalty: float,
+           presence_penalty: float, seed: int, slots: Optional[torch.Tensor] = None,
+           state: Optional[torch.Tensor] = None, stream_ids: Optional[torch.Tensor] = None,
+           update_state: bool = True) -> None:
+    """Samples one token per row of ``logits`` (float32, changed in place) into ``out``."""
+    rows, vocab = logits.shape
+    if logits.stride(1) != 1:
+        raise KernelError("sample: logits must be contiguous along the vocabulary")
+    if not logits.is_cuda:
+        raise KernelError("sample: logits must live on a CUDA device (there is no CPU path)")
+    if logits.dtype != torch.float32:
+        raise KernelError("sample: logits must be float32")
+    _check(_lib("sampling").mf_sample(
+        logits.data_ptr(), logits.stride(0), rows, vocab, _i32(slots, "slots"),
+        _i32(state, "state"), _i32(stream_ids, "stream_ids"), _i32(out, "out"), float(temperature),
+        int(top_k), float(top_p), float(repeat_penalty), float(frequency_penalty),
+        float(presence_penalty), int(seed) & 0xFFFFFFFFFFFFFFFF, 1 if update_state else 0,
+        _stream()), "sample")

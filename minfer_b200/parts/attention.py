@@ -1,0 +1,149 @@
+"""Grouped-query attention as a mixer: fused q|k|v projection with bias, position encoding,
+cache write, attention over the cache, output projection added into the residual stream.
+
+Per layer the reference runs norm -> Wq/Wk/Wv (+bias) -> rotary on q and k -> KV store ->
+attention -> Wo -> residual (src/models/qwen2/graph.rs:63-137); its Metal path packs
+wq|wk|wv into one matrix followed by one bias+rotary+store pass
+(src/models/qwen2/graph.rs:69-98, src/models/qwen2/loader.rs:290-331).  Here the packed
+projection is the only path: one product, then one kernel that rotates and writes the
+cache, then attention, then Wo with the residual add in its epilogue.
+
+Whole prompts (every row of the step starts at position 0) attend over the step's own keys
+and values; any other step attends over the cache.  All sizes are parameters.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config.base import PartSpec
+from ..kernels import api as K
+from ..weights.spec import MATRIX, VECTOR, Init, TensorSpec
+from .base import CacheRequest, CallBinding, Mixer, StepContext
+from .linear import Linear
+
+DECODE_CHUNK = 256     # keys per chunk when attending over the cache
+
+
+class Attention(Mixer):
+    def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                 scale: float, window: int = 0, qkv_bias: bool = True, out_bias: bool = False,
+                 position: Optional[PartSpec] = None, init_std: float = 0.02):
+        from ..registry import build_part
+        if n_heads % n_kv_heads != 0:
+            raise ValueError(f"{n_heads} heads do not divide into {n_kv_heads} key/value heads")
+        if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
+            raise ValueError(
+                f"head size {head_dim} is not supported: the attention kernels take multiples "
+                f"of 16 from 16 to 256")
+        self.hidden_size = int(hidden_size)
+        self.n_heads = int(n_heads)
+        self.n_kv_heads = int(n_kv_heads)
+        self.head_dim = int(head_dim)
+        self.scale = float(scale)
+        self.window = int(window)
+        self.qkv_bias = bool(qkv_bias)
+        self.out_bias = bool(out_bias)
+        self.init_std = float(init_std)
+        self.position = build_part("position", position) if position is not None else None
+        self.qkv: Optional[Linear] = None
+        self.out: Optional[Linear] = None
+
+    # ---- weights ----------------------------------------------------------------------
+    def tensor_specs(self, prefix: str) -> List[TensorSpec]:
+        p = f"{prefix}self_attn."
+        nq, nkv = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        init = Init(0.0, self.init_std)
+        specs = [TensorSpec(f"{p}q_proj.weight", (nq, self.hidden_size), MATRIX, init),
+                 TensorSpec(f"{p}k_proj.weight", (nkv, self.hidden_size), MATRIX, init),
+                 TensorSpec(f"{p}v_proj.weight", (nkv, self.hidden_size), MATRIX, init),
+                 TensorSpec(f"{p}o_proj.weight", (self.hidden_size, nq), MATRIX, init)]
+        if self.qkv_bias:
+            specs += [TensorSpec(f"{p}q_proj.bias", (nq,), VECTOR, init),
+                      TensorSpec(f"{p}k_proj.bias", (nkv,), VECTOR, init),
+                      TensorSpec(f"{p}v_proj.bias", (nkv,), VECTOR, init)]
+        if self.out_bias:
+            specs.append(TensorSpec(f"{p}o_proj.bias", (self.hidden_size,), VECTOR, init))
+        if self.position is not None:
+            specs += self.position.tensor_specs(p)
+        return specs
+
+    def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
+        p = f"{prefix}self_attn."
+        parts = [weights[f"{p}{n}_proj.weight"] for n in "qkv"]
+        if len({t.dtype for t in parts}) != 1:
+            parts = [t.to(torch.float32) for t in parts]
+        w = torch.cat(parts, dim=0).contiguous()
+        b = None
+        if self.qkv_bias:
+            b = torch.cat([weights[f"{p}{n}_proj.bias"] for n in "qkv"]).contiguous()
+        self.qkv = Linear(w, b)
+        self.out = Linear(weights[f"{p}o_proj.weight"],
+                          weights[f"{p}o_proj.bias"] if self.out_bias else None)
+        if self.position is not None:
+            self.position.load(p, weights)
+
+    # ---- what it keeps per sequence -----------------------------------------------------
+    def cache_request(self) -> Optional[CacheRequest]:
+        return CacheRequest(self.n_kv_heads, self.head_dim, self.window)
+
+    # ---- the step -----------------------------------------------------------------------
+    def forward_add(self, x: torch.Tensor, ctx: StepContext, binding: CallBinding,
+                    residual: torch.Tensor) -> None:
+        n = x.shape[0]
+        nh, nk, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        dev, act = x.device, ctx.act_dtype
+        qkv = self.qkv.forward(x, torch.float32)
+
+        inv_freq, rotary_dim, style = None, 0, 0
+        if self.position is not None:
+            fused = self.position.fused_rotary(dev)
+            if fused is None:
+                self.position.apply(qkv, ctx, nh, nk, hd)
+            else:
+                inv_freq, rotary_dim, style = fused
+
+        cache = binding.cache
+        if cache is None:
+            raise K.KernelError("the attention mixer was given no cache entry")
+        q = torch.empty((n, nh, hd), dtype=act, device=dev)
+        write = binding.writes_cache
+        own_kv = ctx.from_start
+        k_step = v_step = None
+        if own_kv and write:
+            k_step = torch.empty((n, nk, hd), dtype=act, device=dev)
+            v_step = torch.empty((n, nk, hd), dtype=act, device=dev)
+            if binding.has_readers:
+                ctx.extras[("step_kv", binding.entry)] = (k_step, v_step)
+        elif own_kv:
+            # whole prompts of a call that reads another call's entry: that call's keys
+            k_step, v_step = ctx.extras[("step_kv", binding.entry)]
+        if cache.k.dtype != act:
+            raise K.KernelError("the cache and the activations must share one dtype")
+        K.rope_kvstore(qkv, ctx.positions, ctx.token_row, ctx.seq_end, inv_freq, q,
+                       k_step if write else None, v_step if write else None,
+                       cache.k if write else None, cache.v if write else None,
+                       cache.page_table if write else None, cache.table_stride, cache.ring,
+                       nh, nk, hd, rotary_dim, style, ctx.status)
+
+        o = torch.empty((n, nh * hd), dtype=act, device=dev)
+        if own_kv:
+            K.attention_packed(q, k_step, v_step, ctx.token_row, ctx.positions, ctx.cu_seqlens, o,
+                               nh, nk, hd, self.window, self.scale)
+        else:
+            # keys and values come from the cache: a later token of a sequence
+            if cache.ring and not ctx.single_token:
+                raise K.KernelError(
+                    "a windowed cache is read one token at a time: several tokens of a sequence "
+                    "in one step must start at position 0")
+            lo_bound = ctx.max_end
+            n_chunks = max(1, -(-lo_bound // DECODE_CHUNK))
+            partial = None
+            if n_chunks > 1:
+                partial = torch.empty((n * nh * n_chunks * (hd + 2),), dtype=torch.float32,
+                                      device=dev)
+            K.attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions, cache.page_table,
+                              cache.table_stride, cache.ring, o, partial, nh, nk, hd, self.window,
+                              DECODE_CHUNK, n_chunks, self.scale)
+        self.out.forward(o, torch.float32, out=residual, accumulate=True)

@@ -1,0 +1,150 @@
+"""Interfaces of the parts a layer is put together from, and what a part sees of a step.
+
+A part has its sizes and constants as constructor parameters, names the tensors it wants
+from the checkpoint, and runs on whatever batch the step context describes.  No part knows
+which model it is in.  The five roles:
+
+``Norm``               ``forward(x32, out_dtype, rows=None) -> y``
+``PositionEncoding``   either ``fused_rotary()`` (parameters the fused rotary kernel takes)
+                       or ``apply(qkv32, ctx, n_heads, n_kv_heads, head_dim)`` in place
+``Mixer``              ``cache_request()``, ``state_request()``,
+                       ``forward_add(x, ctx, binding, residual)``
+``FeedForward``        ``forward_add(x, ctx, residual)``
+``Block``              ``mix(h, ctx, binding)`` then ``feed(h, ctx)``; the engine may drop
+                       rows of ``h`` between the two (only wanted rows go on after the last
+                       mixer, as the reference does: src/models/qwen2/graph.rs:126-138)
+
+The residual stream ``h`` is float32 [tokens, width]; ``x`` is a normed copy in the
+activation dtype.  ``forward_add`` adds the part's output into ``h`` in float32.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..weights.spec import TensorSpec
+
+
+@dataclass(frozen=True)
+class CacheRequest:
+    """Keys and values a mixer keeps per position.  ``window`` 0: every position is kept;
+    otherwise only the last ``window`` positions are ever read."""
+
+    n_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateRequest:
+    """Per-sequence state of fixed size, zeroed when a slot is handed out."""
+
+    name: str
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class CacheView:
+    """One cache entry as kernels see it."""
+
+    k: torch.Tensor                 # [pages, n_kv_heads, 64, head_dim]
+    v: torch.Tensor
+    page_table: torch.Tensor        # int32 [batch rows, table_stride]
+    table_stride: int
+    ring: int                       # 0 = linear, else ring length in positions
+
+
+@dataclass
+class CallBinding:
+    """What one entry of the run order gives its mixer: its cache entry (if the mixer asked
+    for one), whether this call writes it, and its per-sequence state tensors
+    ``[max_slots, *shape]`` by name."""
+
+    cache: Optional[CacheView] = None
+    writes_cache: bool = True
+    entry: int = -1                 # which cache entry (calls that share keys name the same)
+    has_readers: bool = False       # another call reads the entry this call writes
+    state: Dict[str, torch.Tensor] = field(default_factory=dict)
+
+
+@dataclass
+class StepContext:
+    """The batch of one step, as device tensors plus the few host numbers kernels need for
+    their launch shape.  Row ``b`` of the batch is one sequence; tokens are packed row
+    after row."""
+
+    device: torch.device
+    act_dtype: torch.dtype
+    n_tokens: int
+    n_rows: int
+    token_ids: torch.Tensor         # int32 [n_tokens]
+    positions: torch.Tensor         # int32 [n_tokens] absolute position of each token
+    token_row: torch.Tensor         # int32 [n_tokens] batch row of each token
+    cu_seqlens: torch.Tensor        # int32 [n_rows + 1]
+    seq_end: torch.Tensor           # int32 [n_rows] sequence length after this step
+    slots: torch.Tensor             # int32 [n_rows] slot of each row
+    from_start: bool                # every row starts at position 0 (whole prompts)
+    single_token: bool              # every row brings exactly one token
+    max_row_tokens: int
+    max_end: int                    # host: upper bound of seq_end (sizes key chunks)
+    status: torch.Tensor            # int32 [1] error bits set by kernels
+    host_slots: Sequence[int] = ()
+    extras: Dict[str, Any] = field(default_factory=dict)
+
+
+class Part:
+    """Common to all roles: the tensors wanted and how they are taken in."""
+
+    def tensor_specs(self, prefix: str) -> List[TensorSpec]:
+        return []
+
+    def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
+        """Takes its tensors (already on the device, in the precision they are held in)."""
+
+
+class Norm(Part):
+    def forward(self, x32: torch.Tensor, out_dtype: torch.dtype,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def fused_rotary(self, device: torch.device) -> Optional[Tuple[torch.Tensor, int, int]]:
+        """(inv_freq float32 [rotary_dim/2], rotary_dim, style) for the fused rotary kernel,
+        or None if this encoding is not a rotation of pairs."""
+        return None
+
+    def apply(self, qkv32: torch.Tensor, ctx: StepContext, n_heads: int, n_kv_heads: int,
+              head_dim: int) -> None:
+        """Changes q and k inside ``qkv32`` [tokens, (n_heads + 2 n_kv) * head_dim] in place."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_request(self) -> Optional[CacheRequest]:
+        return None
+
+    def state_request(self) -> Sequence[StateRequest]:
+        return ()
+
+    def forward_add(self, x: torch.Tensor, ctx: StepContext, binding: CallBinding,
+                    residual: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward_add(self, x: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class Block(Part):
+    mixer: Mixer
+
+    def mix(self, h: torch.Tensor, ctx: StepContext, binding: CallBinding) -> None:
+        raise NotImplementedError
+
+    def feed(self, h: torch.Tensor, ctx: StepContext) -> None:
+        raise NotImplementedError

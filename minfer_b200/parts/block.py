@@ -1,0 +1,41 @@
+"""Pre-norm block with two residual adds: h += mixer(norm1(h)); h += ffn(norm2(h))
+(src/models/qwen2/graph.rs:59-64, 137, 154-155, 176)."""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from ..config.base import LayerSpec
+from .base import Block, CallBinding, StepContext
+
+
+class PreNormBlock(Block):
+    def __init__(self, layer: LayerSpec):
+        from ..registry import build_part
+        self.prefix = layer.prefix
+        self.mixer_norm = build_part("norm", layer.mixer_norm)
+        self.mixer = build_part("mixer", layer.mixer)
+        self.feed_forward_norm = build_part("norm", layer.feed_forward_norm)
+        self.feed_forward = build_part("feed_forward", layer.feed_forward)
+
+    def _parts(self):
+        return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
+
+    def tensor_specs(self, prefix: str = "") -> List:
+        specs = []
+        for part in self._parts():
+            specs += part.tensor_specs(self.prefix)
+        return specs
+
+    def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
+        for part in self._parts():
+            part.load(self.prefix, weights)
+
+    def mix(self, h: torch.Tensor, ctx: StepContext, binding: CallBinding) -> None:
+        x = self.mixer_norm.forward(h, ctx.act_dtype)
+        self.mixer.forward_add(x, ctx, binding, h)
+
+    def feed(self, h: torch.Tensor, ctx: StepContext) -> None:
+        x = self.feed_forward_norm.forward(h, ctx.act_dtype)
+        self.feed_forward.forward_add(x, ctx, h)

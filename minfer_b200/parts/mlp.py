@@ -1,0 +1,56 @@
+"""Gated feed-forward: down( act(gate(x)) * up(x) ), no biases.
+
+The reference builds it as silu + mul that its fusion pass folds into SwiGLU
+(src/models/qwen2/graph.rs:154-175, src/graph/fusion.rs:37-87), with
+silu(z) = z / (1 + exp(-z)) (src/vec_ops.rs:131-146); its Metal path packs gate|up into
+one matrix (src/models/qwen2/graph.rs:148-169).  Here gate|up is always one product and
+the down projection adds into the residual stream in its epilogue.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kernels import api as K
+from ..weights.spec import MATRIX, Init, TensorSpec
+from .base import FeedForward, StepContext
+from .linear import Linear
+
+
+class GatedMlp(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 init_std: float = 0.02):
+        if activation != "silu":
+            raise ValueError(f"the gated feed-forward has the 'silu' activation only, got "
+                             f"{activation!r}")
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.init_std = float(init_std)
+        self.gate_up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+
+    def tensor_specs(self, prefix: str) -> List[TensorSpec]:
+        p = f"{prefix}mlp."
+        init = Init(0.0, self.init_std)
+        return [TensorSpec(f"{p}gate_proj.weight", (self.intermediate_size, self.hidden_size),
+                           MATRIX, init),
+                TensorSpec(f"{p}up_proj.weight", (self.intermediate_size, self.hidden_size),
+                           MATRIX, init),
+                TensorSpec(f"{p}down_proj.weight", (self.hidden_size, self.intermediate_size),
+                           MATRIX, init)]
+
+    def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
+        p = f"{prefix}mlp."
+        g, u = weights[f"{p}gate_proj.weight"], weights[f"{p}up_proj.weight"]
+        if g.dtype != u.dtype:
+            g, u = g.to(torch.float32), u.to(torch.float32)
+        self.gate_up = Linear(torch.cat([g, u], dim=0).contiguous())
+        self.down = Linear(weights[f"{p}down_proj.weight"])
+
+    def forward_add(self, x: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
+        gu = self.gate_up.forward(x, ctx.act_dtype)
+        act = torch.empty((x.shape[0], self.intermediate_size), dtype=ctx.act_dtype,
+                          device=x.device)
+        K.swiglu(gu, act)
+        self.down.forward(act, torch.float32, out=residual, accumulate=True)

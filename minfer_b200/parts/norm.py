@@ -1,0 +1,34 @@
+"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * w, the weight applied after the scale, no bias
+(src/vec_ops.rs:500-522; src/graph/cpu_backend.rs:195-213)."""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..kernels import api as K
+from ..weights.spec import VECTOR, Init, TensorSpec
+from .base import Norm
+
+
+class RmsNorm(Norm):
+    def __init__(self, size: int, eps: float, name: str = "norm", init_std: float = 0.0):
+        self.size = int(size)
+        self.eps = float(eps)
+        self.name = name
+        self.init_std = float(init_std)
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self, prefix: str) -> List[TensorSpec]:
+        return [TensorSpec(f"{prefix}{self.name}.weight", (self.size,), VECTOR,
+                           Init(1.0, self.init_std))]
+
+    def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
+        self.weight = weights[f"{prefix}{self.name}.weight"]
+
+    def forward(self, x32: torch.Tensor, out_dtype: torch.dtype,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n = x32.shape[0] if rows is None else rows.numel()
+        out = torch.empty((n, self.size), dtype=out_dtype, device=x32.device)
+        K.rmsnorm(x32, self.weight, self.eps, out, rows)
+        return out

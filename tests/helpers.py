@@ -1,0 +1,61 @@
+"""Tiny configurations and shared helpers of the tests."""
+from __future__ import annotations
+
+import os
+import tempfile
+from typing import Dict, List, Sequence
+
+import torch
+
+# Two tiny configurations of the architecture that differ in every size and option.
+TINY_A = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 256, "hidden_size": 64, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 1, "intermediate_size": 128,
+    "rope_theta": 10000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+    "use_sliding_window": False, "max_position_embeddings": 512, "eos_token_id": 7,
+}
+TINY_B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 389, "hidden_size": 192, "num_hidden_layers": 3,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "intermediate_size": 328,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+    "use_sliding_window": True, "sliding_window": 16, "max_window_layers": 1,
+    "max_position_embeddings": 1024, "eos_token_id": [3, 5],
+}
+# head size 48 (a multiple of 16 that is no power of two), 3:1 groups, window wider than a page
+TINY_C = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 131, "hidden_size": 144, "num_hidden_layers": 2,
+    "num_attention_heads": 3, "num_key_value_heads": 3, "intermediate_size": 200,
+    "rope_theta": 50000.0, "rms_norm_eps": 3e-6, "tie_word_embeddings": False,
+    "use_sliding_window": True, "sliding_window": 70, "max_window_layers": 0,
+    "max_position_embeddings": 1024,
+}
+TINY = {"A": (TINY_A, 0, 0.0), "B": (TINY_B, 1, 0.01), "C": (TINY_C, 2, 0.02)}
+
+# Tolerances, as a fraction of the largest logit magnitude of the comparison.  float32
+# differs from the float64 plain implementation by summation order only; bfloat16 rounds
+# weights-times-activations products' inputs to 8 bits of mantissa at every layer.
+TOL = {"float32": 2e-5, "bfloat16": 2.5e-2}
+
+
+def make_folder(name: str, weight_std: float = 0.08, store_dtype: str = "bfloat16") -> str:
+    """A random model folder for a tiny configuration, in a fresh temporary folder.  The
+    weights are larger than N(0, 0.02) so that logits differ visibly between tokens."""
+    from minfer_b200.model import write_random_model
+    cfg, seed, norm_std = TINY[name]
+    folder = tempfile.mkdtemp(prefix=f"minfer_b200_tiny{name}_")
+    write_random_model(folder, cfg, seed, store_dtype, norm_std=norm_std, weight_std=weight_std)
+    return folder
+
+
+def random_ids(n: int, vocab: int, seed: int) -> List[int]:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    got = got.detach().to(torch.float64).cpu()
+    want = want.detach().to(torch.float64).cpu()
+    return float((got - want).abs().max() / max(1e-30, float(want.abs().max())))

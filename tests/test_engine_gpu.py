@@ -1,0 +1,95 @@
+"""The engine against the plain implementation, in float32 and in bfloat16: each request
+alone and whole; with the last 32 tokens one by one; in batches of unequal lengths whose
+shorter requests end earlier, one batch after another so that slots are used again."""
+import pytest
+import torch
+
+import plain_qwen2 as P
+from helpers import TINY, TOL, make_folder, random_ids, rel_err
+
+pytestmark = pytest.mark.gpu
+
+LENGTHS = [37, 5, 90, 64, 1, 65, 130]
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C"])
+def tiny(request):
+    folder = make_folder(request.param)
+    cfg, w = P.load_folder(folder)
+    prompts = [random_ids(n, cfg["vocab_size"], 100 + i) for i, n in enumerate(LENGTHS)]
+    plain = [P.forward(cfg, w, ids) for ids in prompts]
+    return {"name": request.param, "folder": folder, "cfg": cfg, "prompts": prompts, "plain": plain}
+
+
+def _engine(folder, dtype, max_tokens=2048):
+    from minfer_b200.engine.step import Engine
+    from minfer_b200.model import Model
+    return Engine(Model.from_folder(folder, dtype, "cuda:0"), max_tokens=max_tokens)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_requests(tiny, dtype):
+    eng = _engine(tiny["folder"], dtype)
+    for ids, want in zip(tiny["prompts"], tiny["plain"]):
+        s = eng.acquire()
+        got = eng.step([s], [ids], [list(range(len(ids)))])
+        eng.release(s)
+        assert got.shape == want.shape
+        assert rel_err(got, want) < TOL[dtype]
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_last_tokens_one_by_one(tiny, dtype):
+    eng = _engine(tiny["folder"], dtype)
+    for ids, want in zip(tiny["prompts"], tiny["plain"]):
+        n = len(ids)
+        head = max(1, n - 32)
+        s = eng.acquire()
+        rows = [eng.step([s], [ids[:head]], [list(range(head))])]
+        for t in range(head, n):
+            rows.append(eng.step([s], [[ids[t]]], [[0]]))
+        eng.release(s)
+        got = torch.cat(rows)
+        assert rel_err(got, want) < TOL[dtype]
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_unequal_batches_slots_reused(tiny, dtype):
+    """Batches of unequal lengths: the prompts' first parts in one step, then one token
+    each; a request that runs out of tokens leaves the batch; the next batch starts in the
+    slots the first one gave back."""
+    eng = _engine(tiny["folder"], dtype, max_tokens=1024)
+    prompts, plain = tiny["prompts"], tiny["plain"]
+    batches = [[0, 1, 2], [3, 4, 5, 6], [2, 0]]
+    seen_slots = []
+    for batch in batches:
+        slots = [eng.acquire() for _ in batch]
+        seen_slots.append(list(slots))
+        # every request decodes its last min(8, n-1) tokens one by one
+        heads = {r: max(1, len(prompts[r]) - 8) for r in batch}
+        got = {r: [] for r in batch}
+        live = list(batch)
+        out = eng.step([slots[batch.index(r)] for r in live], [prompts[r][:heads[r]] for r in live],
+                       [list(range(heads[r])) for r in live])
+        at = 0
+        for r in live:
+            got[r].append(out[at:at + heads[r]])
+            at += heads[r]
+        pos = dict(heads)
+        while True:
+            live = [r for r in live if pos[r] < len(prompts[r])]
+            if not live:
+                break
+            out = eng.step([slots[batch.index(r)] for r in live], [[prompts[r][pos[r]]] for r in live])
+            for i, r in enumerate(live):
+                got[r].append(out[i:i + 1])
+                pos[r] += 1
+        for s in slots:
+            eng.release(s)
+        for r in batch:
+            assert rel_err(torch.cat(got[r]), plain[r]) < TOL[dtype], (tiny["name"], r)
+    assert set(seen_slots[1]) & set(seen_slots[0]), "the second batch did not reuse a slot"
+    assert all(n == eng.cache.groups[i].n_pages for i, n in enumerate(eng.cache.free_pages()))
+    eng.check_status()
