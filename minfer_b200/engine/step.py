@@ -39,7 +39,8 @@ class Engine:
     """A model plus its cache.  ``max_tokens`` is the most tokens live sequences hold at any
     time, each sequence's count rounded up to a multiple of 64; it sizes the cache."""
 
-    def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None):
+    def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None,
+                 cuda_graphs: bool = True):
         if model.device is None or model.device.type != "cuda":
             raise StepError("the model's weights must be on a CUDA device (there is no CPU path)")
         self.model = model
@@ -50,6 +51,7 @@ class Engine:
         if max_seqs is None:
             max_seqs = max(1, min(max_tokens // PAGE, 256))
         self.max_seqs = int(max_seqs)
+        self.cuda_graphs = bool(cuda_graphs)
 
         # which call writes which cache entry, and what that entry has to hold
         requests: Dict[int, GroupKey] = {}
@@ -82,6 +84,8 @@ class Engine:
             self._call_state.append(tensors)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps_run = 0
+        self.h2d_bytes = 0          # bytes of step inputs copied to the device so far
+        self.d2h_bytes = 0          # bytes of results read back so far
 
     # ---- slots --------------------------------------------------------------------------
     def acquire(self) -> int:
@@ -142,6 +146,38 @@ class Engine:
         self.steps_run += 1
         return logits
 
+    def decode_on_device(self, slots: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
+        """One token per sequence, the token ids already on the device (int32 [rows], for
+        instance the sampler's output): nothing is read back, so steps can follow one
+        another without the host waiting.  Out-of-range ids set the status word."""
+        n_rows = len(slots)
+        if tokens.dtype != torch.int32 or tokens.numel() != n_rows or not tokens.is_cuda:
+            raise StepError("decode_on_device takes int32 token ids on the device, one per row")
+        if len(set(slots)) != n_rows:
+            raise StepError("a slot appears twice in one step")
+        starts = [self.cache.length(s) for s in slots]
+        for b in range(n_rows):
+            if starts[b] < 1:
+                raise StepError("decode_on_device goes on from a prompt; this slot is empty")
+            if starts[b] + 1 > self.model.plan.max_positions:
+                raise StepError(f"sequence in slot {slots[b]} is at the model's last position")
+            self.cache.reserve(slots[b], starts[b] + 1)
+        counts = [1] * n_rows
+        ctx, want_rows = self._context(slots, [[0]] * n_rows, counts, starts, [[0]] * n_rows,
+                                       False, True)
+        ctx.token_ids = tokens
+        logits = self._run(ctx, want_rows)
+        for b in range(n_rows):
+            self.cache.set_length(slots[b], starts[b] + 1)
+        self.steps_run += 1
+        return logits
+
+    def assume_filled(self, slot: int, length: int) -> None:
+        """Benchmarks only: gives the sequence ``length`` positions of cache without running
+        the model; whatever the pages hold stands in for keys and values."""
+        self.cache.reserve(slot, length)
+        self.cache.set_length(slot, length)
+
     # ---- metadata -----------------------------------------------------------------------
     def _context(self, slots, tokens, counts, starts, want, from_start, single):
         n_rows = len(slots)
@@ -165,6 +201,7 @@ class Engine:
         sizes = [len(f) for f in fields]
         host = torch.tensor([x for f in fields for x in f], dtype=torch.int32).pin_memory()
         dev = host.to(self.device, non_blocking=True)
+        self.h2d_bytes += host.numel() * 4
         views, at = [], 0
         for n in sizes:
             views.append(dev[at:at + n])

@@ -33,7 +33,12 @@ def dtype_code(dtype: torch.dtype) -> int:
         raise KernelError(f"kernels take float32 or bfloat16, not {dtype}") from None
 
 
-def _check(code: int, what: str) -> None:
+launches = 0      # kernels launched by this module since import (benchmarks read the difference)
+
+
+def _check(code: int, what: str, n_kernels: int = 1) -> None:
+    global launches
+    launches += n_kernels
     if code != 0:
         why = _ERRORS.get(code, f"CUDA error {code}")
         raise KernelError(f"{what}: {why}")
@@ -246,7 +251,7 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _i32(row_pos, "row_pos"), _i32(page_table, "page_table"), int(table_stride), int(ring),
         _ptr(out, "out"), _f32(partial, "partial"), rows, n_heads, n_kv, head_dim, int(window),
         int(chunk), int(n_chunks), float(scale), dtype_code(q.dtype), _stream()),
-        "attention_paged")
+        "attention_paged", 2 if n_chunks > 1 else 1)
 
 
 # ---------------------------------------------------------------------------------------

@@ -1,0 +1,57 @@
+"""The sampler that generation uses: one kernel launch per step for the whole batch.
+
+Per sequence it keeps, in the cache's fixed-size state area, the window of the last 64
+tokens the penalties look at and the number of draws made, so that a sequence's draws do
+not depend on the rest of the batch: draw n of stream s is Philox(seed; n, s).
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import torch
+
+from ..kernels import api as K
+from .params import RECENT_WINDOW, SamplingParams
+
+STATE_NAME = "sampler"
+
+
+class DeviceSampler:
+    def __init__(self, engine, params: SamplingParams):
+        params.validate()
+        self.engine = engine
+        self.params = params
+        self.device = engine.device
+        pool = engine.cache.state
+        self.width = 2 + RECENT_WINDOW
+        if STATE_NAME not in pool.tensors:
+            pool.add(STATE_NAME, (self.width,), torch.int32)
+        self.state = pool.tensors[STATE_NAME]
+        if K.sampler_state_ints() != self.width:
+            raise K.KernelError("the sampler kernel and its state layout disagree")
+
+    def begin(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> None:
+        """Seeds each sequence's window with the tail of its prompt (src/main.rs:537-540) and
+        sets its draw counter to zero."""
+        rows = torch.zeros((len(slots), self.width), dtype=torch.int32)
+        for b, prompt in enumerate(prompts):
+            tail = list(prompt[-RECENT_WINDOW:])
+            rows[b, 0] = len(tail)
+            rows[b, 2:2 + len(tail)] = torch.tensor(tail, dtype=torch.int32)
+        index = torch.tensor(list(slots), dtype=torch.long, device=self.device)
+        self.state.index_copy_(0, index, rows.to(self.device))
+
+    def sample(self, logits: torch.Tensor, slots: Sequence[int],
+               streams: Sequence[int]) -> List[int]:
+        """One token per row of ``logits`` (changed in place); returns them on the host."""
+        p = self.params
+        n = logits.shape[0]
+        meta = torch.tensor(list(slots) + list(streams), dtype=torch.int32).to(self.device)
+        out = torch.empty(n, dtype=torch.int32, device=self.device)
+        K.sample(logits, out, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
+                 repeat_penalty=p.repeat_penalty, frequency_penalty=p.frequency_penalty,
+                 presence_penalty=p.presence_penalty, seed=p.seed, slots=meta[:n],
+                 state=self.state, stream_ids=meta[n:], update_state=True)
+        self.engine.h2d_bytes += meta.numel() * 4
+        self.engine.d2h_bytes += n * 4
+        return out.cpu().tolist()

@@ -1,0 +1,118 @@
+"""Generation through the entry point against the plain implementation: greedy tokens,
+sampled tokens with the same seed, stop tokens, batches one after another, and the
+sampling kernel alone."""
+import math
+
+import pytest
+import torch
+
+import plain_qwen2 as P
+from helpers import TINY, make_folder, random_ids
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", params=["A", "B"])
+def tiny(request):
+    folder = make_folder(request.param)
+    cfg, w = P.load_folder(folder)
+    return {"name": request.param, "folder": folder, "cfg": cfg, "w": w}
+
+
+def _generator(folder, dtype="float32", max_batch=4, max_tokens=2048):
+    from minfer_b200.engine.generate import Generator
+    from minfer_b200.model import Model
+    return Generator(Model.from_folder(folder, dtype, "cuda:0"), max_tokens=max_tokens,
+                     max_batch=max_batch)
+
+
+def test_greedy_equals_plain(tiny):
+    from minfer_b200.sampling.params import SamplingParams
+    cfg, w = tiny["cfg"], tiny["w"]
+    prompts = [random_ids(n, cfg["vocab_size"], 40 + n) for n in (5, 9, 13, 1, 33)]
+    want = [P.generate(cfg, w, p, 8) for p in prompts]
+    gen = _generator(tiny["folder"], max_batch=3)          # 5 requests -> two batches
+    got = gen.generate(prompts, 8, SamplingParams.greedy(), stop_token_ids=[])
+    assert [r.tokens for r in got] == want
+    assert gen.stats.batches == 2
+    assert all(r.finish_reason == "length" for r in got)
+
+
+def test_stop_token_ends_a_sequence_early(tiny):
+    from minfer_b200.sampling.params import SamplingParams
+    cfg, w = tiny["cfg"], tiny["w"]
+    prompts = [random_ids(n, cfg["vocab_size"], 70 + n) for n in (6, 11, 3)]
+    free = [P.generate(cfg, w, p, 10) for p in prompts]
+    stop = free[1][4]                     # the fifth token of the second request stops it
+    want = [P.generate(cfg, w, p, 10, stop_ids=[stop]) for p in prompts]
+    gen = _generator(tiny["folder"])
+    got = gen.generate(prompts, 10, SamplingParams.greedy(), stop_token_ids=[stop])
+    assert [r.tokens for r in got] == want
+    assert got[1].finish_reason == "stop" and len(got[1].tokens) <= 4
+    assert stop not in got[1].tokens
+    # every slot and page went back
+    assert gen.engine.cache.slots.n_free() == gen.engine.max_seqs
+    assert all(n == g.n_pages for n, g in zip(gen.engine.cache.free_pages(), gen.engine.cache.groups))
+
+
+@pytest.mark.parametrize("params", [
+    dict(temperature=0.8, top_k=0, top_p=1.0, repeat_penalty=1.0),
+    dict(temperature=0.8, top_k=40, top_p=0.95, repeat_penalty=1.1),
+    dict(temperature=1.3, top_k=5, top_p=0.5, repeat_penalty=1.3, frequency_penalty=0.2,
+         presence_penalty=0.1),
+    dict(temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.5, presence_penalty=0.4),
+])
+def test_sampled_generation_equals_plain_and_ignores_the_batch(tiny, params):
+    from minfer_b200.sampling.params import SamplingParams
+    cfg, w = tiny["cfg"], tiny["w"]
+    prompts = [random_ids(n, cfg["vocab_size"], 90 + n) for n in (1, 7, 20, 33)]
+    sp = SamplingParams(seed=7, **params)
+    gen = _generator(tiny["folder"])
+    got = [r.tokens for r in gen.generate(prompts, 12, sp, stop_token_ids=[])]
+    for i, p in enumerate(prompts):
+        want = P.generate(cfg, w, p, 12, temp=sp.temperature, top_k=sp.top_k, top_p=sp.top_p,
+                          repeat=sp.repeat_penalty, frequency=sp.frequency_penalty,
+                          presence=sp.presence_penalty, seed=7, stream=i)
+        assert got[i] == want, (i, params)
+    # the same requests in another batch composition give the same tokens
+    gen2 = _generator(tiny["folder"], max_batch=2)
+    again = [r.tokens for r in gen2.generate(prompts, 12, sp, stop_token_ids=[])]
+    assert again == got
+
+
+def test_sampling_kernel_alone():
+    """The kernel against the plain sampler on logits made so that ties, the top-k edge and
+    the top-p edge all occur; a vocabulary that is no power of two."""
+    from minfer_b200.kernels import api as K
+    V, rows = 1531, 6
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(rows, V, generator=g) * 3.0
+    logits[0, 100] = logits[0, 7] = logits[0].max() + 1.0           # tie: lowest index wins
+    logits[1, :50] = 2.5                                            # many ties at the top-k edge
+    logits[2, 5] = 30.0                                             # one dominant token
+    cases = [dict(temp=0.0, top_k=0, top_p=1.0), dict(temp=0.7, top_k=40, top_p=0.95),
+             dict(temp=1.0, top_k=0, top_p=0.9), dict(temp=1.0, top_k=0, top_p=1.0),
+             dict(temp=2.0, top_k=3, top_p=1.0)]
+    for case in cases:
+        for seed in (1, 2):
+            dev = logits.clone().cuda()
+            out = torch.empty(rows, dtype=torch.int32, device="cuda")
+            K.sample(dev, out, temperature=case["temp"], top_k=case["top_k"], top_p=case["top_p"],
+                     repeat_penalty=1.0, frequency_penalty=0.0, presence_penalty=0.0, seed=seed)
+            got = out.cpu().tolist()
+            for r in range(rows):
+                u = P.philox_uniform(seed, 0, r)
+                want = P.sample(logits[r].double(), case["temp"], case["top_k"], case["top_p"],
+                                1.0, 0.0, 0.0, [], u)
+                assert got[r] == want, (case, seed, r)
+
+
+def test_cli_generates(tiny, capsys):
+    from minfer_b200 import cli
+    rc = cli.main([tiny["folder"], "5,17,3", "--greedy", "--repeat-penalty", "1.0", "-n", "6",
+                   "--dtype", "float32", "--stop", "100000"])
+    out = capsys.readouterr().out
+    assert rc == 0
+    want = P.generate(tiny["cfg"], tiny["w"], [5, 17, 3], 6)
+    assert " ".join(str(t) for t in want) in out
+    assert "Prefill: 3 tokens" in out and "Generated: 6 tokens" in out
