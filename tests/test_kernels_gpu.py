@@ -1,0 +1,328 @@
+"""Each kernel alone against a plain PyTorch float32/float64 statement of the same op, at
+sizes other than the engine's tiny models: odd widths, head sizes 16..256, groups, windows,
+rings, chunked keys."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return 2e-5 if dtype == torch.float32 else 2e-2
+
+
+def close(got, want, dtype, scale=None):
+    got, want = got.double().cpu(), want.double().cpu()
+    s = float(want.abs().max()) if scale is None else scale
+    err = float((got - want).abs().max()) / max(s, 1e-30)
+    assert err < tol(dtype), err
+
+
+def status():
+    return torch.zeros(1, dtype=torch.int32, device="cuda")
+
+
+def test_embed_and_bad_token_flag():
+    from minfer_b200.kernels import api as K
+    for dt in DTYPES:
+        table = torch.randn(131, 72).to(dt).cuda()
+        ids = torch.tensor([0, 130, 5, 5, 77], dtype=torch.int32, device="cuda")
+        out = torch.empty(5, 72, device="cuda")
+        st = status()
+        K.embed(table, ids, out, st)
+        assert torch.equal(out, table.float()[ids.long()]) and int(st) == 0
+    bad = torch.tensor([3, 131], dtype=torch.int32, device="cuda")
+    out = torch.full((2, 72), 9.0, device="cuda")
+    K.embed(table, bad, out, st)
+    assert int(st) & 1 and float(out[1].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("width", [64, 200, 3584, 5000])
+def test_rmsnorm(width):
+    from minfer_b200.kernels import api as K
+    x = (torch.randn(7, width) * 3).cuda()
+    w = (1 + 0.1 * torch.randn(width)).cuda()
+    want = x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + 1e-5) * w.double()
+    for dt in DTYPES:
+        out = torch.empty(7, width, dtype=dt, device="cuda")
+        K.rmsnorm(x, w, 1e-5, out)
+        close(out, want, dt)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device="cuda")
+    out = torch.empty(3, width, device="cuda")
+    K.rmsnorm(x, w, 1e-5, out, rows)
+    close(out, want[[6, 0, 3]], torch.float32)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 16), (5, 130, 72), (64, 64, 64), (65, 67, 200),
+                                   (130, 389, 328), (3, 1000, 1031)])
+def test_gemm_simt_all_precisions(m, n, k):
+    from minfer_b200.kernels import api as K
+    g = torch.Generator().manual_seed(m * 1000 + n)
+    a32, w32 = torch.randn(m, k, generator=g), torch.randn(n, k, generator=g)
+    bias = torch.randn(n, generator=g).cuda()
+    for ta in DTYPES:
+        for tw in DTYPES:
+            a, w = a32.to(ta).cuda(), w32.to(tw).cuda()
+            want = a.double() @ w.double().t() + bias.double()
+            for tc in DTYPES:
+                out = torch.empty(m, n, dtype=tc, device="cuda")
+                K.gemm_simt(a, w, bias, out)
+                close(out, want, tc if tc == torch.bfloat16 else torch.float32)
+            acc = torch.randn(m, n, generator=g).cuda()
+            before = acc.clone()
+            K.gemm_simt(a, w, None, acc, accumulate=True)
+            close(acc, before.double() + a.double() @ w.double().t(), torch.float32)
+
+
+def test_gemm_rows_do_not_depend_on_the_batch():
+    """A row's result is bit-identical whether it is multiplied alone or among others."""
+    from minfer_b200.kernels import api as K
+    a = torch.randn(70, 200).cuda()
+    w = torch.randn(90, 200).cuda()
+    whole = torch.empty(70, 90, device="cuda")
+    K.gemm_simt(a, w, None, whole)
+    for r in (0, 33, 69):
+        one = torch.empty(1, 90, device="cuda")
+        K.gemm_simt(a[r:r + 1].contiguous(), w, None, one)
+        assert torch.equal(one[0], whole[r])
+
+
+def rope_reference(x, pos, inv_freq, rotary_dim, style):
+    """x [T, H, hd] float64."""
+    out = x.clone()
+    ang = pos.double()[:, None] * inv_freq.double()[None, :]
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    h = rotary_dim // 2
+    if style == 0:
+        a, b = x[..., :h], x[..., h:rotary_dim]
+        out[..., :h], out[..., h:rotary_dim] = a * cos - b * sin, a * sin + b * cos
+    else:
+        a, b = x[..., 0:rotary_dim:2], x[..., 1:rotary_dim:2]
+        out[..., 0:rotary_dim:2], out[..., 1:rotary_dim:2] = a * cos - b * sin, a * sin + b * cos
+    return out
+
+
+@pytest.mark.parametrize("hd,rotary_dim,style", [(16, 16, 0), (48, 48, 0), (64, 32, 0),
+                                                 (128, 128, 1), (32, 16, 1), (256, 256, 0)])
+def test_rope_kvstore_pages_and_rotation(hd, rotary_dim, style):
+    from minfer_b200.kernels import api as K
+    nh, nk = 3, 2
+    # two sequences: row 0 holds positions 100..104 (5 tokens), row 1 position 63 and 64
+    positions = torch.tensor([100, 101, 102, 103, 104, 63, 64], dtype=torch.int32)
+    rows = torch.tensor([0, 0, 0, 0, 0, 1, 1], dtype=torch.int32)
+    T = 7
+    qkv = torch.randn(T, (nh + 2 * nk) * hd)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(rotary_dim // 2).double() * 2 / rotary_dim))).float()
+    n_pages = 6
+    table = torch.tensor([[4, 2, -1], [5, 0, -1]], dtype=torch.int32)   # logical page -> physical
+    for dt in DTYPES:
+        kc = torch.zeros(n_pages, nk, 64, hd, dtype=dt, device="cuda")
+        vc = torch.zeros_like(kc)
+        q = torch.empty(T, nh, hd, dtype=dt, device="cuda")
+        ks = torch.empty(T, nk, hd, dtype=dt, device="cuda")
+        vs = torch.empty_like(ks)
+        st = status()
+        K.rope_kvstore(qkv.cuda(), positions.cuda(), rows.cuda(),
+                       torch.tensor([105, 65], dtype=torch.int32, device="cuda"), inv_freq.cuda(),
+                       q, ks, vs, kc, vc, table.cuda(), 3, 0, nh, nk, hd, rotary_dim, style, st)
+        x = qkv.double().reshape(T, nh + 2 * nk, hd)
+        want_q = rope_reference(x[:, :nh], positions, inv_freq, rotary_dim, style)
+        want_k = rope_reference(x[:, nh:nh + nk], positions, inv_freq, rotary_dim, style)
+        want_v = x[:, nh + nk:]
+        close(q, want_q, dt); close(ks, want_k, dt); close(vs, want_v, dt)
+        assert int(st) == 0
+        for t in range(T):
+            p, b = int(positions[t]), int(rows[t])
+            page = int(table[b, p // 64])
+            assert torch.equal(kc[page, :, p % 64, :], ks[t]) and torch.equal(vc[page, :, p % 64, :], vs[t])
+        written = {(int(table[int(rows[t]), int(positions[t]) // 64]), int(positions[t]) % 64)
+                   for t in range(T)}
+        mask = torch.ones(n_pages, 64, dtype=torch.bool)
+        for pg, off in written:
+            mask[pg, off] = False
+        untouched = kc.float().cpu().permute(0, 2, 1, 3)[mask]          # [page, offset] pairs
+        assert float(untouched.abs().sum()) == 0.0                       # nothing else was touched
+
+
+def test_rope_kvstore_ring_keeps_only_the_tail_and_flags_missing_pages():
+    from minfer_b200.kernels import api as K
+    nh, nk, hd, T = 1, 1, 16, 150
+    qkv = torch.randn(T, 3 * hd).cuda()
+    positions = torch.arange(T, dtype=torch.int32, device="cuda")
+    rows = torch.zeros(T, dtype=torch.int32, device="cuda")
+    kc = torch.zeros(2, nk, 64, hd, device="cuda"); vc = torch.zeros_like(kc)
+    q = torch.empty(T, nh, hd, device="cuda")
+    ks = torch.empty(T, nk, hd, device="cuda"); vs = torch.empty_like(ks)
+    st = status()
+    table = torch.tensor([[1, 0]], dtype=torch.int32, device="cuda")
+    K.rope_kvstore(qkv, positions, rows, torch.tensor([T], dtype=torch.int32, device="cuda"), None,
+                   q, ks, vs, kc, vc, table, 2, 128, nh, nk, hd, 0, 0, st)
+    assert int(st) == 0
+    for p in range(T - 128, T):                     # the last 128 positions, at p % 128
+        page = int(table[0, (p % 128) // 64])
+        assert torch.equal(vc[page, 0, p % 64], vs[p, 0])
+    assert torch.equal(ks, qkv[:, hd:2 * hd].reshape(T, 1, hd))       # no rotation asked for
+    bad = torch.tensor([[1, -1]], dtype=torch.int32, device="cuda")
+    K.rope_kvstore(qkv, positions, rows, torch.tensor([T], dtype=torch.int32, device="cuda"), None,
+                   q, ks, vs, kc, vc, bad, 2, 128, nh, nk, hd, 0, 0, st)
+    assert int(st) & 2
+
+
+def attention_reference(q, k, v, scale, window):
+    """q [T, nh, hd], k/v [T, nk, hd] of one sequence, float64."""
+    T, nh, hd = q.shape
+    g = nh // k.shape[1]
+    out = torch.zeros_like(q)
+    idx = torch.arange(T)
+    mask = idx[None, :] <= idx[:, None]
+    if window > 0:
+        mask &= (idx[:, None] - idx[None, :]) < window
+    for h in range(nh):
+        s = (q[:, h] @ k[:, h // g].t()) * scale
+        s = s.masked_fill(~mask, -math.inf)
+        out[:, h] = torch.softmax(s, dim=-1) @ v[:, h // g]
+    return out
+
+
+@pytest.mark.parametrize("hd,nh,nk,window", [(16, 4, 1, 0), (32, 6, 2, 16), (48, 3, 3, 70),
+                                             (64, 14, 2, 0), (128, 7, 1, 33), (256, 2, 2, 0)])
+def test_attention_packed_unequal_sequences(hd, nh, nk, window):
+    from minfer_b200.kernels import api as K
+    lens = [37, 1, 100, 65]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    g = torch.Generator().manual_seed(hd + nh)
+    q32, k32, v32 = (torch.randn(T, h, hd, generator=g) for h in (nh, nk, nk))
+    row_seq = torch.cat([torch.full((n,), b, dtype=torch.int32) for b, n in enumerate(lens)])
+    row_pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens])
+    scale = 1.0 / math.sqrt(hd)
+    for dt in DTYPES:
+        q, k, v = q32.to(dt).cuda(), k32.to(dt).cuda(), v32.to(dt).cuda()
+        out = torch.empty(T, nh * hd, dtype=dt, device="cuda")
+        K.attention_packed(q, k, v, row_seq.cuda(), row_pos.cuda(),
+                           torch.tensor(cu, dtype=torch.int32, device="cuda"), out, nh, nk, hd,
+                           window, scale)
+        for b, n in enumerate(lens):
+            sl = slice(cu[b], cu[b + 1])
+            want = attention_reference(q[sl].double().cpu(), k[sl].double().cpu(),
+                                       v[sl].double().cpu(), scale, window)
+            close(out[sl].reshape(n, nh, hd), want, dt, scale=float(v32.abs().max()))
+
+
+def test_attention_finds_a_far_key_among_hundreds():
+    """One key far back gets a score that stands out; the output must be its value."""
+    from minfer_b200.kernels import api as K
+    T, hd = 700, 64
+    q = torch.randn(T, 1, hd) * 0.1
+    k = torch.randn(T, 1, hd) * 0.1
+    v = torch.randn(T, 1, hd)
+    k[13, 0] = 0.0; k[13, 0, 5] = 40.0
+    q[T - 1, 0] = 0.0; q[T - 1, 0, 5] = 40.0            # score 1600 * scale at key 13
+    out = torch.empty(T, hd, device="cuda")
+    K.attention_packed(q.cuda(), k.cuda(), v.cuda(), torch.zeros(T, dtype=torch.int32, device="cuda"),
+                       torch.arange(T, dtype=torch.int32, device="cuda"),
+                       torch.tensor([0, T], dtype=torch.int32, device="cuda"), out, 1, 1, hd, 0, 0.125)
+    assert torch.allclose(out[T - 1].cpu(), v[13, 0], atol=1e-5)
+    # with a window that ends before key 13 it must NOT be seen
+    K.attention_packed(q.cuda(), k.cuda(), v.cuda(), torch.zeros(T, dtype=torch.int32, device="cuda"),
+                       torch.arange(T, dtype=torch.int32, device="cuda"),
+                       torch.tensor([0, T], dtype=torch.int32, device="cuda"), out, 1, 1, hd,
+                       T - 1 - 13, 0.125)
+    assert not torch.allclose(out[T - 1].cpu(), v[13, 0], atol=1e-2)
+    K.attention_packed(q.cuda(), k.cuda(), v.cuda(), torch.zeros(T, dtype=torch.int32, device="cuda"),
+                       torch.arange(T, dtype=torch.int32, device="cuda"),
+                       torch.tensor([0, T], dtype=torch.int32, device="cuda"), out, 1, 1, hd,
+                       T - 13, 0.125)                   # the window's edge: key 13 is the oldest seen
+    assert torch.allclose(out[T - 1].cpu(), v[13, 0], atol=1e-5)
+
+
+@pytest.mark.parametrize("hd,nh,nk,window,ring", [(16, 4, 1, 0, 0), (32, 6, 2, 16, 64),
+                                                  (48, 3, 3, 70, 128), (128, 28, 4, 0, 0),
+                                                  (64, 2, 1, 100, 0)])
+def test_attention_paged_matches_packed_history(hd, nh, nk, window, ring):
+    """Queries at the ends of sequences of unequal lengths over a scattered paged cache."""
+    from minfer_b200.kernels import api as K
+    lens = [600, 1, 64, 65, 300]
+    B = len(lens)
+    n_pages = 40
+    g = torch.Generator().manual_seed(7)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    scale = 1.0 / math.sqrt(hd)
+    for dt in DTYPES:
+        kc = torch.randn(n_pages, nk, 64, hd, generator=g).to(dt).cuda()   # stale values everywhere
+        vc = torch.randn(n_pages, nk, 64, hd, generator=g).to(dt).cuda()
+        width = 10
+        table = torch.full((B, width), -1, dtype=torch.int32)
+        hist_k, hist_v = [], []
+        for b, n in enumerate(lens):
+            kk = torch.randn(n, nk, hd, generator=g).to(dt)
+            vv = torch.randn(n, nk, hd, generator=g).to(dt)
+            hist_k.append(kk); hist_v.append(vv)
+            lo = max(0, n - ring) if ring else 0
+            for p in range(lo, n):
+                pe = p % ring if ring else p
+                lp = pe // 64
+                if table[b, lp] < 0:
+                    table[b, lp] = perm.pop()
+                kc[table[b, lp], :, p % 64] = kk[p].cuda()
+                vc[table[b, lp], :, p % 64] = vv[p].cuda()
+        q32 = torch.randn(B, nh, hd, generator=g)
+        q = q32.to(dt).cuda()
+        row_seq = torch.arange(B, dtype=torch.int32, device="cuda")
+        row_pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device="cuda")
+        for chunk, n_chunks in ((256, 3), (64, 10), (1024, 1)):
+            out = torch.empty(B, nh * hd, dtype=dt, device="cuda")
+            partial = torch.empty(B * nh * n_chunks * (hd + 2), device="cuda")
+            K.attention_paged(q, kc, vc, row_seq, row_pos, table.cuda(), width, ring, out, partial,
+                              nh, nk, hd, window, chunk, n_chunks, scale)
+            for b, n in enumerate(lens):
+                qq = torch.zeros(n, nh, hd, dtype=torch.float64)
+                qq[n - 1] = q[b].double().cpu()
+                want = attention_reference(qq, hist_k[b].double(), hist_v[b].double(), scale, window)
+                close(out[b].reshape(nh, hd), want[n - 1], dt, scale=3.0)
+
+
+def test_swiglu_gather_cast():
+    from minfer_b200.kernels import api as K
+    gu = torch.randn(5, 2 * 328).cuda()
+    want = torch.nn.functional.silu(gu[:, :328].double()) * gu[:, 328:].double()
+    for dt in DTYPES:
+        out = torch.empty(5, 328, dtype=dt, device="cuda")
+        K.swiglu(gu, out)
+        close(out, want, dt)
+    out = torch.empty(5, 328, dtype=torch.bfloat16, device="cuda")
+    K.swiglu(gu.bfloat16(), out)
+    close(out, torch.nn.functional.silu(gu.bfloat16()[:, :328].double()) * gu.bfloat16()[:, 328:].double(),
+          torch.bfloat16)
+    x = torch.randn(9, 100).cuda()
+    rows = torch.tensor([8, 8, 0, 3], dtype=torch.int32, device="cuda")
+    picked = torch.empty(4, 100, device="cuda")
+    K.gather_rows(x, rows, picked)
+    assert torch.equal(picked, x[rows.long()])
+    b = torch.empty(9, 100, dtype=torch.bfloat16, device="cuda")
+    K.cast(x, b)
+    assert torch.equal(b, x.bfloat16())
+    back = torch.empty(9, 100, device="cuda")
+    K.cast(b, back)
+    assert torch.equal(back, b.float())
+
+
+def test_unsupported_sizes_are_refused_not_miscomputed():
+    from minfer_b200.kernels import api as K
+    q = torch.zeros(1, 1, 24, device="cuda")
+    with pytest.raises(K.KernelError, match="does not take"):
+        K.attention_packed(q, q, q, torch.zeros(1, dtype=torch.int32, device="cuda"),
+                           torch.zeros(1, dtype=torch.int32, device="cuda"),
+                           torch.tensor([0, 1], dtype=torch.int32, device="cuda"),
+                           torch.zeros(1, 24, device="cuda"), 1, 1, 24, 0, 1.0)
+    with pytest.raises(K.KernelError, match="CUDA device"):
+        K.rmsnorm(torch.zeros(1, 8), torch.zeros(8), 1e-6, torch.zeros(1, 8))
+    from minfer_b200.parts.attention import Attention
+    with pytest.raises(ValueError, match="multiples of 16"):
+        Attention(hidden_size=40, n_heads=2, n_kv_heads=1, head_dim=20, scale=1.0)

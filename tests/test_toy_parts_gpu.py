@@ -1,0 +1,191 @@
+"""A toy mixer with state of its own, a toy feed-forward and a toy position encoding, all
+defined here, are registered, built and stepped without a change to the framework's files.
+They are not models of anyone's: they only show that the interfaces carry other parts.
+
+The toy mixer keeps, per sequence, a decaying sum of its projected inputs:
+    s_t = decay * s_{t-1} + W_in x_t ;  y_t = W_out s_t
+Its state has a fixed size, whatever the sequence's length, and must give the same result
+for a whole prompt and token by token, and be zero again when a slot is reused."""
+import json
+import os
+import tempfile
+
+import pytest
+import torch
+
+from helpers import random_ids, rel_err
+
+pytestmark = pytest.mark.gpu
+
+VOCAB, WIDTH, INNER = 97, 48, 24
+
+
+def _register():
+    from minfer_b200 import registry
+    from minfer_b200.config.base import (ConfigReader, LayerSpec, ModelPlan, PartSpec,
+                                         default_schedule)
+    from minfer_b200.kernels import api as K
+    from minfer_b200.parts.base import FeedForward, Mixer, PositionEncoding, StateRequest
+    from minfer_b200.weights.spec import MATRIX, Init, TensorSpec
+
+    class DecayMixer(Mixer):
+        def __init__(self, width, inner, decay):
+            self.width, self.inner, self.decay = width, inner, decay
+
+        def tensor_specs(self, prefix):
+            return [TensorSpec(f"{prefix}mix.in.weight", (self.inner, self.width), MATRIX, Init(0, 0.2)),
+                    TensorSpec(f"{prefix}mix.out.weight", (self.width, self.inner), MATRIX, Init(0, 0.2))]
+
+        def load(self, prefix, weights):
+            self.w_in = weights[f"{prefix}mix.in.weight"]
+            self.w_out = weights[f"{prefix}mix.out.weight"]
+
+        def state_request(self):
+            return [StateRequest("sum", (self.inner,), torch.float32)]
+
+        def forward_add(self, x, ctx, binding, residual):
+            # the toy's own arithmetic is plain tensor code; a real part would be a kernel
+            state = binding.state["sum"]                       # [max_slots, inner]
+            u = torch.empty((x.shape[0], self.inner), dtype=torch.float32, device=x.device)
+            K.gemm_simt(x, self.w_in, None, u)
+            s_all = torch.empty_like(u)
+            cu = ctx.cu_seqlens.tolist()
+            for b, slot in enumerate(ctx.host_slots):
+                s = state[slot].clone()
+                for t in range(cu[b], cu[b + 1]):
+                    s = self.decay * s + u[t]
+                    s_all[t] = s
+                state[slot] = s
+            K.gemm_simt(s_all.to(x.dtype), self.w_out, None, residual, accumulate=True)
+
+    class SquareFeedForward(FeedForward):
+        """y = W2 (W1 x)^2: another feed-forward than the gated one."""
+        def __init__(self, width, inner):
+            self.width, self.inner = width, inner
+
+        def tensor_specs(self, prefix):
+            return [TensorSpec(f"{prefix}ff.w1", (self.inner, self.width), MATRIX, Init(0, 0.2)),
+                    TensorSpec(f"{prefix}ff.w2", (self.width, self.inner), MATRIX, Init(0, 0.2))]
+
+        def load(self, prefix, weights):
+            self.w1, self.w2 = weights[f"{prefix}ff.w1"], weights[f"{prefix}ff.w2"]
+
+        def forward_add(self, x, ctx, residual):
+            u = torch.empty((x.shape[0], self.inner), dtype=torch.float32, device=x.device)
+            K.gemm_simt(x, self.w1, None, u)
+            K.gemm_simt((u * u).to(x.dtype), self.w2, None, residual, accumulate=True)
+
+    class ShiftPosition(PositionEncoding):
+        """Adds 0.01 * position to every dimension of q and k: not a rotation, so it goes
+        through ``apply`` instead of the fused rotary kernel."""
+        def apply(self, qkv32, ctx, n_heads, n_kv_heads, head_dim):
+            n_rot = (n_heads + n_kv_heads) * head_dim
+            qkv32[:, :n_rot] += 0.01 * ctx.positions.to(torch.float32)[:, None]
+
+    class ToyConfig:
+        def __init__(self, d):
+            r = ConfigReader(d)
+            self.vocab, self.width, self.inner = r.integer("vocab"), r.integer("width"), r.integer("inner")
+            self.layers, self.decay = r.integer("layers"), r.number("decay")
+
+        def plan(self):
+            norm = PartSpec("rms_norm", {"size": self.width, "eps": 1e-5})
+            layers = []
+            for l in range(self.layers):
+                if l % 2 == 0:      # layers differ: the state mixer here, attention there
+                    mixer = PartSpec("toy_decay", dict(width=self.width, inner=self.inner, decay=self.decay))
+                else:
+                    mixer = PartSpec("attention", dict(
+                        hidden_size=self.width, n_heads=3, n_kv_heads=1, head_dim=16, scale=0.25,
+                        window=0, qkv_bias=False, position=PartSpec("toy_shift", {})))
+                ffn = (PartSpec("toy_square", dict(width=self.width, inner=self.inner)) if l % 2 == 0
+                       else PartSpec("gated_mlp", dict(hidden_size=self.width, intermediate_size=40)))
+                layers.append(LayerSpec(f"toy.{l}.", PartSpec("pre_norm", {}), mixer,
+                                        norm.with_params(name="n1"), ffn, norm.with_params(name="n2")))
+            return ModelPlan("ToyStateLM", self.vocab, self.width, "toy.embed", None,
+                             norm.with_params(name="final"), "toy.", layers,
+                             default_schedule(self.layers), 4096, ())
+
+    registry.register_part("mixer", "toy_decay", DecayMixer, replace=True)
+    registry.register_part("feed_forward", "toy_square", SquareFeedForward, replace=True)
+    registry.register_part("position", "toy_shift", ShiftPosition, replace=True)
+    registry.register_architecture("ToyStateLM", lambda d, where: ToyConfig(d), replace=True)
+
+
+CONFIG = {"architectures": ["ToyStateLM"], "vocab": VOCAB, "width": WIDTH, "inner": INNER,
+          "layers": 3, "decay": 0.9}
+
+
+def _reference(w, ids):
+    """The toy model in float64, whole sequence."""
+    def norm(x, wt):
+        return x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5) * wt
+    h = w["toy.embed"][torch.tensor(ids)]
+    T = len(ids)
+    for l in range(3):
+        p = f"toy.{l}."
+        x = norm(h, w[p + "n1.weight"])
+        if l % 2 == 0:
+            u = x @ w[p + "mix.in.weight"].t()
+            s, out = torch.zeros(INNER, dtype=torch.float64), []
+            for t in range(T):
+                s = 0.9 * s + u[t]
+                out.append(s)
+            h = h + torch.stack(out) @ w[p + "mix.out.weight"].t()
+        else:
+            a = p + "self_attn."
+            pos = torch.arange(T, dtype=torch.float64)[:, None]
+            q = (x @ w[a + "q_proj.weight"].t() + 0.01 * pos).reshape(T, 3, 16)
+            k = (x @ w[a + "k_proj.weight"].t() + 0.01 * pos).reshape(T, 1, 16)
+            v = (x @ w[a + "v_proj.weight"].t()).reshape(T, 1, 16)
+            o = torch.zeros(T, 3, 16, dtype=torch.float64)
+            for hh in range(3):
+                sc = (q[:, hh] @ k[:, 0].t()) * 0.25
+                sc = sc.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+                o[:, hh] = torch.softmax(sc, -1) @ v[:, 0]
+            h = h + o.reshape(T, 48) @ w[a + "o_proj.weight"].t()
+        x = norm(h, w[p + "n2.weight"])
+        if l % 2 == 0:
+            h = h + ((x @ w[p + "ff.w1"].t()) ** 2) @ w[p + "ff.w2"].t()
+        else:
+            g, u = x @ w[p + "mlp.gate_proj.weight"].t(), x @ w[p + "mlp.up_proj.weight"].t()
+            h = h + (torch.nn.functional.silu(g) * u) @ w[p + "mlp.down_proj.weight"].t()
+    return norm(h, w["toy.final.weight"]) @ w["toy.embed"].t()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_is_registered_built_and_stepped(dtype):
+    _register()
+    from minfer_b200.engine.step import Engine
+    from minfer_b200.model import Model, write_random_model
+    from minfer_b200.weights.safetensors_io import load_all
+    with tempfile.TemporaryDirectory() as folder:
+        json.dump(CONFIG, open(os.path.join(folder, "config.json"), "w"))
+        from minfer_b200.registry import read_config
+        cfg = read_config(CONFIG)
+        from minfer_b200.weights.random_init import write_model_folder
+        write_model_folder(folder, CONFIG, Model(cfg.plan(), "float32", cfg).tensor_specs(), 5, "bfloat16")
+        w = {k: v.double() for k, v in load_all(folder).items()}
+        model = Model.from_folder(folder, dtype, "cuda:0")
+    eng = Engine(model, 1024, max_seqs=3)
+    assert eng.cache.state.bytes_per_slot() == 2 * INNER * 4          # two state layers
+    assert len(eng.cache.groups) == 1                                 # one attention layer
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    prompts = [random_ids(n, VOCAB, n) for n in (30, 7, 70)]
+    want = [_reference(w, p) for p in prompts]
+    # batch of unequal lengths: heads in one step, then one token each, shorter ones ending
+    for round_ in range(2):                                           # second round reuses slots
+        slots = [eng.acquire() for _ in prompts]
+        heads = [len(p) - 5 for p in prompts]
+        out = eng.step(slots, [p[:h] for p, h in zip(prompts, heads)],
+                       [list(range(h)) for h in heads])
+        got = [[o] for o in torch.split(out, heads)]
+        for t in range(5):
+            o = eng.step(slots, [[p[h + t]] for p, h in zip(prompts, heads)])
+            for b in range(3):
+                got[b].append(o[b:b + 1])
+        for s in slots:
+            eng.release(s)
+        for b in range(3):
+            assert rel_err(torch.cat(got[b]), want[b]) < tol, (round_, b)
+    eng.check_status()
