@@ -1,0 +1,458 @@
+// bfloat16 projections on the 5th-generation tensor cores:
+//     Y[tokens][N] (+)= X[tokens][K] * W[N][K]^T (+ bias)
+// tcgen05.mma with the accumulator in tensor memory, both operands staged in shared
+// memory by TMA (128-byte swizzle), an mbarrier ring between the TMA thread, the MMA
+// thread and the epilogue warps.  The reference multiplies with scalar SIMT kernels that
+// re-read the weights for every token (src/cuda_kernels.cu:32-93, grid.y = tokens); here a
+// weight tile is read once per step and the same kernel serves whole prompts (256-token
+// tiles) and decoding (16..64-token tiles that stream the weights at memory speed).
+//
+// Roles of the operands are swapped against the usual convention: the WEIGHT tile
+// [128 rows of W][64 k] is the MMA's M side, the token tile [NT tokens][64 k] its N side,
+// so the accumulator holds D[n][token] with n along the 128 TMEM lanes.  A thread of the
+// epilogue owns one n and walks over the tokens; a warp's store for one token covers 32
+// consecutive n.
+//
+// Work that does not fill the GPU is split along K: each split writes float32 partial sums
+// that mf_splitk_reduce adds in split order (no atomics, so results are reproducible).
+//
+// Every wait on an mbarrier is bounded: when it runs out the kernel sets
+// MF_STATUS_WAIT_TIMEOUT in the status word, stops issuing work, lets its copies land,
+// frees its tensor memory and returns.
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+#define TILE_N 128            // rows of W per CTA (MMA M)
+#define TILE_K 64             // k per stage: 64 bf16 = 128 bytes = one swizzle row
+#define A_BYTES (TILE_N * TILE_K * 2)
+#define MAX_SPIN (1u << 24)
+
+#define EPI_STORE 0           // out = acc + bias          (float32 or bfloat16)
+#define EPI_ACCUM 1           // out += acc + bias         (float32)
+#define EPI_SWIGLU 2          // rows of W interleaved gate,up: out[j] = silu(g) * u (bfloat16)
+#define EPI_PARTIAL 3         // ws[split][token][n] = acc (float32)
+
+#define MF_ERR_NO_TENSORMAP 2003
+#define MF_ERR_TENSORMAP 2004
+
+struct GemmArgs {
+    void* out;                // EPI_STORE/ACCUM/SWIGLU
+    float* partial;           // EPI_PARTIAL
+    const float* bias;
+    unsigned* status;
+    long long ldo;            // elements between consecutive tokens of out
+    int M, N, K;              // tokens, rows of W, reduction length
+    int kblocks_per_split;
+    int epi;
+    int out_dtype;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded wait; false = gave up (abort flag set)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t it = 0; it < MAX_SPIN; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                       uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32"
+        " {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte
+// swizzle: 8-row groups 1024 bytes apart (SBO), version 1, layout type 2.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);          // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                                // leading byte offset (unused here)
+    d |= (uint64_t)(1024 >> 4) << 32;                      // stride byte offset
+    d |= (uint64_t)1 << 46;                                // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                                // SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = NT.
+__host__ __device__ constexpr uint32_t umma_idesc(int nt) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(nt >> 3) << 17) |
+           ((uint32_t)(TILE_N >> 4) << 24);
+}
+
+template <int NT> struct TmemCols { static constexpr int value = NT < 32 ? 32 : NT; };
+
+template <int NT, int STAGES>
+__global__ void __launch_bounds__(128, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               const GemmArgs a) {
+    constexpr int B_BYTES = NT * TILE_K * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int TMEM_COLS = TmemCols<NT>::value;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);   // full[S], empty[S], acc
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.x * NT;                  // first token of this tile
+    const int n0 = blockIdx.y * TILE_N;              // first row of W
+    const int split = blockIdx.z;
+    const int kblocks = (a.K + TILE_K - 1) / TILE_K;
+    const int kb0 = split * a.kblocks_per_split;
+    const int kb1 = min(kblocks, kb0 + a.kblocks_per_split);
+    const int n_iter = kb1 - kb0;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[STAGES + s]), 1);
+        }
+        mbar_init(smem_u32(&bars[2 * STAGES]), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer ------------------------------------------------------------
+        for (int i = 0; i < n_iter; ++i) {
+            const int s = i % STAGES;
+            const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+            if (!mbar_wait(smem_u32(&bars[STAGES + s]), ph ^ 1u, abort_flag)) break;
+            const uint32_t full = smem_u32(&bars[s]);
+            mbar_expect_tx(full, STAGE_BYTES);
+            const uint32_t dst = smem_u32(smem + s * STAGE_BYTES);
+            tma_load_2d(dst, &map_w, (kb0 + i) * TILE_K, n0, full);
+            tma_load_2d(dst + A_BYTES, &map_x, (kb0 + i) * TILE_K, m0, full);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer --------------------------------------------------------------
+        constexpr uint32_t idesc = umma_idesc(NT);
+        bool ok = true;
+        for (int i = 0; i < n_iter && ok; ++i) {
+            const int s = i % STAGES;
+            const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+            ok = mbar_wait(smem_u32(&bars[s]), ph, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+            const uint64_t da = umma_desc(sa), db = umma_desc(sa + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < TILE_K / 16; ++k) {
+                // 16 k = 32 bytes further along the swizzled row: +2 in 16-byte units
+                tc_mma(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                       (i > 0 || k > 0) ? 1u : 0u);
+            }
+            tc_commit(smem_u32(&bars[STAGES + s]));      // frees the stage when the MMAs are done
+        }
+        if (ok) tc_commit(smem_u32(&bars[2 * STAGES]));  // accumulator complete
+    }
+    __syncwarp();
+
+    // ---- epilogue: all four warps, warp w owns TMEM lanes 32w..32w+31 -------------------
+    const bool acc_ok = mbar_wait(smem_u32(&bars[2 * STAGES]), 0u, abort_flag);
+    tc_fence_after();
+    if (acc_ok) {
+        const int n = n0 + warp * 32 + lane;
+        const bool n_ok = n < a.N;
+        const float bias = (a.bias != nullptr && n_ok && a.epi != EPI_PARTIAL) ? a.bias[n] : 0.0f;
+#pragma unroll 1
+        for (int c0 = 0; c0 < NT; c0 += 16) {
+            if (m0 + c0 >= a.M) break;                   // uniform across the CTA
+            uint32_t r[16];
+            tc_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+            tc_wait_ld();
+            if (a.epi == EPI_SWIGLU) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int tok = m0 + c0 + j;
+                    const float v = __uint_as_float(r[j]);
+                    const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+                    if (tok < a.M && n_ok && (lane & 1) == 0) {
+                        const float g = v, u = other;
+                        ((__nv_bfloat16*)a.out)[(size_t)tok * a.ldo + (n >> 1)] =
+                            __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+                    }
+                }
+            } else if (a.epi == EPI_ACCUM) {
+                // all loads of the chunk first, so that they are in flight together
+                float old[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int tok = m0 + c0 + j;
+                    old[j] = (tok < a.M && n_ok) ? ((const float*)a.out)[(size_t)tok * a.ldo + n] : 0.0f;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int tok = m0 + c0 + j;
+                    if (tok < a.M && n_ok)
+                        ((float*)a.out)[(size_t)tok * a.ldo + n] = old[j] + __uint_as_float(r[j]) + bias;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int tok = m0 + c0 + j;
+                    const float v = __uint_as_float(r[j]) + bias;
+                    if (tok < a.M && n_ok) {
+                        if (a.epi == EPI_PARTIAL)
+                            a.partial[((size_t)split * a.M + tok) * a.N + n] = v;
+                        else if (a.out_dtype == MF_DTYPE_F32)
+                            ((float*)a.out)[(size_t)tok * a.ldo + n] = v;
+                        else
+                            ((__nv_bfloat16*)a.out)[(size_t)tok * a.ldo + n] = __float2bfloat16_rn(v);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (tid == 0) {
+            atomicOr(a.status, MF_STATUS_WAIT_TIMEOUT);
+            // give copies that are still in flight time to land before the memory is reused
+            for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// adds the K splits in order: out (+)= sum_s partial[s] + bias
+template <typename TO>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ bias,
+                                     TO* __restrict__ out, long long ldo, int M, int N, int splits,
+                                     int accumulate) {
+    const long long total = (long long)M * N;
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const int n = (int)(idx % N);
+        const long long m = idx / N;
+        float v = 0.0f;
+        for (int s = 0; s < splits; ++s) v += partial[(size_t)s * total + idx];
+        if (bias) v += bias[n];
+        TO* o = out + m * ldo + n;
+        if (accumulate) v += to_f32(*o);
+        *o = from_f32<TO>(v);
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// bf16 matrix [rows][K] with `ld` elements between rows; box = [box_rows][64]
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return MF_ERR_NO_TENSORMAP;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TILE_K, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : MF_ERR_TENSORMAP;
+}
+
+struct MapKey {
+    const void* ptr; int rows, K, box; long long ld;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && K == o.K && box == o.box && ld == o.ld;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ (size_t)k.rows * 1315423911u ^ (size_t)k.K * 2654435761u ^
+               (size_t)k.box * 97u ^ (size_t)k.ld * 31u;
+    }
+};
+
+// tensor maps of weights are made once and kept (weights do not move)
+static int weight_map(CUtensorMap* out, const void* ptr, int rows, int K, long long ld) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    MapKey key{ptr, rows, K, TILE_N, ld};
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+        CUtensorMap m;
+        if (int e = make_map(&m, ptr, rows, K, ld, TILE_N)) return e;
+        it = cache.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+
+template <int NT, int STAGES>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int splits,
+                  cudaStream_t stream) {
+    constexpr int smem = STAGES * (A_BYTES + NT * TILE_K * 2) + 1024 + 256;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((a.M + NT - 1) / NT, (a.N + TILE_N - 1) / TILE_N, splits);
+    gemm_tc_kernel<NT, STAGES><<<grid, 128, smem, stream>>>(mw, mx, a);
+    return MF_LAUNCH_CHECK();
+}
+
+// How a product of these sizes is cut: the token tile and the number of K splits.  A
+// function of the sizes only (never of the data), so results are reproducible.
+extern "C" int mf_gemm_tc_plan(int M, int N, int K, int epi, int* token_tile, int* splits) {
+    int nt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    const int tiles = ((M + nt - 1) / nt) * ((N + TILE_N - 1) / TILE_N);
+    const int kblocks = (K + TILE_K - 1) / TILE_K;
+    int s = 1;
+    if (epi != EPI_SWIGLU && tiles < 100 && kblocks >= 8) {
+        s = (148 + tiles - 1) / tiles;                 // aim at one wave of 148 CTAs
+        if (s > kblocks / 4) s = kblocks / 4;          // at least 4 k-blocks per split
+        if (s > 16) s = 16;
+        if (s < 1) s = 1;
+    }
+    *token_tile = nt;
+    *splits = s;
+    return 0;
+}
+
+extern "C" long long mf_gemm_tc_workspace_floats(int M, int N, int K, int epi) {
+    int nt, s;
+    mf_gemm_tc_plan(M, N, K, epi, &nt, &s);
+    return s > 1 ? (long long)s * M * N : 0;
+}
+
+// out[M][N] (+)= x[M][K] * w[N][K]^T (+ bias).  x, w bfloat16; for EPI_SWIGLU the rows of w
+// alternate gate,up and out is [M][N/2] bfloat16.  `workspace` must hold
+// mf_gemm_tc_workspace_floats floats when that is not zero.
+extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long ldw,
+                          const float* bias, void* out, long long ldo, int out_dtype, int M, int N,
+                          int K, int epi, float* workspace, unsigned* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return MF_ERR_UNSUPPORTED;
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MF_ERR_UNSUPPORTED;
+    if (epi == EPI_ACCUM && out_dtype != MF_DTYPE_F32) return MF_ERR_UNSUPPORTED;
+    if (epi == EPI_SWIGLU && (out_dtype != MF_DTYPE_BF16 || N % 2 != 0)) return MF_ERR_UNSUPPORTED;
+    if (epi < EPI_STORE || epi > EPI_SWIGLU) return MF_ERR_ARGUMENT;
+    int nt, splits;
+    mf_gemm_tc_plan(M, N, K, epi, &nt, &splits);
+    if (splits > 1 && workspace == nullptr) return MF_ERR_ARGUMENT;
+    CUtensorMap mw, mx;
+    if (int e = weight_map(&mw, w, N, K, ldw)) return e;
+    if (int e = make_map(&mx, x, M, K, ldx, nt)) return e;
+    const int kblocks = (K + TILE_K - 1) / TILE_K;
+    GemmArgs a;
+    a.out = out; a.partial = workspace; a.bias = bias; a.status = status; a.ldo = ldo;
+    a.M = M; a.N = N; a.K = K; a.out_dtype = out_dtype;
+    a.kblocks_per_split = (kblocks + splits - 1) / splits;
+    splits = (kblocks + a.kblocks_per_split - 1) / a.kblocks_per_split;   // no empty split
+    a.epi = splits > 1 ? EPI_PARTIAL : epi;
+    int e;
+    switch (nt) {
+        case 16: e = launch<16, 8>(mw, mx, a, splits, stream); break;
+        case 32: e = launch<32, 8>(mw, mx, a, splits, stream); break;
+        case 64: e = launch<64, 8>(mw, mx, a, splits, stream); break;
+        case 128: e = launch<128, 6>(mw, mx, a, splits, stream); break;
+        default: e = launch<256, 4>(mw, mx, a, splits, stream); break;
+    }
+    if (e || splits == 1) return e;
+    const long long total = (long long)M * N;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads
+                                                                       : 148 * 8);
+    if (out_dtype == MF_DTYPE_F32)
+        splitk_reduce_kernel<float><<<blocks, threads, 0, stream>>>(
+            workspace, bias, (float*)out, ldo, M, N, splits, epi == EPI_ACCUM);
+    else
+        splitk_reduce_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+            workspace, bias, (__nv_bfloat16*)out, ldo, M, N, splits, 0);
+    return MF_LAUNCH_CHECK();
+}

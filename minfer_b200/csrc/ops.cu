@@ -207,31 +207,33 @@ extern "C" int mf_rope_kvstore(const float* qkv, const int* positions, const int
 }
 
 // ------------------------------------------------------------------------------------
-// SwiGLU over the fused gate|up projection: out[t][j] = silu(gu[t][j]) * gu[t][nf + j],
-// silu(z) = z / (1 + exp(-z)), in float32.
+// SwiGLU over the fused gate|up projection, silu(z) = z / (1 + exp(-z)), in float32:
+//   layout 0 (gate rows then up rows):   out[t][j] = silu(gu[t][j])  * gu[t][nf + j]
+//   layout 1 (rows alternate gate, up):  out[t][j] = silu(gu[t][2j]) * gu[t][2j + 1]
 // ------------------------------------------------------------------------------------
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int nf,
-                              long long total) {
+                              long long total, int interleaved) {
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long t = idx / nf;
         const int j = (int)(idx - t * nf);
-        const float g = to_f32(gu[t * 2 * nf + j]);
-        const float u = to_f32(gu[t * 2 * nf + nf + j]);
+        const float g = to_f32(gu[t * 2 * nf + (interleaved ? 2 * j : j)]);
+        const float u = to_f32(gu[t * 2 * nf + (interleaved ? 2 * j + 1 : nf + j)]);
         out[idx] = from_f32<TO>(g / (1.0f + expf(-g)) * u);
     }
 }
 
 extern "C" int mf_swiglu(const void* gu, int in_dtype, void* out, int out_dtype, int n_rows, int nf,
-                         cudaStream_t stream) {
+                         int interleaved, cudaStream_t stream) {
     const long long total = (long long)n_rows * nf;
     if (total <= 0) return 0;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16
                                  ? (total + threads - 1) / threads : 148 * 16);
 #define MF_SWIGLU(TI, TO) \
-    swiglu_kernel<TI, TO><<<blocks, threads, 0, stream>>>((const TI*)gu, (TO*)out, nf, total)
+    swiglu_kernel<TI, TO><<<blocks, threads, 0, stream>>>((const TI*)gu, (TO*)out, nf, total, \
+                                                          interleaved)
     if (in_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_F32) MF_SWIGLU(float, float);
     else if (in_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_BF16) MF_SWIGLU(float, __nv_bfloat16);
     else if (in_dtype == MF_DTYPE_BF16 && out_dtype == MF_DTYPE_BF16)

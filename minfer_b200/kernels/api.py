@@ -87,7 +87,7 @@ def _sig_ops(lib: ctypes.CDLL) -> None:
     lib.mf_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                                c_void_p]
     lib.mf_rope_kvstore.argtypes = [c_void_p] * 11 + [c_int] * 9 + [c_void_p, c_void_p]
-    lib.mf_swiglu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p]
+    lib.mf_swiglu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     lib.mf_gather_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.mf_cast.argtypes = [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p]
     lib.mf_advance_positions.argtypes = [c_void_p, c_void_p, c_int, c_void_p]
@@ -112,7 +112,16 @@ def _sig_sampling(lib: ctypes.CDLL) -> None:
     lib.mf_sampler_state_ints.argtypes = []
 
 
-_SIGNATURES = {"ops": _sig_ops, "gemm_simt": _sig_gemm_simt, "attention": _sig_attention,
+def _sig_gemm_tc(lib: ctypes.CDLL) -> None:
+    lib.mf_gemm_tc.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
+                               c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                               c_void_p]
+    lib.mf_gemm_tc_workspace_floats.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mf_gemm_tc_workspace_floats.restype = c_longlong
+    lib.mf_gemm_tc_plan.argtypes = [c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+
+
+_SIGNATURES = {"gemm_tc": _sig_gemm_tc, "ops": _sig_ops, "gemm_simt": _sig_gemm_simt, "attention": _sig_attention,
                "sampling": _sig_sampling}
 
 
@@ -166,12 +175,15 @@ def rope_kvstore(qkv: torch.Tensor, positions: torch.Tensor, token_row: torch.Te
         _stream()), "rope_kvstore")
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+    """out = silu(gate) * up; ``interleaved``: the columns of ``gate_up`` alternate gate, up
+    instead of all gates first."""
     n, nf = out.shape
     if gate_up.shape != (n, 2 * nf):
         raise KernelError("swiglu: shapes do not fit")
     _check(_lib("ops").mf_swiglu(_ptr(gate_up, "gate_up"), dtype_code(gate_up.dtype),
-                                 _ptr(out, "out"), dtype_code(out.dtype), n, nf, _stream()),
+                                 _ptr(out, "out"), dtype_code(out.dtype), n, nf,
+                                 1 if interleaved else 0, _stream()),
            "swiglu")
 
 
@@ -217,6 +229,52 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
         a.data_ptr(), dtype_code(a.dtype), w.data_ptr(), dtype_code(w.dtype), _f32(bias, "bias"),
         out.data_ptr(), dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(0), out.stride(0),
         1 if accumulate else 0, _stream()), "gemm_simt")
+
+
+# ---------------------------------------------------------------------------------------
+# matrix product on the tensor cores (bfloat16 x bfloat16, float32 accumulation)
+# ---------------------------------------------------------------------------------------
+EPI_STORE, EPI_ACCUM, EPI_SWIGLU = 0, 1, 2
+
+
+def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """The tensor-core kernel takes bfloat16 operands whose rows start on 16-byte
+    boundaries (TMA); anything else goes to the FP32-pipe kernel."""
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2
+            and w.dim() == 2 and x.shape[1] % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0)
+
+
+def gemm_tc_plan(m: int, n: int, k: int, epi: int = EPI_STORE) -> tuple[int, int]:
+    """(token tile, K splits) the kernel uses for these sizes."""
+    nt, sp = ctypes.c_int(0), ctypes.c_int(0)
+    _lib("gemm_tc").mf_gemm_tc_plan(m, n, k, epi, ctypes.addressof(nt), ctypes.addressof(sp))
+    return nt.value, sp.value
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+            epi: int, status: torch.Tensor) -> None:
+    """out (+)= x @ w^T + bias on tcgen05.  EPI_SWIGLU: w's rows alternate gate, up and out is
+    [M, N/2] bfloat16 = silu(gate) * up."""
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise KernelError(f"gemm: shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    want_cols = n // 2 if epi == EPI_SWIGLU else n
+    if out.shape != (m, want_cols) or out.stride(1) != 1:
+        raise KernelError(f"gemm: out has shape {tuple(out.shape)}, expected {(m, want_cols)}")
+    if not gemm_tc_supported(x, w):
+        raise KernelError("gemm_tc: operands must be bfloat16 with 16-byte aligned rows")
+    if bias is not None and bias.numel() != n:
+        raise KernelError("gemm: bias has the wrong length")
+    lib = _lib("gemm_tc")
+    need = int(lib.mf_gemm_tc_workspace_floats(m, n, k, epi))
+    ws = torch.empty(need, dtype=torch.float32, device=x.device) if need else None
+    _check(lib.mf_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _f32(bias, "bias"),
+                          out.data_ptr(), out.stride(0), dtype_code(out.dtype), m, n, k, epi,
+                          _ptr(ws, "workspace"), _i32(status, "status"), _stream()),
+           "gemm_tc", 2 if need else 1)
 
 
 # ---------------------------------------------------------------------------------------

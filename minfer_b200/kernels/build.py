@@ -32,6 +32,7 @@ LIBRARIES = {
     "gemm_simt": ("gemm_simt.cu", []),
     "attention": ("attention.cu", []),
     "sampling": ("sampling.cu", []),
+    "gemm_tc": ("gemm_tc.cu", []),
 }
 
 

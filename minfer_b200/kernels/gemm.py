@@ -1,13 +1,33 @@
-"""Chooses the kernel of a bfloat16 x bfloat16 projection."""
+"""Chooses the kernel of a bfloat16 x bfloat16 projection: the tcgen05 kernel whenever its
+operands qualify (rows on 16-byte boundaries for TMA), else the FP32-pipe kernel."""
 from __future__ import annotations
 
-from typing import Any, Optional
+import os
+from typing import Optional
 
 import torch
 
 from . import api as K
 
+_status: dict = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """A device word the tensor-core kernels set bits in when a bounded wait runs out."""
+    key = str(device)
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def use_tensor_cores() -> bool:
+    return os.environ.get("MINFER_B200_NO_TCGEN05", "0") != "1"
+
 
 def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
-              out: torch.Tensor, accumulate: bool, owner: Any = None) -> None:
-    K.gemm_simt(x, weight, bias, out, accumulate)
+              out: torch.Tensor, accumulate: bool) -> None:
+    if use_tensor_cores() and K.gemm_tc_supported(x, weight) and out.stride(1) == 1:
+        K.gemm_tc(x, weight, bias, out, K.EPI_ACCUM if accumulate else K.EPI_STORE,
+                  status_word(x.device))
+    else:
+        K.gemm_simt(x, weight, bias, out, accumulate)

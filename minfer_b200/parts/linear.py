@@ -37,7 +37,7 @@ class Linear:
             return out
         if x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
             from ..kernels import gemm
-            gemm.gemm_bf16(x, self.weight, self.bias, out, accumulate, self)
+            gemm.gemm_bf16(x, self.weight, self.bias, out, accumulate)
         else:
             K.gemm_simt(x, self.weight, self.bias, out, accumulate)
         return out

@@ -27,6 +27,7 @@ class GatedMlp(FeedForward):
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
         self.init_std = float(init_std)
+        self.interleaved = False
         self.gate_up: Optional[Linear] = None
         self.down: Optional[Linear] = None
 
@@ -45,12 +46,25 @@ class GatedMlp(FeedForward):
         g, u = weights[f"{p}gate_proj.weight"], weights[f"{p}up_proj.weight"]
         if g.dtype != u.dtype:
             g, u = g.to(torch.float32), u.to(torch.float32)
-        self.gate_up = Linear(torch.cat([g, u], dim=0).contiguous())
+        # bfloat16: rows alternate gate, up so that the tensor-core kernel's epilogue finds a
+        # pair in neighbouring lanes and writes silu(gate) * up directly; float32: gates first
+        self.interleaved = g.dtype == torch.bfloat16
+        if self.interleaved:
+            packed = torch.stack([g, u], dim=1).reshape(2 * self.intermediate_size, self.hidden_size)
+        else:
+            packed = torch.cat([g, u], dim=0)
+        self.gate_up = Linear(packed.contiguous())
         self.down = Linear(weights[f"{p}down_proj.weight"])
 
     def forward_add(self, x: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
-        gu = self.gate_up.forward(x, ctx.act_dtype)
+        from ..kernels import gemm
         act = torch.empty((x.shape[0], self.intermediate_size), dtype=ctx.act_dtype,
                           device=x.device)
-        K.swiglu(gu, act)
+        w = self.gate_up.weight
+        if (self.interleaved and x.shape[0] > 0 and gemm.use_tensor_cores()
+                and K.gemm_tc_supported(x, w)):
+            K.gemm_tc(x, w, None, act, K.EPI_SWIGLU, gemm.status_word(x.device))
+        else:
+            gu = self.gate_up.forward(x, ctx.act_dtype)
+            K.swiglu(gu, act, self.interleaved)
         self.down.forward(act, torch.float32, out=residual, accumulate=True)

@@ -300,6 +300,10 @@ def test_swiglu_gather_cast():
     K.swiglu(gu.bfloat16(), out)
     close(out, torch.nn.functional.silu(gu.bfloat16()[:, :328].double()) * gu.bfloat16()[:, 328:].double(),
           torch.bfloat16)
+    il = torch.stack([gu[:, :328], gu[:, 328:]], dim=2).reshape(5, 656).contiguous()
+    out = torch.empty(5, 328, device="cuda")
+    K.swiglu(il, out, interleaved=True)
+    close(out, want, torch.float32)
     x = torch.randn(9, 100).cuda()
     rows = torch.tensor([8, 8, 0, 3], dtype=torch.int32, device="cuda")
     picked = torch.empty(4, 100, device="cuda")
@@ -326,3 +330,52 @@ def test_unsupported_sizes_are_refused_not_miscomputed():
     from minfer_b200.parts.attention import Attention
     with pytest.raises(ValueError, match="multiples of 16"):
         Attention(hidden_size=40, n_heads=2, n_kv_heads=1, head_dim=20, scale=1.0)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 256, 128), (5, 130, 72), (16, 389, 328),
+                                   (33, 640, 200), (64, 512, 1024), (100, 384, 512),
+                                   (300, 640, 3584), (8, 3584, 3584), (700, 1000, 264)])
+def test_gemm_tensor_core_against_float64(m, n, k):
+    """The tcgen05 kernel at every token tile (16..256), with and without K splits, ragged
+    edges in all three dimensions, every epilogue."""
+    from minfer_b200.kernels import api as K
+    g = torch.Generator().manual_seed(m + n + k)
+    x = (torch.randn(m, k, generator=g) * 0.5).bfloat16().cuda()
+    w = (torch.randn(n, k, generator=g) * 0.5).bfloat16().cuda()
+    bias = torch.randn(n, generator=g).cuda()
+    st = status()
+    want = x.double() @ w.double().t()
+    out = torch.zeros(m, n, device="cuda")
+    K.gemm_tc(x, w, bias, out, K.EPI_STORE, st)
+    close(out, want + bias.double(), torch.float32)
+    outb = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
+    K.gemm_tc(x, w, None, outb, K.EPI_STORE, st)
+    close(outb, want, torch.bfloat16)
+    acc = torch.randn(m, n, generator=g).cuda()
+    before = acc.clone()
+    K.gemm_tc(x, w, None, acc, K.EPI_ACCUM, st)
+    close(acc, before.double() + want, torch.float32)
+    if n % 2 == 0:
+        act = torch.zeros(m, n // 2, dtype=torch.bfloat16, device="cuda")
+        K.gemm_tc(x, w, None, act, K.EPI_SWIGLU, st)
+        close(act, torch.nn.functional.silu(want[:, 0::2]) * want[:, 1::2], torch.bfloat16)
+    assert int(st) == 0
+    # run twice: the same bits (splits are added in a fixed order)
+    again = torch.zeros(m, n, device="cuda")
+    K.gemm_tc(x, w, bias, again, K.EPI_STORE, st)
+    assert torch.equal(again, out)
+
+
+def test_gemm_tensor_core_refuses_unaligned_rows():
+    from minfer_b200.kernels import api as K
+    x = torch.zeros(4, 20, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(8, 20, dtype=torch.bfloat16, device="cuda")
+    assert not K.gemm_tc_supported(x, w)
+    with pytest.raises(K.KernelError, match="aligned"):
+        K.gemm_tc(x, w, None, torch.zeros(4, 8, device="cuda"), K.EPI_STORE, status())
+    # the projection falls back to the FP32-pipe kernel for such widths
+    from minfer_b200.parts.linear import Linear
+    xr = torch.randn(4, 20).bfloat16().cuda()
+    wr = torch.randn(8, 20).bfloat16().cuda()
+    got = Linear(wr).forward(xr, torch.float32)
+    close(got, xr.double() @ wr.double().t(), torch.float32)
