@@ -130,8 +130,10 @@ class CacheGroup:
         self.pool = PagePool(n_pages)
         self.pages: List[List[int]] = [[] for _ in range(n_slots)]
         shape = (len(self.entries), n_pages, key.n_kv_heads, PAGE, key.head_dim)
-        self.k = torch.empty(shape, dtype=dtype, device=device)
-        self.v = torch.empty(shape, dtype=dtype, device=device)
+        # zeros, once: a page's unwritten positions are masked by length but still multiplied
+        # by a zero weight in the tensor-core kernels, so they must never hold NaN or Inf
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
         self._index = {e: i for i, e in enumerate(self.entries)}
 
     def pages_needed(self, length: int) -> int:

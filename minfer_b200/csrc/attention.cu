@@ -188,6 +188,208 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial, T* _
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// Decoding over the paged cache on tensor cores (bfloat16, head size 64 or 128, up to 16
+// query heads per key/value head).
+//
+// One CTA owns (key chunk of 256 positions, key/value head, query row); its four warps each
+// take one page of 64 keys.  The group's query heads are the 16 rows of an m16n8k16 MMA, so
+// a key or value element is read once for the whole group (the reference's kernel re-reads
+// the cache for every query head: src/cuda_kernels.cu:673-790).  Keys go from global memory
+// straight into MMA fragments (16-byte loads; k is permuted the same way in both operands,
+// which a dot product does not see); values are staged in shared memory by cp.async with an
+// XOR swizzle and read transposed by ldmatrix.  Scores, maxima and sums are float32; the
+// probabilities are rounded to bfloat16 for the second product.  The warps' results are
+// merged in shared memory in warp order and written as one partial per chunk, which
+// attention_combine_kernel merges in chunk order.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16_16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(128) attention_decode_mma_kernel(AttnArgs a) {
+    constexpr int CPR = HD / 8;                       // 16-byte chunks per row
+    extern __shared__ __align__(128) uint8_t dec_smem[];
+    __nv_bfloat16* v_s = (__nv_bfloat16*)dec_smem;                      // [4][64][HD], swizzled
+    float* o_s = (float*)(dec_smem + 4 * 64 * HD * 2);                   // [4][16][HD]
+    float* ml_s = o_s + 4 * 16 * HD;                                     // [4][16][2]
+
+    const int chunk_id = blockIdx.x, hk = blockIdx.y, row = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int G = a.n_heads / a.n_kv;
+    const int b = a.row_seq[row];
+    const int pos = a.row_pos[row];
+    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int hi = pos + 1;
+    const int c_lo = chunk_id * 256;
+    const size_t part_stride = (size_t)(HD + 2);
+    float* part0 = a.partial + (((size_t)row * a.n_heads + (size_t)hk * G) * a.n_chunks + chunk_id) * part_stride;
+    if (max(lo, c_lo) >= min(hi, c_lo + 256)) {       // nothing of this chunk is visible
+        if (tid < G) {
+            float* p = part0 + (size_t)tid * a.n_chunks * part_stride;
+            p[0] = -INFINITY;
+            p[1] = 0.0f;
+        }
+        return;
+    }
+
+    const int j0 = c_lo + warp * 64;                  // first position of this warp's page
+    const int w_lo = max(lo, j0), w_hi = min(hi, j0 + 64);
+    const bool active = w_lo < w_hi;
+    float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+
+    if (active) {
+        const int p_eff = a.ring > 0 ? j0 % a.ring : j0;
+        const int page = a.page_table[(size_t)b * a.table_stride + (p_eff >> 6)];
+        const __nv_bfloat16* kp = (const __nv_bfloat16*)a.k + ((size_t)page * a.n_kv + hk) * MF_PAGE * HD;
+        const __nv_bfloat16* vp = (const __nv_bfloat16*)a.v + ((size_t)page * a.n_kv + hk) * MF_PAGE * HD;
+        __nv_bfloat16* vw = v_s + (size_t)warp * 64 * HD;
+        // values -> shared memory (asynchronously; the scores are computed meanwhile)
+        for (int i = lane; i < 64 * CPR; i += 32) {
+            const int r = i / CPR, c = i % CPR;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(vw + (r * CPR + (c ^ (r & 7))) * 8);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(vp + (size_t)i * 8) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+
+        // query fragments: rows g and g+8 of the group (zero beyond the group's heads)
+        uint32_t qa[HD / 16][4];
+        const __nv_bfloat16* qrow = (const __nv_bfloat16*)a.q + ((size_t)row * a.n_heads + (size_t)hk * G) * HD;
+#pragma unroll
+        for (int s = 0; s < HD / 32; ++s) {
+            uint4 q0 = make_uint4(0, 0, 0, 0), q1 = make_uint4(0, 0, 0, 0);
+            if (g < G) q0 = *reinterpret_cast<const uint4*>(qrow + (size_t)g * HD + 32 * s + 8 * t);
+            if (g + 8 < G) q1 = *reinterpret_cast<const uint4*>(qrow + (size_t)(g + 8) * HD + 32 * s + 8 * t);
+            qa[2 * s][0] = q0.x; qa[2 * s][1] = q1.x; qa[2 * s][2] = q0.y; qa[2 * s][3] = q1.y;
+            qa[2 * s + 1][0] = q0.z; qa[2 * s + 1][1] = q1.z; qa[2 * s + 1][2] = q0.w; qa[2 * s + 1][3] = q1.w;
+        }
+
+        // scores S[16 heads][64 keys]
+        float sacc[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.0f;
+            const __nv_bfloat16* kr = kp + (size_t)(nt * 8 + g) * HD + 8 * t;
+#pragma unroll
+            for (int s = 0; s < HD / 32; ++s) {
+                const uint4 kv = *reinterpret_cast<const uint4*>(kr + 32 * s);
+                mma_bf16_16816(sacc[nt], qa[2 * s], kv.x, kv.y);
+                mma_bf16_16816(sacc[nt], qa[2 * s + 1], kv.z, kv.w);
+            }
+        }
+        // scale, mask by position, row maxima
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = j0 + nt * 8 + 2 * t + (e & 1);
+                const float sv = (key >= w_lo && key < w_hi) ? sacc[nt][e] * a.scale : -INFINITY;
+                sacc[nt][e] = sv;
+                m_r[e >> 1] = fmaxf(m_r[e >> 1], sv);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            m_r[r] = fmaxf(m_r[r], __shfl_xor_sync(0xffffffffu, m_r[r], 1));
+            m_r[r] = fmaxf(m_r[r], __shfl_xor_sync(0xffffffffu, m_r[r], 2));
+        }
+        uint32_t pa[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            float p[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                p[e] = expf(sacc[nt][e] - m_r[e >> 1]);
+                l_r[e >> 1] += p[e];
+            }
+            pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
+            pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 1);
+            l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 2);
+        }
+
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncwarp();
+        // O[16 heads][HD] = P[16][64] V[64][HD]
+        const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(vw);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+            for (int np = 0; np < HD / 16; ++np) {
+                const int dchunk = 2 * np + (lane >> 4);
+                const uint32_t addr = vbase + (uint32_t)((key * CPR + (dchunk ^ (key & 7))) * 16);
+                uint32_t r0, r1, r2, r3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+                mma_bf16_16816(o[2 * np], pa[ks], r0, r1);
+                mma_bf16_16816(o[2 * np + 1], pa[ks], r2, r3);
+            }
+        }
+    }
+    // hand the warp's result over: rows g and g+8
+    if (t == 0) {
+        ml_s[(warp * 16 + g) * 2 + 0] = m_r[0]; ml_s[(warp * 16 + g) * 2 + 1] = l_r[0];
+        ml_s[(warp * 16 + g + 8) * 2 + 0] = m_r[1]; ml_s[(warp * 16 + g + 8) * 2 + 1] = l_r[1];
+    }
+    float* ow = o_s + (size_t)warp * 16 * HD;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+        *reinterpret_cast<float2*>(ow + (size_t)g * HD + nt * 8 + 2 * t) = make_float2(o[nt][0], o[nt][1]);
+        *reinterpret_cast<float2*>(ow + (size_t)(g + 8) * HD + nt * 8 + 2 * t) = make_float2(o[nt][2], o[nt][3]);
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += 128) {
+        const int r = idx / HD, d = idx - r * HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, ml_s[(w * 16 + r) * 2]);
+        float l = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = ml_s[(w * 16 + r) * 2];
+            if (mw > -INFINITY) {
+                const float f = expf(mw - m);
+                l += ml_s[(w * 16 + r) * 2 + 1] * f;
+                acc += o_s[((size_t)w * 16 + r) * HD + d] * f;
+            }
+        }
+        float* p = part0 + (size_t)r * a.n_chunks * part_stride;
+        p[2 + d] = acc;
+        if (d == 0) { p[0] = m; p[1] = l; }
+    }
+}
+
+template <int HD>
+static int launch_decode_mma(const AttnArgs& a, cudaStream_t stream) {
+    constexpr int smem = 4 * 64 * HD * 2 + 4 * 16 * HD * 4 + 4 * 16 * 2 * 4;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(a.n_chunks, a.n_kv, a.rows);
+    attention_decode_mma_kernel<HD><<<grid, 128, smem, stream>>>(a);
+    return MF_LAUNCH_CHECK();
+}
+
 static int check_sizes(int n_heads, int n_kv, int hd) {
     if (hd <= 0 || hd % 16 != 0 || hd > ATT_MAX_HD) return MF_ERR_UNSUPPORTED;
     if (n_kv <= 0 || n_heads <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
@@ -223,7 +425,7 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
                                   const int* row_seq, const int* row_pos, const int* page_table,
                                   int table_stride, int ring, void* out, float* partial, int rows,
                                   int n_heads, int n_kv, int hd, int window, int chunk, int n_chunks,
-                                  float scale, int dtype, cudaStream_t stream) {
+                                  float scale, int dtype, int force_generic, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (int e = check_sizes(n_heads, n_kv, hd)) return e;
     if (n_chunks < 1 || (n_chunks > 1 && (partial == nullptr || chunk <= 0))) return MF_ERR_ARGUMENT;
@@ -234,6 +436,18 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
     a.out = out; a.partial = n_chunks > 1 ? partial : nullptr;
     a.rows = rows; a.n_heads = n_heads; a.n_kv = n_kv; a.hd = hd; a.window = window;
     a.chunk = chunk; a.n_chunks = n_chunks; a.scale = scale;
+    // tensor-core path: bfloat16, head size 64 or 128, groups of up to 16 heads, 256-key chunks
+    const bool fast = dtype == MF_DTYPE_BF16 && (hd == 64 || hd == 128) && n_heads / n_kv <= 16 &&
+                      chunk == 256 && partial != nullptr && rows <= 65535 && n_kv <= 65535 &&
+                      !force_generic;
+    if (fast) {
+        a.partial = partial;
+        int e = hd == 64 ? launch_decode_mma<64>(a, stream) : launch_decode_mma<128>(a, stream);
+        if (e) return e;
+        attention_combine_kernel<__nv_bfloat16><<<rows * n_heads, hd, 0, stream>>>(
+            partial, (__nv_bfloat16*)out, n_chunks, hd);
+        return MF_LAUNCH_CHECK();
+    }
     const long long items = (long long)rows * n_heads * n_chunks;
     const unsigned blocks = (unsigned)((items + ATT_WARPS - 1) / ATT_WARPS);
     if (dtype == MF_DTYPE_F32)

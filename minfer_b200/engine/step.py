@@ -82,7 +82,19 @@ class Engine:
             for req in model.blocks[call.layer].mixer.state_request():
                 tensors[req.name] = self.cache.state.add(f"call{i}.{req.name}", req.shape, req.dtype)
             self._call_state.append(tensors)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        from ..kernels import gemm
+        self.status = gemm.status_word(self.device)       # one word for every kernel's error bits
+        self._graphs: Dict[tuple, dict] = {}
+        self._seen_shapes: set = set()
+        # a part that reads device memory on the host, or changes state outside its kernels,
+        # cannot be captured: every part has to declare itself capturable
+        parts = [model.final_norm]
+        for block in model.blocks:
+            parts += [block, block.mixer, getattr(block, "feed_forward", None),
+                      getattr(block, "mixer_norm", None), getattr(block, "feed_forward_norm", None)]
+        if not all(getattr(p, "capturable", False) for p in parts if p is not None):
+            self.cuda_graphs = False
+        self._graph_pool = None
         self.steps_run = 0
         self.h2d_bytes = 0          # bytes of step inputs copied to the device so far
         self.d2h_bytes = 0          # bytes of results read back so far
@@ -139,8 +151,15 @@ class Engine:
         for b in range(n_rows):
             self.cache.reserve(slots[b], starts[b] + counts[b])
 
-        ctx, want_rows = self._context(slots, tokens, counts, starts, want, from_start, single)
-        logits = self._run(ctx, want_rows)
+        logits = None
+        if (self.cuda_graphs and single and not from_start
+                and all(list(w) == [0] for w in want)):
+            logits = self._graph_step(slots, tokens, starts, None)
+            if logits is not None:
+                logits = logits.clone()
+        if logits is None:
+            ctx, want_rows = self._context(slots, tokens, counts, starts, want, from_start, single)
+            logits = self._run(ctx, want_rows)
         for b in range(n_rows):
             self.cache.set_length(slots[b], starts[b] + counts[b])
         self.steps_run += 1
@@ -149,7 +168,9 @@ class Engine:
     def decode_on_device(self, slots: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
         """One token per sequence, the token ids already on the device (int32 [rows], for
         instance the sampler's output): nothing is read back, so steps can follow one
-        another without the host waiting.  Out-of-range ids set the status word."""
+        another without the host waiting.  Out-of-range ids set the status word.  With CUDA
+        graphs the returned logits live in the graph's own memory and are overwritten by the
+        next step of the same shape."""
         n_rows = len(slots)
         if tokens.dtype != torch.int32 or tokens.numel() != n_rows or not tokens.is_cuda:
             raise StepError("decode_on_device takes int32 token ids on the device, one per row")
@@ -163,10 +184,13 @@ class Engine:
                 raise StepError(f"sequence in slot {slots[b]} is at the model's last position")
             self.cache.reserve(slots[b], starts[b] + 1)
         counts = [1] * n_rows
-        ctx, want_rows = self._context(slots, [[0]] * n_rows, counts, starts, [[0]] * n_rows,
-                                       False, True)
-        ctx.token_ids = tokens
-        logits = self._run(ctx, want_rows)
+        logits = self._graph_step(slots, [[0]] * n_rows, starts, tokens) if self.cuda_graphs \
+            else None
+        if logits is None:
+            ctx, want_rows = self._context(slots, [[0]] * n_rows, counts, starts, [[0]] * n_rows,
+                                           False, True)
+            ctx.token_ids = tokens
+            logits = self._run(ctx, want_rows)
         for b in range(n_rows):
             self.cache.set_length(slots[b], starts[b] + 1)
         self.steps_run += 1
@@ -179,9 +203,11 @@ class Engine:
         self.cache.set_length(slot, length)
 
     # ---- metadata -----------------------------------------------------------------------
-    def _context(self, slots, tokens, counts, starts, want, from_start, single):
+    def _host_fields(self, slots, tokens, counts, starts, want, widths):
+        """The step's integers, field by field: tokens, positions, batch row of each token,
+        cu_seqlens, lengths after the step, slots, wanted rows, then one page table per cache
+        group (``widths[g]`` entries a row, -1 where a sequence has no page)."""
         n_rows = len(slots)
-        n_tokens = sum(counts)
         flat_tokens, positions, token_row, cu, want_rows = [], [], [], [0], []
         for b in range(n_rows):
             base = cu[-1]
@@ -192,31 +218,108 @@ class Engine:
             want_rows.extend(base + int(w) for w in want[b])
         seq_end = [starts[b] + counts[b] for b in range(n_rows)]
         fields = [flat_tokens, positions, token_row, cu, seq_end, list(slots), want_rows]
-        widths = []
-        for g in self.cache.groups:
-            width = max(1, g.max_pages_of(slots))
-            widths.append(width)
+        for g, width in zip(self.cache.groups, widths):
             rows = g.table_rows(slots, width)
             fields.append([p for row in rows for p in row])
-        sizes = [len(f) for f in fields]
-        host = torch.tensor([x for f in fields for x in f], dtype=torch.int32).pin_memory()
-        dev = host.to(self.device, non_blocking=True)
-        self.h2d_bytes += host.numel() * 4
+        return fields
+
+    def _views(self, dev: torch.Tensor, sizes) -> List[torch.Tensor]:
         views, at = [], 0
         for n in sizes:
             views.append(dev[at:at + n])
             at += n
-        tables = {}
-        for gi, g in enumerate(self.cache.groups):
-            tables[id(g)] = (views[7 + gi], widths[gi])
+        return views
+
+    def _make_ctx(self, views, widths, n_tokens, slots, from_start, single, max_row_tokens,
+                  max_end) -> StepContext:
+        tables = {id(g): (views[7 + gi], widths[gi]) for gi, g in enumerate(self.cache.groups)}
         ctx = StepContext(
-            device=self.device, act_dtype=self.dtype, n_tokens=n_tokens, n_rows=n_rows,
+            device=self.device, act_dtype=self.dtype, n_tokens=n_tokens, n_rows=len(slots),
             token_ids=views[0], positions=views[1], token_row=views[2], cu_seqlens=views[3],
             seq_end=views[4], slots=views[5], from_start=from_start, single_token=single,
-            max_row_tokens=max(counts), max_end=max(seq_end), status=self.status,
+            max_row_tokens=max_row_tokens, max_end=max_end, status=self.status,
             host_slots=list(slots))
         ctx.extras["page_tables"] = tables
-        return ctx, (views[6] if want_rows else None)
+        return ctx
+
+    def _context(self, slots, tokens, counts, starts, want, from_start, single):
+        widths = [max(1, g.max_pages_of(slots)) for g in self.cache.groups]
+        fields = self._host_fields(slots, tokens, counts, starts, want, widths)
+        sizes = [len(f) for f in fields]
+        host = torch.tensor([x for f in fields for x in f], dtype=torch.int32).pin_memory()
+        dev = host.to(self.device, non_blocking=True)
+        self.h2d_bytes += host.numel() * 4
+        views = self._views(dev, sizes)
+        ctx = self._make_ctx(views, widths, sum(counts), slots, from_start, single, max(counts),
+                             max(starts[b] + counts[b] for b in range(len(slots))))
+        return ctx, (views[6] if sizes[6] else None)
+
+    # ---- decode steps replayed as CUDA graphs -------------------------------------------------
+    def _graph_step(self, slots, tokens, starts, device_tokens: Optional[torch.Tensor]):
+        """A one-token-per-sequence step through a captured graph.  The graph is keyed by the
+        number of rows and by a power-of-two bound on the sequences' lengths (which fixes the
+        page tables' width and the number of key chunks); positions, slots, tokens and page
+        tables are data in a buffer the graph reads, as positions are in the reference
+        (src/graph/params.rs:10-60: the reuse identity has no n_past)."""
+        n_rows = len(slots)
+        max_end = max(starts) + 1
+        cap = 256
+        while cap < max_end:
+            cap *= 2
+        key = (n_rows, cap)
+        entry = self._graphs.get(key)
+        if entry is None and key not in self._seen_shapes:
+            # the first step of a shape runs kernel by kernel (it also builds libraries and sets
+            # kernel attributes, which capture does not allow); the second one is captured
+            self._seen_shapes.add(key)
+            return None
+        widths = [(g.ring // PAGE) if g.ring else cap // PAGE for g in self.cache.groups]
+        counts = [1] * n_rows
+        want = [[0]] * n_rows
+        fields = self._host_fields(slots, tokens, counts, starts, want, widths)
+        sizes = [len(f) for f in fields]
+        flat = [x for f in fields for x in f]
+        if entry is None:
+            entry = self._capture(key, sizes, widths, flat, slots, cap)
+        ring = entry["ring"]
+        slot_i = entry["next"] % len(ring)
+        entry["next"] += 1
+        host, event = ring[slot_i]
+        event.synchronize()                         # the copy that last used this buffer is done
+        host.copy_(torch.tensor(flat, dtype=torch.int32))
+        entry["dev"].copy_(host, non_blocking=True)
+        event.record()
+        self.h2d_bytes += host.numel() * 4
+        if device_tokens is not None:
+            entry["dev"][:n_rows].copy_(device_tokens)
+        entry["graph"].replay()
+        K.launches += entry["kernels"]
+        return entry["logits"]
+
+    def _capture(self, key, sizes, widths, flat, slots, cap):
+        n_rows = key[0]
+        total = sum(sizes)
+        dev = torch.zeros(total, dtype=torch.int32, device=self.device)
+        dev.copy_(torch.tensor(flat, dtype=torch.int32))
+        views = self._views(dev, sizes)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        ctx = self._make_ctx(views, widths, n_rows, slots, False, True, 1, cap)
+        before = K.launches
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self._run(ctx, views[6])
+        captured = K.launches - before
+        K.launches = before                         # nothing ran yet; replays are counted
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        ring = []
+        for _ in range(4):
+            host = torch.empty(total, dtype=torch.int32).pin_memory()
+            ring.append((host, torch.cuda.Event()))
+        entry = {"graph": graph, "dev": dev, "logits": logits, "ring": ring, "next": 0,
+                 "kernels": captured}
+        self._graphs[key] = entry
+        return entry
 
     def _bindings(self, ctx: StepContext) -> List[CallBinding]:
         plan = self.model.plan

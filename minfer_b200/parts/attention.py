@@ -27,6 +27,8 @@ DECODE_CHUNK = 256     # keys per chunk when attending over the cache
 
 
 class Attention(Mixer):
+    capturable = True      # launches kernels only; safe inside a CUDA graph capture
+
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  scale: float, window: int = 0, qkv_bias: bool = True, out_bias: bool = False,
                  position: Optional[PartSpec] = None, init_std: float = 0.02):
@@ -140,7 +142,7 @@ class Attention(Mixer):
             lo_bound = ctx.max_end
             n_chunks = max(1, -(-lo_bound // DECODE_CHUNK))
             partial = None
-            if n_chunks > 1:
+            if n_chunks > 1 or act == torch.bfloat16:
                 partial = torch.empty((n * nh * n_chunks * (hd + 2),), dtype=torch.float32,
                                       device=dev)
             K.attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions, cache.page_table,

@@ -96,7 +96,13 @@ class StepContext:
 
 
 class Part:
-    """Common to all roles: the tensors wanted and how they are taken in."""
+    """Common to all roles: the tensors wanted and how they are taken in.
+
+    ``capturable``: the part only launches kernels on the current stream (no read of device
+    memory on the host, no allocation the caching allocator cannot replay).  The engine
+    replays decode steps as CUDA graphs only when every part of the model says so."""
+
+    capturable = False
 
     def tensor_specs(self, prefix: str) -> List[TensorSpec]:
         return []

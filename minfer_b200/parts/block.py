@@ -11,6 +11,8 @@ from .base import Block, CallBinding, StepContext
 
 
 class PreNormBlock(Block):
+    capturable = True      # launches kernels only; safe inside a CUDA graph capture
+
     def __init__(self, layer: LayerSpec):
         from ..registry import build_part
         self.prefix = layer.prefix

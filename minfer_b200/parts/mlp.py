@@ -19,6 +19,8 @@ from .linear import Linear
 
 
 class GatedMlp(FeedForward):
+    capturable = True      # launches kernels only; safe inside a CUDA graph capture
+
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
                  init_std: float = 0.02):
         if activation != "silu":

@@ -12,6 +12,8 @@ from .base import Norm
 
 
 class RmsNorm(Norm):
+    capturable = True      # launches kernels only; safe inside a CUDA graph capture
+
     def __init__(self, size: int, eps: float, name: str = "norm", init_std: float = 0.0):
         self.size = int(size)
         self.eps = float(eps)

@@ -19,6 +19,8 @@ STYLES = {"neox": 0, "interleaved": 1}
 
 
 class Rotary(PositionEncoding):
+    capturable = True      # launches kernels only; safe inside a CUDA graph capture
+
     def __init__(self, head_dim: int, rotary_dim: int, theta: float, frequency_scale: float = 1.0,
                  style: str = "neox"):
         if style not in STYLES:

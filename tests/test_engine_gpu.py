@@ -93,3 +93,34 @@ def test_unequal_batches_slots_reused(tiny, dtype):
     assert set(seen_slots[1]) & set(seen_slots[0]), "the second batch did not reuse a slot"
     assert all(n == eng.cache.groups[i].n_pages for i, n in enumerate(eng.cache.free_pages()))
     eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_through_cuda_graphs_equals_kernel_by_kernel(tiny, dtype):
+    """Long decoding (300 steps across page and chunk boundaries), a batch of three whose
+    shortest prompt is one token, replayed as CUDA graphs and launched kernel by kernel:
+    the same bits."""
+    from minfer_b200.engine.step import Engine
+    from minfer_b200.model import Model
+    model = Model.from_folder(tiny["folder"], dtype, "cuda:0")
+    V = tiny["cfg"]["vocab_size"]
+    prompts = [random_ids(n, V, 900 + n) for n in (1, 50, 200)]
+    feed = [random_ids(300, V, 950 + i) for i in range(3)]
+    outs = []
+    for graphs in (True, False):
+        eng = Engine(model, max_tokens=2048, cuda_graphs=graphs)
+        assert eng.cuda_graphs == graphs
+        slots = [eng.acquire() for _ in prompts]
+        rows = [eng.step(slots, prompts)]
+        for t in range(300):
+            rows.append(eng.step(slots, [[f[t]] for f in feed]))
+        outs.append(torch.stack(rows))
+        if graphs:
+            assert len(eng._graphs) >= 2          # the length bound was crossed at least once
+        eng.check_status()
+    assert torch.equal(outs[0], outs[1])
+    # and the last logits of the longest request agree with the plain implementation
+    ids = prompts[2] + feed[2]
+    want = P.forward(tiny["cfg"], P.load_folder(tiny["folder"])[1], ids)
+    assert rel_err(outs[0][-1, 2], want[-1]) < TOL[dtype]
+    assert rel_err(outs[0][150, 2], want[200 + 149]) < TOL[dtype]

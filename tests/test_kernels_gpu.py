@@ -379,3 +379,61 @@ def test_gemm_tensor_core_refuses_unaligned_rows():
     wr = torch.randn(8, 20).bfloat16().cuda()
     got = Linear(wr).forward(xr, torch.float32)
     close(got, xr.double() @ wr.double().t(), torch.float32)
+
+
+@pytest.mark.parametrize("hd,nh,nk,window,ring", [(128, 28, 4, 0, 0), (64, 14, 2, 0, 0),
+                                                  (128, 16, 1, 0, 0), (64, 3, 3, 100, 128),
+                                                  (128, 8, 2, 300, 0), (64, 12, 4, 40, 64)])
+def test_attention_decode_tensor_core_kernel(hd, nh, nk, window, ring):
+    """The mma decode kernel (bfloat16, head size 64/128) against float64 attention over the
+    same cache, with sequences ending inside a page, at a page edge and at a chunk edge,
+    and a far key that must be found; also against the generic kernel."""
+    from minfer_b200.kernels import api as K
+    lens = [600, 1, 64, 65, 256, 257, 1000]
+    B = len(lens)
+    n_pages = 60
+    g = torch.Generator().manual_seed(hd + nh)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    scale = 1.0 / math.sqrt(hd)
+    dt = torch.bfloat16
+    kc = torch.randn(n_pages, nk, 64, hd, generator=g).to(dt).cuda()       # stale values everywhere
+    vc = torch.randn(n_pages, nk, 64, hd, generator=g).to(dt).cuda()
+    width = 16
+    table = torch.full((B, width), -1, dtype=torch.int32)
+    hist_k, hist_v = [], []
+    q32 = torch.randn(B, nh, hd, generator=g)
+    for b, n in enumerate(lens):
+        kk = torch.randn(n, nk, hd, generator=g)
+        vv = torch.randn(n, nk, hd, generator=g)
+        if n == 1000 and window == 0:           # a far key that dominates head 0
+            kk[17, 0] = 0.0; kk[17, 0, 3] = 30.0
+            q32[b, 0] = 0.0; q32[b, 0, 3] = 30.0
+        kk, vv = kk.to(dt), vv.to(dt)
+        hist_k.append(kk); hist_v.append(vv)
+        lo = max(0, n - ring) if ring else 0
+        for p in range(lo, n):
+            pe = p % ring if ring else p
+            lp = pe // 64
+            if table[b, lp] < 0:
+                table[b, lp] = perm.pop()
+            kc[table[b, lp], :, p % 64] = kk[p].cuda()
+            vc[table[b, lp], :, p % 64] = vv[p].cuda()
+    q = q32.to(dt).cuda()
+    row_seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    row_pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device="cuda")
+    n_chunks = 4
+    outs = {}
+    for force in (False, True):
+        out = torch.empty(B, nh * hd, dtype=dt, device="cuda")
+        partial = torch.full((B * nh * n_chunks * (hd + 2),), float("nan"), device="cuda")
+        K.attention_paged(q, kc, vc, row_seq, row_pos, table.cuda(), width, ring, out, partial,
+                          nh, nk, hd, window, 256, n_chunks, scale, force_generic=force)
+        outs[force] = out
+        for b, n in enumerate(lens):
+            qq = torch.zeros(n, nh, hd, dtype=torch.float64)
+            qq[n - 1] = q[b].double().cpu()
+            want = attention_reference(qq, hist_k[b].double(), hist_v[b].double(), scale, window)
+            close(out[b].reshape(nh, hd), want[n - 1], dt, scale=3.0)
+    close(outs[False], outs[True].double(), dt, scale=3.0)
+    if window == 0:
+        assert torch.allclose(outs[False][6, :hd].float().cpu(), hist_v[6][17, 0].float(), atol=2e-2)
