@@ -467,3 +467,47 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
             partial, (__nv_bfloat16*)out, n_chunks, hd);
     return MF_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------------------------------
+// The same attention for callers that cannot allocate device memory (see
+// attention_noalloc.h for who they are and for the limits).  The scratch that merges key
+// chunks lives in this fixed array.  In host code the array's name only stands for the
+// symbol: it is not a device address, so the address is looked up once per device and that
+// pointer is what the kernels get.
+// ------------------------------------------------------------------------------------------
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float mf_noalloc_scratch[MF_ATTENTION_NOALLOC_FLOATS];
+
+#define MF_NOALLOC_MAX_DEVICES 64
+static float* noalloc_scratch_of_device[MF_NOALLOC_MAX_DEVICES];
+
+extern "C" long long mf_attention_noalloc_capacity(void) {
+    return (long long)MF_ATTENTION_NOALLOC_FLOATS;
+}
+
+extern "C" int mf_attention_paged_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                                          const int* row_seq, const int* row_pos,
+                                          const int* page_table, int table_stride, int ring,
+                                          void* out, int rows, int n_heads, int n_kv, int hd,
+                                          int window, int chunk, int n_chunks, float scale,
+                                          int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (n_heads <= 0 || n_chunks < 1 || hd <= 0) return MF_ERR_ARGUMENT;
+    const long long need = (long long)rows * n_heads * n_chunks * (hd + 2);
+    if (need > (long long)MF_ATTENTION_NOALLOC_FLOATS) return MF_ERR_SCRATCH_LIMIT;
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= MF_NOALLOC_MAX_DEVICES) return MF_ERR_UNSUPPORTED;
+    if (noalloc_scratch_of_device[device] == nullptr) {
+        // set-up, once per device, with that device current
+        float* address = nullptr;
+        e = cudaGetSymbolAddress((void**)&address, mf_noalloc_scratch);
+        if (e != cudaSuccess) return (int)e;
+        noalloc_scratch_of_device[device] = address;
+    }
+    return mf_attention_paged(q, k_cache, v_cache, row_seq, row_pos, page_table, table_stride, ring,
+                              out, noalloc_scratch_of_device[device], rows, n_heads, n_kv, hd, window,
+                              chunk, n_chunks, scale, dtype, 0, stream);
+}
