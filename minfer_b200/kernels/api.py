@@ -121,7 +121,11 @@ def _sig_gemm_tc(lib: ctypes.CDLL) -> None:
     lib.mf_gemm_tc_plan.argtypes = [c_int, c_int, c_int, c_int, c_void_p, c_void_p]
 
 
-_SIGNATURES = {"gemm_tc": _sig_gemm_tc, "ops": _sig_ops, "gemm_simt": _sig_gemm_simt, "attention": _sig_attention,
+def _sig_attention_prefill(lib: ctypes.CDLL) -> None:
+    lib.mf_attention_prefill_mma.argtypes = [c_void_p] * 5 + [c_int] * 6 + [c_float, c_void_p]
+
+
+_SIGNATURES = {"attention_prefill": _sig_attention_prefill, "gemm_tc": _sig_gemm_tc, "ops": _sig_ops, "gemm_simt": _sig_gemm_simt, "attention": _sig_attention,
                "sampling": _sig_sampling}
 
 
@@ -290,6 +294,25 @@ def attention_packed(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, row_seq:
         _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v"), _i32(row_seq, "row_seq"), _i32(row_pos, "row_pos"),
         _i32(cu_seqlens, "cu_seqlens"), _ptr(out, "out"), rows, n_heads, n_kv, head_dim,
         int(window), float(scale), dtype_code(q.dtype), _stream()), "attention_packed")
+
+
+def attention_prefill_supported(q: torch.Tensor, n_heads: int, n_kv: int, head_dim: int) -> bool:
+    """The tensor-core kernel for whole prompts takes bfloat16 and head sizes 64 and 128."""
+    return q.dtype == torch.bfloat16 and head_dim in (64, 128) and n_heads % n_kv == 0
+
+
+def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
+                      out: torch.Tensor, n_seqs: int, max_len: int, n_heads: int, n_kv: int,
+                      head_dim: int, window: int, scale: float) -> None:
+    """Causal attention of whole sequences (positions 0..len-1) packed one after another, on
+    tensor cores.  ``max_len`` is the longest sequence (it sizes the grid)."""
+    for t in (q, k, v, out):
+        if t.dtype != torch.bfloat16:
+            raise KernelError("attention_prefill takes bfloat16")
+    _check(_lib("attention_prefill").mf_attention_prefill_mma(
+        _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v"), _i32(cu_seqlens, "cu_seqlens"), _ptr(out, "out"),
+        int(n_seqs), int(max_len), n_heads, n_kv, head_dim, int(window), float(scale), _stream()),
+        "attention_prefill")
 
 
 def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -33,6 +33,7 @@ LIBRARIES = {
     "attention": ("attention.cu", []),
     "sampling": ("sampling.cu", []),
     "gemm_tc": ("gemm_tc.cu", []),
+    "attention_prefill": ("attention_prefill.cu", []),
 }
 
 

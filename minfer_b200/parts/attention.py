@@ -13,6 +13,7 @@ and values; any other step attends over the cache.  All sizes are parameters.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -24,6 +25,7 @@ from .base import CacheRequest, CallBinding, Mixer, StepContext
 from .linear import Linear
 
 DECODE_CHUNK = 256     # keys per chunk when attending over the cache
+FORCE_GENERIC_ATTENTION = os.environ.get("MINFER_B200_GENERIC_ATTENTION", "0") == "1"
 
 
 class Attention(Mixer):
@@ -131,8 +133,12 @@ class Attention(Mixer):
 
         o = torch.empty((n, nh * hd), dtype=act, device=dev)
         if own_kv:
-            K.attention_packed(q, k_step, v_step, ctx.token_row, ctx.positions, ctx.cu_seqlens, o,
-                               nh, nk, hd, self.window, self.scale)
+            if K.attention_prefill_supported(q, nh, nk, hd) and not FORCE_GENERIC_ATTENTION:
+                K.attention_prefill(q, k_step, v_step, ctx.cu_seqlens, o, ctx.n_rows,
+                                    ctx.max_row_tokens, nh, nk, hd, self.window, self.scale)
+            else:
+                K.attention_packed(q, k_step, v_step, ctx.token_row, ctx.positions,
+                                   ctx.cu_seqlens, o, nh, nk, hd, self.window, self.scale)
         else:
             # keys and values come from the cache: a later token of a sequence
             if cache.ring and not ctx.single_token:
@@ -147,5 +153,6 @@ class Attention(Mixer):
                                       device=dev)
             K.attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions, cache.page_table,
                               cache.table_stride, cache.ring, o, partial, nh, nk, hd, self.window,
-                              DECODE_CHUNK, n_chunks, self.scale)
+                              DECODE_CHUNK, n_chunks, self.scale,
+                              force_generic=FORCE_GENERIC_ATTENTION)
         self.out.forward(o, torch.float32, out=residual, accumulate=True)

@@ -32,7 +32,25 @@ TINY_C = {
     "use_sliding_window": True, "sliding_window": 70, "max_window_layers": 0,
     "max_position_embeddings": 1024,
 }
-TINY = {"A": (TINY_A, 0, 0.0), "B": (TINY_B, 1, 0.01), "C": (TINY_C, 2, 0.02)}
+# head sizes 64 and 128: the sizes the tensor-core attention kernels take, so that the
+# bfloat16 engine runs its product kernels in the whole-model comparisons
+TINY_D = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 300, "hidden_size": 256, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "intermediate_size": 384,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+    "use_sliding_window": True, "sliding_window": 40, "max_window_layers": 1,
+    "max_position_embeddings": 2048,
+}
+TINY_E = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 211, "hidden_size": 384, "num_hidden_layers": 2,
+    "num_attention_heads": 3, "num_key_value_heads": 1, "intermediate_size": 264,
+    "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+    "use_sliding_window": False, "max_position_embeddings": 2048,
+}
+TINY = {"A": (TINY_A, 0, 0.0), "B": (TINY_B, 1, 0.01), "C": (TINY_C, 2, 0.02),
+        "D": (TINY_D, 3, 0.01), "E": (TINY_E, 4, 0.0)}
 
 # Tolerances, as a fraction of the largest logit magnitude of the comparison.  float32
 # differs from the float64 plain implementation by summation order only; bfloat16 rounds

@@ -437,3 +437,41 @@ def test_attention_decode_tensor_core_kernel(hd, nh, nk, window, ring):
     close(outs[False], outs[True].double(), dt, scale=3.0)
     if window == 0:
         assert torch.allclose(outs[False][6, :hd].float().cpu(), hist_v[6][17, 0].float(), atol=2e-2)
+
+
+@pytest.mark.parametrize("hd,nh,nk,window", [(128, 7, 1, 0), (64, 14, 2, 0), (128, 4, 4, 33),
+                                             (64, 6, 2, 200), (128, 2, 1, 64), (64, 3, 1, 1)])
+def test_attention_prefill_tensor_core_kernel(hd, nh, nk, window):
+    """Whole prompts of unequal lengths (one token, tile edges, several tiles) on the mma
+    kernel against float64 attention and against the generic kernel."""
+    from minfer_b200.kernels import api as K
+    lens = [37, 1, 64, 65, 128, 300, 129]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    g = torch.Generator().manual_seed(hd * 3 + nh)
+    dt = torch.bfloat16
+    q = torch.randn(T, nh, hd, generator=g).to(dt).cuda()
+    k = torch.randn(T, nk, hd, generator=g).to(dt).cuda()
+    v = torch.randn(T, nk, hd, generator=g).to(dt).cuda()
+    if window == 0:       # a far key that dominates: the last query of the 300-token sequence
+        b0 = cu[5]
+        k[b0 + 3, 0] = 0.0; k[b0 + 3, 0, 7] = 30.0
+        q[b0 + 299, 0] = 0.0; q[b0 + 299, 0, 7] = 30.0
+    scale = 1.0 / math.sqrt(hd)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    out = torch.full((T, nh * hd), float("nan"), dtype=dt, device="cuda")
+    K.attention_prefill(q, k, v, cu_t, out, len(lens), max(lens), nh, nk, hd, window, scale)
+    row_seq = torch.cat([torch.full((n,), b, dtype=torch.int32) for b, n in enumerate(lens)]).cuda()
+    row_pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).cuda()
+    gen = torch.empty_like(out)
+    K.attention_packed(q, k, v, row_seq, row_pos, cu_t, gen, nh, nk, hd, window, scale)
+    for b, n in enumerate(lens):
+        sl = slice(cu[b], cu[b + 1])
+        want = attention_reference(q[sl].double().cpu(), k[sl].double().cpu(), v[sl].double().cpu(),
+                                   scale, window)
+        close(out[sl].reshape(n, nh, hd), want, dt, scale=3.0)
+    close(out, gen.double(), dt, scale=3.0)
+    if window == 0:
+        assert torch.allclose(out[cu[5] + 299, :hd].float().cpu(), v[cu[5] + 3, 0].float().cpu(), atol=2e-2)
