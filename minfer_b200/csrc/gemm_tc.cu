@@ -394,7 +394,7 @@ extern "C" int mf_gemm_tc_plan(int M, int N, int K, int epi, int* token_tile, in
     const int kblocks = (K + TILE_K - 1) / TILE_K;
     int s = 1;
     if (epi != EPI_SWIGLU && tiles < 100 && kblocks >= 8) {
-        s = (148 + tiles - 1) / tiles;                 // aim at one wave of 148 CTAs
+        s = 148 / tiles;                               // at most one wave of 148 CTAs
         if (s > kblocks / 4) s = kblocks / 4;          // at least 4 k-blocks per split
         if (s > 16) s = 16;
         if (s < 1) s = 1;
@@ -413,9 +413,15 @@ extern "C" long long mf_gemm_tc_workspace_floats(int M, int N, int K, int epi) {
 // out[M][N] (+)= x[M][K] * w[N][K]^T (+ bias).  x, w bfloat16; for EPI_SWIGLU the rows of w
 // alternate gate,up and out is [M][N/2] bfloat16.  `workspace` must hold
 // mf_gemm_tc_workspace_floats floats when that is not zero.
+// `deferred` (may be null): if the product is split along K, the partial sums are LEFT in
+// `workspace` as [splits][M][N], nothing is written to `out`, and *deferred receives the number
+// of splits, so that the caller's next kernel can add them (and the bias) itself; otherwise
+// *deferred is 0 and `out` is complete.
 extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long ldw,
                           const float* bias, void* out, long long ldo, int out_dtype, int M, int N,
-                          int K, int epi, float* workspace, unsigned* status, cudaStream_t stream) {
+                          int K, int epi, float* workspace, int* deferred, unsigned* status,
+                          cudaStream_t stream) {
+    if (deferred) *deferred = 0;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return MF_ERR_UNSUPPORTED;
     if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return MF_ERR_UNSUPPORTED;
@@ -444,6 +450,10 @@ extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long
         default: e = launch<256, 4>(mw, mx, a, splits, stream); break;
     }
     if (e || splits == 1) return e;
+    if (deferred) {
+        *deferred = splits;
+        return 0;
+    }
     const long long total = (long long)M * N;
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads
@@ -454,5 +464,28 @@ extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long
     else
         splitk_reduce_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
             workspace, bias, (__nv_bfloat16*)out, ldo, M, N, splits, 0);
+    return MF_LAUNCH_CHECK();
+}
+
+// out (+)= bias + sum over the K splits left in `partial` ([splits][M][N]) by a deferred
+// product, added in split order.
+extern "C" int mf_splitk_reduce(const float* partial, int splits, const float* bias, void* out,
+                                long long ldo, int out_dtype, int M, int N, int accumulate,
+                                cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (splits < 1 || partial == nullptr) return MF_ERR_ARGUMENT;
+    if (accumulate && out_dtype != MF_DTYPE_F32) return MF_ERR_UNSUPPORTED;
+    const long long total = (long long)M * N;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads
+                                                                       : 148 * 8);
+    if (out_dtype == MF_DTYPE_F32)
+        splitk_reduce_kernel<float><<<blocks, threads, 0, stream>>>(partial, bias, (float*)out, ldo, M,
+                                                                    N, splits, accumulate);
+    else if (out_dtype == MF_DTYPE_BF16)
+        splitk_reduce_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+            partial, bias, (__nv_bfloat16*)out, ldo, M, N, splits, 0);
+    else
+        return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();
 }

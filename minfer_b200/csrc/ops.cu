@@ -83,6 +83,64 @@ extern "C" int mf_rmsnorm(const float* x, const float* w, const int* rows, void*
 }
 
 // ------------------------------------------------------------------------------------
+// Residual add + RMSNorm in one pass: h[r] += bias + sum_s partial[s][r] (the K splits of the
+// projection before it, added in split order), then y[r] = rmsnorm(h[r]) * w.  Saves the
+// separate reduction kernel and one round trip of h.
+// ------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ partial,
+                                   int n_partials, const float* __restrict__ bias,
+                                   const float* __restrict__ w, TO* __restrict__ y, int n_rows,
+                                   int width, float eps) {
+    extern __shared__ float row_s[];                  // the updated row
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    float* hr = h + (size_t)r * width;
+    const size_t plane = (size_t)n_rows * width;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float add = 0.0f;
+        for (int s = 0; s < n_partials; ++s) add += partial[s * plane + (size_t)r * width + i];
+        if (bias) add += bias[i];
+        const float v = hr[i] + add;
+        hr[i] = v;
+        row_s[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    TO* yr = y + (size_t)r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) yr[i] = from_f32<TO>(row_s[i] * scale * w[i]);
+}
+
+extern "C" int mf_add_rmsnorm(float* h, const float* partial, int n_partials, const float* bias,
+                              const float* w, void* y, int out_dtype, int n_rows, int width,
+                              float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (n_partials < 0 || (n_partials > 0 && partial == nullptr)) return MF_ERR_ARGUMENT;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 200 * 1024) return MF_ERR_UNSUPPORTED;
+    int threads = 32;
+    while (threads < 512 && threads * 4 < width) threads <<= 1;
+    if (out_dtype == MF_DTYPE_F32) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_kernel<float>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<float><<<n_rows, threads, smem, stream>>>(h, partial, n_partials, bias, w,
+                                                                    (float*)y, n_rows, width, eps);
+    } else if (out_dtype == MF_DTYPE_BF16) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(
+            h, partial, n_partials, bias, w, (__nv_bfloat16*)y, n_rows, width, eps);
+    } else {
+        return MF_ERR_UNSUPPORTED;
+    }
+    return MF_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
 // rotary + cache write.  Input: the fused projection's float32 output qkv[t] =
 // [q (n_heads*hd) | k (n_kv*hd) | v (n_kv*hd)], bias already added.  Rotates q and k by
 // the token's position (angles in float32: pos * inv_freq[i]), writes
@@ -98,9 +156,13 @@ extern "C" int mf_rmsnorm(const float* x, const float* w, const int* rows, void*
 // style: 0 = pairs (i, i + R/2) ("NeoX", the reference's NonInterleaved), 1 = pairs
 // (2i, 2i+1); R = rotary_dim <= hd, dimensions beyond R pass through; inv_freq null = no
 // rotation at all.
+// n_partials > 0: `qkv` holds [n_partials][tokens][width] K splits of the projection, which
+// are added here in split order together with `bias` (else bias must already be inside).
 // ------------------------------------------------------------------------------------
 template <typename T>
-__global__ void rope_kvstore_kernel(const float* __restrict__ qkv, const int* __restrict__ positions,
+__global__ void rope_kvstore_kernel(const float* __restrict__ qkv, int n_partials, int n_tokens,
+                                    const float* __restrict__ bias,
+                                    const int* __restrict__ positions,
                                     const int* __restrict__ token_row,
                                     const int* __restrict__ seq_end,
                                     const float* __restrict__ inv_freq, T* __restrict__ q_out,
@@ -117,6 +179,14 @@ __global__ void rope_kvstore_kernel(const float* __restrict__ qkv, const int* __
     const int n_slots = (n_heads + 2 * n_kv) * half;
     const size_t in_width = (size_t)(n_heads + 2 * n_kv) * hd;
     const float* in = qkv + (size_t)t * in_width;
+    const size_t plane = (size_t)n_tokens * in_width;
+    // value of element `col` of this token's projection
+    auto value = [&](int col) -> float {
+        float v = in[col];
+        for (int sp = 1; sp < n_partials; ++sp) v += in[sp * plane + col];
+        if (bias != nullptr) v += bias[col];
+        return v;
+    };
 
     // where this token's keys and values go in the cache
     long long cache_row = -1;     // element offset of [kv_head 0][pos%64][0] in the page, or -1
@@ -140,13 +210,13 @@ __global__ void rope_kvstore_kernel(const float* __restrict__ qkv, const int* __
     for (int s = threadIdx.x; s < n_slots; s += blockDim.x) {
         const int head = s / half;      // 0..n_heads-1: q, then k heads, then v heads
         const int i = s - head * half;
-        const float* hin = in + (size_t)head * hd;
+        const int hbase = head * hd;
         int d0, d1;
         float x0, x1;
         const bool is_v = head >= n_heads + n_kv;
         if (!is_v && inv_freq != nullptr && i < rhalf) {
             if (style == 0) { d0 = i; d1 = i + rhalf; } else { d0 = 2 * i; d1 = 2 * i + 1; }
-            const float a = hin[d0], c = hin[d1];
+            const float a = value(hbase + d0), c = value(hbase + d1);
             float sn, cs;
             sincosf((float)pos * inv_freq[i], &sn, &cs);
             x0 = a * cs - c * sn;
@@ -155,8 +225,8 @@ __global__ void rope_kvstore_kernel(const float* __restrict__ qkv, const int* __
             // pass-through pair: for rotated heads the dimensions beyond R, else (2i, 2i+1)
             const int j = (!is_v && inv_freq != nullptr) ? rotary_dim + 2 * (i - rhalf) : 2 * i;
             d0 = j; d1 = j + 1;
-            x0 = hin[d0];
-            x1 = hin[d1];
+            x0 = value(hbase + d0);
+            x1 = value(hbase + d1);
         }
         const T y0 = from_f32<T>(x0), y1 = from_f32<T>(x1);
         if (head < n_heads) {
@@ -177,7 +247,8 @@ __global__ void rope_kvstore_kernel(const float* __restrict__ qkv, const int* __
     }
 }
 
-extern "C" int mf_rope_kvstore(const float* qkv, const int* positions, const int* token_row,
+extern "C" int mf_rope_kvstore(const float* qkv, int n_partials, const float* bias,
+                               const int* positions, const int* token_row,
                                const int* seq_end, const float* inv_freq, void* q_out, void* k_out,
                                void* v_out, void* k_cache, void* v_cache, const int* page_table,
                                int table_stride, int ring, int n_tokens, int n_heads, int n_kv,
@@ -192,12 +263,12 @@ extern "C" int mf_rope_kvstore(const float* qkv, const int* positions, const int
     while (threads < 256 && threads < n_slots) threads <<= 1;
     if (dtype == MF_DTYPE_F32)
         rope_kvstore_kernel<float><<<n_tokens, threads, 0, stream>>>(
-            qkv, positions, token_row, seq_end, inv_freq, (float*)q_out, (float*)k_out,
+            qkv, n_partials, n_tokens, bias, positions, token_row, seq_end, inv_freq, (float*)q_out, (float*)k_out,
             (float*)v_out, (float*)k_cache, (float*)v_cache, page_table, table_stride, ring,
             n_heads, n_kv, hd, rotary_dim, style, status);
     else if (dtype == MF_DTYPE_BF16)
         rope_kvstore_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-            qkv, positions, token_row, seq_end, inv_freq, (__nv_bfloat16*)q_out,
+            qkv, n_partials, n_tokens, bias, positions, token_row, seq_end, inv_freq, (__nv_bfloat16*)q_out,
             (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, (__nv_bfloat16*)k_cache,
             (__nv_bfloat16*)v_cache, page_table, table_stride, ring, n_heads, n_kv, hd,
             rotary_dim, style, status);

@@ -23,7 +23,7 @@ import torch
 from ..cache.paged import PAGE, Cache, CacheError, GroupKey
 from ..kernels import api as K
 from ..model import Model
-from ..parts.base import CacheView, CallBinding, StepContext
+from ..parts.base import CacheView, CallBinding, StepContext, settle_pending
 
 
 class StepError(RuntimeError):
@@ -348,7 +348,12 @@ class Engine:
         n_want = 0 if want_rows is None else want_rows.numel()
         for i, call in enumerate(plan.schedule):
             block = model.blocks[call.layer]
+            takes_pending = getattr(block, "accepts_pending", False)
+            if not takes_pending:
+                settle_pending(ctx, h)
             block.mix(h, ctx, bindings[i])
+            if i == last or not takes_pending:
+                settle_pending(ctx, h)
             if i == last:
                 if n_want == 0:
                     return torch.empty((0, plan.vocab_size), dtype=torch.float32,
@@ -359,7 +364,11 @@ class Engine:
                     K.gather_rows(h, want_rows, picked)
                     h = picked
             block.feed(h, ctx)
-        x = model.final_norm.forward(h, self.dtype)
+        pending = ctx.extras.pop("pending", None)
+        if pending is not None:
+            x = model.final_norm.forward_settling(h, pending, self.dtype)
+        else:
+            x = model.final_norm.forward(h, self.dtype)
         return model.head.forward(x, torch.float32)
 
     def check_status(self) -> None:

@@ -86,7 +86,10 @@ def _sig_ops(lib: ctypes.CDLL) -> None:
                              c_void_p]
     lib.mf_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                                c_void_p]
-    lib.mf_rope_kvstore.argtypes = [c_void_p] * 11 + [c_int] * 9 + [c_void_p, c_void_p]
+    lib.mf_rope_kvstore.argtypes = ([c_void_p, c_int, c_void_p] + [c_void_p] * 10 + [c_int] * 9 +
+                                    [c_void_p, c_void_p])
+    lib.mf_add_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                   c_int, c_int, c_float, c_void_p]
     lib.mf_swiglu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     lib.mf_gather_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.mf_cast.argtypes = [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p]
@@ -115,7 +118,9 @@ def _sig_sampling(lib: ctypes.CDLL) -> None:
 def _sig_gemm_tc(lib: ctypes.CDLL) -> None:
     lib.mf_gemm_tc.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
                                c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                               c_void_p]
+                               c_void_p, c_void_p]
+    lib.mf_splitk_reduce.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int, c_int,
+                                     c_int, c_int, c_void_p]
     lib.mf_gemm_tc_workspace_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mf_gemm_tc_workspace_floats.restype = c_longlong
     lib.mf_gemm_tc_plan.argtypes = [c_int, c_int, c_int, c_int, c_void_p, c_void_p]
@@ -154,16 +159,41 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
                                   _stream()), "rmsnorm")
 
 
+def add_rmsnorm(h: torch.Tensor, partial: Optional[torch.Tensor], n_partials: int,
+                bias: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor) -> None:
+    """h += bias + sum of the K splits in ``partial`` [n_partials, rows, width]; out = rmsnorm(h)."""
+    n, width = out.shape
+    if h.shape != (n, width) or weight.numel() != width:
+        raise KernelError("add_rmsnorm: shapes do not fit")
+    if n_partials > 0 and (partial is None or partial.numel() < n_partials * n * width):
+        raise KernelError("add_rmsnorm: the partial sums are too small")
+    _check(_lib("ops").mf_add_rmsnorm(_f32(h, "h"), _f32(partial, "partial"), int(n_partials),
+                                      _f32(bias, "bias"), _f32(weight, "weight"), _ptr(out, "out"),
+                                      dtype_code(out.dtype), n, width, float(eps), _stream()),
+           "add_rmsnorm")
+
+
 def rope_kvstore(qkv: torch.Tensor, positions: torch.Tensor, token_row: torch.Tensor,
                  seq_end: torch.Tensor, inv_freq: Optional[torch.Tensor], q_out: torch.Tensor,
                  k_out: Optional[torch.Tensor], v_out: Optional[torch.Tensor],
                  k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
                  page_table: Optional[torch.Tensor], table_stride: int, ring: int,
                  n_heads: int, n_kv: int, head_dim: int, rotary_dim: int, style: int,
-                 status: torch.Tensor) -> None:
-    n = qkv.shape[0]
-    if qkv.shape[1] != (n_heads + 2 * n_kv) * head_dim:
+                 status: torch.Tensor, n_partials: int = 0,
+                 bias: Optional[torch.Tensor] = None) -> None:
+    """``n_partials`` > 0: ``qkv`` is [n_partials, tokens, width], the K splits a deferred
+    projection left; they are added here in split order, with ``bias``."""
+    if n_partials > 0:
+        if qkv.dim() != 3 or qkv.shape[0] != n_partials:
+            raise KernelError("rope_kvstore: partial sums must be [splits, tokens, width]")
+        n, width = qkv.shape[1], qkv.shape[2]
+    else:
+        n, width = qkv.shape
+    if width != (n_heads + 2 * n_kv) * head_dim:
         raise KernelError("rope_kvstore: qkv has the wrong width")
+    if bias is not None and bias.numel() != width:
+        raise KernelError("rope_kvstore: bias has the wrong length")
     dt = q_out.dtype
     for t in (k_out, v_out, k_cache, v_cache):
         if t is not None and t.dtype != dt:
@@ -171,7 +201,8 @@ def rope_kvstore(qkv: torch.Tensor, positions: torch.Tensor, token_row: torch.Te
     if (k_cache is None) != (v_cache is None) or (k_cache is not None and page_table is None):
         raise KernelError("rope_kvstore: the cache needs keys, values and a page table")
     _check(_lib("ops").mf_rope_kvstore(
-        _f32(qkv, "qkv"), _i32(positions, "positions"), _i32(token_row, "token_row"),
+        _f32(qkv, "qkv"), int(n_partials), _f32(bias, "bias"), _i32(positions, "positions"),
+        _i32(token_row, "token_row"),
         _i32(seq_end, "seq_end"), _f32(inv_freq, "inv_freq"), _ptr(q_out, "q_out"),
         _ptr(k_out, "k_out"), _ptr(v_out, "v_out"), _ptr(k_cache, "k_cache"),
         _ptr(v_cache, "v_cache"), _i32(page_table, "page_table"), int(table_stride), int(ring),
@@ -277,8 +308,44 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
     ws = torch.empty(need, dtype=torch.float32, device=x.device) if need else None
     _check(lib.mf_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _f32(bias, "bias"),
                           out.data_ptr(), out.stride(0), dtype_code(out.dtype), m, n, k, epi,
-                          _ptr(ws, "workspace"), _i32(status, "status"), _stream()),
+                          _ptr(ws, "workspace"), None, _i32(status, "status"), _stream()),
            "gemm_tc", 2 if need else 1)
+
+
+def gemm_tc_partial_sums(x: torch.Tensor, w: torch.Tensor,
+                         status: torch.Tensor) -> Optional[torch.Tensor]:
+    """If the kernel would split x @ w^T along K, runs only the splits and returns their
+    float32 partial sums [splits, M, N] for the caller's next kernel to add; returns None
+    (and runs nothing) if the product is not split."""
+    m, k = x.shape
+    n = w.shape[0]
+    if not gemm_tc_supported(x, w) or w.shape[1] != k:
+        return None
+    lib = _lib("gemm_tc")
+    need = int(lib.mf_gemm_tc_workspace_floats(m, n, k, EPI_STORE))
+    if need == 0:
+        return None
+    ws = torch.empty(need, dtype=torch.float32, device=x.device)
+    splits = ctypes.c_int(0)
+    _check(lib.mf_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), None,
+                          ws.data_ptr(), n, F32, m, n, k, EPI_STORE, ws.data_ptr(),
+                          ctypes.addressof(splits), _i32(status, "status"), _stream()),
+           "gemm_tc")
+    if splits.value < 1:
+        raise KernelError("gemm_tc: a split product reported no splits")
+    return ws[:splits.value * m * n].view(splits.value, m, n)
+
+
+def splitk_reduce(partial: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                  accumulate: bool) -> None:
+    """out (+)= bias + the sum of ``partial`` [splits, M, N] over its first dimension."""
+    splits, m, n = partial.shape
+    if out.shape != (m, n) or out.stride(1) != 1:
+        raise KernelError("splitk_reduce: out has the wrong shape")
+    _check(_lib("gemm_tc").mf_splitk_reduce(_f32(partial, "partial"), splits, _f32(bias, "bias"),
+                                            out.data_ptr(), out.stride(0), dtype_code(out.dtype),
+                                            m, n, 1 if accumulate else 0, _stream()),
+           "splitk_reduce")
 
 
 # ---------------------------------------------------------------------------------------

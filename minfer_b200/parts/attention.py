@@ -21,7 +21,7 @@ import torch
 from ..config.base import PartSpec
 from ..kernels import api as K
 from ..weights.spec import MATRIX, VECTOR, Init, TensorSpec
-from .base import CacheRequest, CallBinding, Mixer, StepContext
+from .base import CacheRequest, CallBinding, Mixer, StepContext, settle_pending
 from .linear import Linear
 
 DECODE_CHUNK = 256     # keys per chunk when attending over the cache
@@ -98,15 +98,18 @@ class Attention(Mixer):
         n = x.shape[0]
         nh, nk, hd = self.n_heads, self.n_kv_heads, self.head_dim
         dev, act = x.device, ctx.act_dtype
-        qkv = self.qkv.forward(x, torch.float32)
-
         inv_freq, rotary_dim, style = None, 0, 0
-        if self.position is not None:
-            fused = self.position.fused_rotary(dev)
-            if fused is None:
-                self.position.apply(qkv, ctx, nh, nk, hd)
-            else:
-                inv_freq, rotary_dim, style = fused
+        fused = self.position.fused_rotary(dev) if self.position is not None else (None, 0, 0)
+        # the K splits of a small projection are added by the rotary kernel itself
+        split = self.qkv.partial_sums(x) if fused is not None else None
+        if split is not None:
+            qkv, n_partials, qkv_bias = split.partial, split.partial.shape[0], split.bias
+        else:
+            qkv, n_partials, qkv_bias = self.qkv.forward(x, torch.float32), 0, None
+        if fused is None:
+            self.position.apply(qkv, ctx, nh, nk, hd)
+        else:
+            inv_freq, rotary_dim, style = fused
 
         cache = binding.cache
         if cache is None:
@@ -129,7 +132,8 @@ class Attention(Mixer):
                        k_step if write else None, v_step if write else None,
                        cache.k if write else None, cache.v if write else None,
                        cache.page_table if write else None, cache.table_stride, cache.ring,
-                       nh, nk, hd, rotary_dim, style, ctx.status)
+                       nh, nk, hd, rotary_dim, style, ctx.status, n_partials=n_partials,
+                       bias=qkv_bias)
 
         o = torch.empty((n, nh * hd), dtype=act, device=dev)
         if own_kv:
@@ -155,4 +159,9 @@ class Attention(Mixer):
                               cache.table_stride, cache.ring, o, partial, nh, nk, hd, self.window,
                               DECODE_CHUNK, n_chunks, self.scale,
                               force_generic=FORCE_GENERIC_ATTENTION)
-        self.out.forward(o, torch.float32, out=residual, accumulate=True)
+        pending = self.out.partial_sums(o)
+        if pending is None:
+            self.out.forward(o, torch.float32, out=residual, accumulate=True)
+        else:
+            settle_pending(ctx, residual)          # never two at once
+            ctx.extras["pending"] = pending

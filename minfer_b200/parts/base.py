@@ -71,6 +71,28 @@ class CallBinding:
 
 
 @dataclass
+class Pending:
+    """A projection's output that has not been added into the residual stream yet: the
+    float32 K splits ``partial`` [splits, rows, width] and an optional bias.  The true
+    residual is ``h + bias + partial.sum(0)``.  The next norm adds it while it reads ``h``
+    (``Norm.forward_settling``); anything else calls ``settle``."""
+
+    partial: torch.Tensor
+    bias: Optional[torch.Tensor] = None
+
+    def settle(self, h: torch.Tensor) -> None:
+        from ..kernels import api as K
+        K.splitk_reduce(self.partial, self.bias, h, accumulate=True)
+
+
+def settle_pending(ctx: "StepContext", h: torch.Tensor) -> None:
+    """Adds what a part left pending into ``h``."""
+    pending = ctx.extras.pop("pending", None)
+    if pending is not None:
+        pending.settle(h)
+
+
+@dataclass
 class StepContext:
     """The batch of one step, as device tensors plus the few host numbers kernels need for
     their launch shape.  Row ``b`` of the batch is one sequence; tokens are packed row
@@ -115,6 +137,13 @@ class Norm(Part):
     def forward(self, x32: torch.Tensor, out_dtype: torch.dtype,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
+
+    def forward_settling(self, h: torch.Tensor, pending: "Pending",
+                         out_dtype: torch.dtype) -> torch.Tensor:
+        """Adds ``pending`` into ``h`` and norms the result.  Norms that can do both in one
+        kernel override this."""
+        pending.settle(h)
+        return self.forward(h, out_dtype)
 
 
 class PositionEncoding(Part):

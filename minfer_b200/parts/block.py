@@ -34,10 +34,19 @@ class PreNormBlock(Block):
         for part in self._parts():
             part.load(self.prefix, weights)
 
+    accepts_pending = True     # its norms add a pending projection output while reading h
+
+    @staticmethod
+    def _normed(norm, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        pending = ctx.extras.pop("pending", None)
+        if pending is not None:
+            return norm.forward_settling(h, pending, ctx.act_dtype)
+        return norm.forward(h, ctx.act_dtype)
+
     def mix(self, h: torch.Tensor, ctx: StepContext, binding: CallBinding) -> None:
-        x = self.mixer_norm.forward(h, ctx.act_dtype)
+        x = self._normed(self.mixer_norm, h, ctx)
         self.mixer.forward_add(x, ctx, binding, h)
 
     def feed(self, h: torch.Tensor, ctx: StepContext) -> None:
-        x = self.feed_forward_norm.forward(h, ctx.act_dtype)
+        x = self._normed(self.feed_forward_norm, h, ctx)
         self.feed_forward.forward_add(x, ctx, h)

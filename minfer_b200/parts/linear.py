@@ -41,3 +41,15 @@ class Linear:
         else:
             K.gemm_simt(x, self.weight, self.bias, out, accumulate)
         return out
+
+    def partial_sums(self, x: torch.Tensor):
+        """If the tensor-core kernel would split this product along K (few tokens, few output
+        rows), runs the splits and returns them as a ``Pending`` (bias included) for the next
+        kernel to add; otherwise returns None and the caller uses ``forward``."""
+        from ..kernels import gemm
+        from .base import Pending
+        if (x.dtype != torch.bfloat16 or self.weight.dtype != torch.bfloat16 or x.shape[0] == 0
+                or not gemm.use_tensor_cores()):
+            return None
+        partial = K.gemm_tc_partial_sums(x, self.weight, gemm.status_word(x.device))
+        return None if partial is None else Pending(partial, self.bias)

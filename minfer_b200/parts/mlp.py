@@ -14,7 +14,7 @@ import torch
 
 from ..kernels import api as K
 from ..weights.spec import MATRIX, Init, TensorSpec
-from .base import FeedForward, StepContext
+from .base import FeedForward, StepContext, settle_pending
 from .linear import Linear
 
 
@@ -69,4 +69,9 @@ class GatedMlp(FeedForward):
         else:
             gu = self.gate_up.forward(x, ctx.act_dtype)
             K.swiglu(gu, act, self.interleaved)
-        self.down.forward(act, torch.float32, out=residual, accumulate=True)
+        pending = self.down.partial_sums(act)
+        if pending is None:
+            self.down.forward(act, torch.float32, out=residual, accumulate=True)
+        else:
+            settle_pending(ctx, residual)          # never two at once
+            ctx.extras["pending"] = pending

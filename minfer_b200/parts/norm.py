@@ -34,3 +34,9 @@ class RmsNorm(Norm):
         out = torch.empty((n, self.size), dtype=out_dtype, device=x32.device)
         K.rmsnorm(x32, self.weight, self.eps, out, rows)
         return out
+
+    def forward_settling(self, h: torch.Tensor, pending, out_dtype: torch.dtype) -> torch.Tensor:
+        out = torch.empty((h.shape[0], self.size), dtype=out_dtype, device=h.device)
+        K.add_rmsnorm(h, pending.partial, pending.partial.shape[0], pending.bias, self.weight,
+                      self.eps, out)
+        return out

@@ -475,3 +475,62 @@ def test_attention_prefill_tensor_core_kernel(hd, nh, nk, window):
     close(out, gen.double(), dt, scale=3.0)
     if window == 0:
         assert torch.allclose(out[cu[5] + 299, :hd].float().cpu(), v[cu[5] + 3, 0].float().cpu(), atol=2e-2)
+
+
+def test_deferred_split_sums_feed_the_next_kernel():
+    """A small projection leaves its K splits; add_rmsnorm and rope_kvstore add them (and the
+    bias) themselves: the same numbers as reducing first."""
+    from minfer_b200.kernels import api as K
+    g = torch.Generator().manual_seed(5)
+    m, n, k = 8, 3584, 3584
+    x = (torch.randn(m, k, generator=g) * 0.3).bfloat16().cuda()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16().cuda()
+    bias = torch.randn(n, generator=g).cuda()
+    st = status()
+    partial = K.gemm_tc_partial_sums(x, w, st)
+    assert partial is not None and partial.shape[0] > 1 and partial.shape[1:] == (m, n)
+    full = x.double() @ w.double().t()
+    close(partial.sum(0), full, torch.float32)
+    # reduce, accumulate
+    h = torch.randn(m, n, generator=g).cuda()
+    h0 = h.clone()
+    K.splitk_reduce(partial, bias, h, accumulate=True)
+    close(h, h0.double() + full + bias.double(), torch.float32)
+    # add + norm in one kernel
+    wn = (1 + 0.1 * torch.randn(n, generator=g)).cuda()
+    for dt in DTYPES:
+        h2 = h0.clone()
+        y = torch.empty(m, n, dtype=dt, device="cuda")
+        K.add_rmsnorm(h2, partial, partial.shape[0], bias, wn, 1e-6, y)
+        assert torch.equal(h2, h)                      # the same sums in the same order
+        hd_ = h.double()
+        want = hd_ / torch.sqrt((hd_ ** 2).mean(-1, keepdim=True) + 1e-6) * wn.double()
+        close(y, want, dt)
+    # no partial sums: plain residual + norm
+    h3 = h0.clone()
+    y = torch.empty(m, n, device="cuda")
+    K.add_rmsnorm(h3, None, 0, None, wn, 1e-6, y)
+    assert torch.equal(h3, h0)
+    # a product that is not split leaves nothing
+    assert K.gemm_tc_partial_sums(torch.zeros(2048, 64, dtype=torch.bfloat16, device="cuda"),
+                                  torch.zeros(256, 64, dtype=torch.bfloat16, device="cuda"), st) is None
+    # rotary kernel adding the splits: equals the kernel run on the reduced projection
+    nh, nk, hd = 20, 4, 128
+    assert (nh + 2 * nk) * hd == n
+    red = torch.empty(m, n, device="cuda")
+    K.splitk_reduce(partial, bias, red, accumulate=False)
+    pos = torch.arange(100, 100 + m, dtype=torch.int32, device="cuda")
+    rows = torch.zeros(m, dtype=torch.int32, device="cuda")
+    end = torch.tensor([100 + m], dtype=torch.int32, device="cuda")
+    inv_freq = (1.0 / (1e6 ** (torch.arange(hd // 2).double() * 2 / hd))).float().cuda()
+    outs = []
+    for src, npart, b in ((red, 0, None), (partial, partial.shape[0], bias)):
+        q = torch.empty(m, nh, hd, dtype=torch.bfloat16, device="cuda")
+        ks = torch.empty(m, nk, hd, dtype=torch.bfloat16, device="cuda")
+        vs = torch.empty_like(ks)
+        K.rope_kvstore(src, pos, rows, end, inv_freq, q, ks, vs, None, None, None, 0, 0, nh, nk, hd,
+                       hd, 0, st, n_partials=npart, bias=b)
+        outs.append((q, ks, vs))
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b)
+    assert int(st) == 0
