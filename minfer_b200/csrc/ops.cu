@@ -113,11 +113,79 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const float* __restric
     for (int i = threadIdx.x; i < width; i += blockDim.x) yr[i] = from_f32<TO>(row_s[i] * scale * w[i]);
 }
 
+// the same for widths that are multiples of 4 up to 4 * 4 * 1024: float4 accesses, the row
+// kept in registers, all loads of a thread independent of each other
+#define ARN_MAXV 4
+template <typename TO>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ partial, int n_partials,
+                       const float* __restrict__ bias, const float* __restrict__ w,
+                       TO* __restrict__ y, int n_rows, int width, float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int nv = width >> 2;                         // float4 per row
+    float4* hr = reinterpret_cast<float4*>(h + (size_t)r * width);
+    const size_t plane4 = ((size_t)n_rows * width) >> 2;
+    const float4* pr = reinterpret_cast<const float4*>(partial) + ((size_t)r * width >> 2);
+    float4 row[ARN_MAXV];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < ARN_MAXV; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+            for (int s = 0; s < n_partials; ++s) {
+                const float4 p = pr[s * plane4 + i];
+                acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+            }
+            if (bias) {
+                const float4 b = reinterpret_cast<const float4*>(bias)[i];
+                acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
+            }
+            float4 v = hr[i];
+            v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;
+            hr[i] = v;
+            row[j] = v;
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    TO* yr = y + (size_t)r * width;
+#pragma unroll
+    for (int j = 0; j < ARN_MAXV; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            const float4 g = reinterpret_cast<const float4*>(w)[i];
+            const float4 v = row[j];
+            yr[4 * i + 0] = from_f32<TO>(v.x * scale * g.x);
+            yr[4 * i + 1] = from_f32<TO>(v.y * scale * g.y);
+            yr[4 * i + 2] = from_f32<TO>(v.z * scale * g.z);
+            yr[4 * i + 3] = from_f32<TO>(v.w * scale * g.w);
+        }
+    }
+}
+
 extern "C" int mf_add_rmsnorm(float* h, const float* partial, int n_partials, const float* bias,
                               const float* w, void* y, int out_dtype, int n_rows, int width,
                               float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (n_partials < 0 || (n_partials > 0 && partial == nullptr)) return MF_ERR_ARGUMENT;
+    if (width % 4 == 0 && width <= 4 * ARN_MAXV * 1024 && (out_dtype == MF_DTYPE_F32 ||
+                                                            out_dtype == MF_DTYPE_BF16)) {
+        // one thread per float4 where that fits; the block size depends on the width only
+        int threads = 32;
+        while (threads < 1024 && threads * 4 < width) threads <<= 1;
+        if (out_dtype == MF_DTYPE_F32)
+            add_rmsnorm_vec_kernel<float><<<n_rows, threads, 0, stream>>>(
+                h, partial, n_partials, bias, w, (float*)y, n_rows, width, eps);
+        else
+            add_rmsnorm_vec_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
+                h, partial, n_partials, bias, w, (__nv_bfloat16*)y, n_rows, width, eps);
+        return MF_LAUNCH_CHECK();
+    }
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 200 * 1024) return MF_ERR_UNSUPPORTED;
     int threads = 32;
@@ -200,14 +268,15 @@ __global__ void rope_kvstore_kernel(const float* __restrict__ qkv, int n_partial
         if (keep) {
             const int page = page_table[(size_t)b * table_stride + (p_eff >> 6)];
             if (page < 0) {
-                if (threadIdx.x == 0) atomicOr(status, MF_STATUS_BAD_POSITION);
+                if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, MF_STATUS_BAD_POSITION);
             } else {
                 cache_row = ((long long)page * n_kv * MF_PAGE + (pos & (MF_PAGE - 1))) * hd;
             }
         }
     }
 
-    for (int s = threadIdx.x; s < n_slots; s += blockDim.x) {
+    // blockIdx.y spreads a token's pairs over several blocks when there are few tokens
+    for (int s = blockIdx.y * blockDim.x + threadIdx.x; s < n_slots; s += gridDim.y * blockDim.x) {
         const int head = s / half;      // 0..n_heads-1: q, then k heads, then v heads
         const int i = s - head * half;
         const int hbase = head * hd;
@@ -259,15 +328,20 @@ extern "C" int mf_rope_kvstore(const float* qkv, int n_partials, const float* bi
         return MF_ERR_UNSUPPORTED;
     if (ring % MF_PAGE != 0) return MF_ERR_ARGUMENT;
     const int n_slots = (n_heads + 2 * n_kv) * (hd / 2);
-    int threads = 64;
-    while (threads < 256 && threads < n_slots) threads <<= 1;
+    const int threads = 128;
+    // enough blocks to fill the GPU even for a handful of tokens
+    int gy = (592 + n_tokens - 1) / n_tokens;
+    const int gy_max = (n_slots + threads - 1) / threads;
+    if (gy > gy_max) gy = gy_max;
+    if (gy < 1) gy = 1;
+    const dim3 grid(n_tokens, gy);
     if (dtype == MF_DTYPE_F32)
-        rope_kvstore_kernel<float><<<n_tokens, threads, 0, stream>>>(
+        rope_kvstore_kernel<float><<<grid, threads, 0, stream>>>(
             qkv, n_partials, n_tokens, bias, positions, token_row, seq_end, inv_freq, (float*)q_out, (float*)k_out,
             (float*)v_out, (float*)k_cache, (float*)v_cache, page_table, table_stride, ring,
             n_heads, n_kv, hd, rotary_dim, style, status);
     else if (dtype == MF_DTYPE_BF16)
-        rope_kvstore_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        rope_kvstore_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
             qkv, n_partials, n_tokens, bias, positions, token_row, seq_end, inv_freq, (__nv_bfloat16*)q_out,
             (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, (__nv_bfloat16*)k_cache,
             (__nv_bfloat16*)v_cache, page_table, table_stride, ring, n_heads, n_kv, hd,
