@@ -62,6 +62,7 @@ struct AttnArgs {
 
 template <typename T, bool PAGED>
 __global__ void __launch_bounds__(ATT_WARPS * 32) attention_generic_kernel(AttnArgs a) {
+    pdl_prologue();
     __shared__ float q_s[ATT_WARPS][ATT_MAX_HD];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const long long item = (long long)blockIdx.x * ATT_WARPS + warp;
@@ -168,6 +169,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_generic_kernel(AttnA
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ partial, T* __restrict__ out,
                                          int n_chunks, int hd) {
+    pdl_prologue();
     const size_t rh = blockIdx.x;                     // row * n_heads + head
     const float* p = partial + rh * n_chunks * (hd + 2);
     float m = -INFINITY;
@@ -217,6 +219,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 template <int HD>
 __global__ void __launch_bounds__(128) attention_decode_mma_kernel(AttnArgs a) {
+    pdl_prologue();
     constexpr int CPR = HD / 8;                       // 16-byte chunks per row
     extern __shared__ __align__(128) uint8_t dec_smem[];
     __nv_bfloat16* v_s = (__nv_bfloat16*)dec_smem;                      // [4][64][HD], swizzled
@@ -386,7 +389,7 @@ static int launch_decode_mma(const AttnArgs& a, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(a.n_chunks, a.n_kv, a.rows);
-    attention_decode_mma_kernel<HD><<<grid, 128, smem, stream>>>(a);
+    mf_launch(attention_decode_mma_kernel<HD>, dim3(grid), dim3(128), smem, stream, a);
     return MF_LAUNCH_CHECK();
 }
 
@@ -411,9 +414,9 @@ extern "C" int mf_attention_packed(const void* q, const void* k, const void* v, 
     const long long items = (long long)rows * n_heads;
     const unsigned blocks = (unsigned)((items + ATT_WARPS - 1) / ATT_WARPS);
     if (dtype == MF_DTYPE_F32)
-        attention_generic_kernel<float, false><<<blocks, ATT_WARPS * 32, 0, stream>>>(a);
+        mf_launch(attention_generic_kernel<float, false>, dim3(blocks), dim3(ATT_WARPS * 32), 0, stream, a);
     else if (dtype == MF_DTYPE_BF16)
-        attention_generic_kernel<__nv_bfloat16, false><<<blocks, ATT_WARPS * 32, 0, stream>>>(a);
+        mf_launch(attention_generic_kernel<__nv_bfloat16, false>, dim3(blocks), dim3(ATT_WARPS * 32), 0, stream, a);
     else
         return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();
@@ -444,26 +447,30 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
         a.partial = partial;
         int e = hd == 64 ? launch_decode_mma<64>(a, stream) : launch_decode_mma<128>(a, stream);
         if (e) return e;
-        attention_combine_kernel<__nv_bfloat16><<<rows * n_heads, hd, 0, stream>>>(
+        // measured: started early, the merge of the chunks costs 5 us more than it saves (its
+        // blocks sit on the SMs while the last attention blocks still look for room)
+        mf_launch_serial = true;
+        mf_launch(attention_combine_kernel<__nv_bfloat16>, dim3(rows * n_heads), dim3(hd), 0, stream, 
             partial, (__nv_bfloat16*)out, n_chunks, hd);
+        mf_launch_serial = false;
         return MF_LAUNCH_CHECK();
     }
     const long long items = (long long)rows * n_heads * n_chunks;
     const unsigned blocks = (unsigned)((items + ATT_WARPS - 1) / ATT_WARPS);
     if (dtype == MF_DTYPE_F32)
-        attention_generic_kernel<float, true><<<blocks, ATT_WARPS * 32, 0, stream>>>(a);
+        mf_launch(attention_generic_kernel<float, true>, dim3(blocks), dim3(ATT_WARPS * 32), 0, stream, a);
     else if (dtype == MF_DTYPE_BF16)
-        attention_generic_kernel<__nv_bfloat16, true><<<blocks, ATT_WARPS * 32, 0, stream>>>(a);
+        mf_launch(attention_generic_kernel<__nv_bfloat16, true>, dim3(blocks), dim3(ATT_WARPS * 32), 0, stream, a);
     else
         return MF_ERR_UNSUPPORTED;
     int e = MF_LAUNCH_CHECK();
     if (e || n_chunks == 1) return e;
     const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
     if (dtype == MF_DTYPE_F32)
-        attention_combine_kernel<float><<<rows * n_heads, threads, 0, stream>>>(
+        mf_launch(attention_combine_kernel<float>, dim3(rows * n_heads), dim3(threads), 0, stream, 
             partial, (float*)out, n_chunks, hd);
     else
-        attention_combine_kernel<__nv_bfloat16><<<rows * n_heads, threads, 0, stream>>>(
+        mf_launch(attention_combine_kernel<__nv_bfloat16>, dim3(rows * n_heads), dim3(threads), 0, stream, 
             partial, (__nv_bfloat16*)out, n_chunks, hd);
     return MF_LAUNCH_CHECK();
 }

@@ -70,6 +70,7 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* tile, const __nv_bfloat
 
 template <int HD>
 __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_mma_kernel(PrefillArgs a) {
+    pdl_prologue();
     constexpr int CPR = HD / 8;
     extern __shared__ __align__(128) uint8_t pf_smem[];
     __nv_bfloat16* q_s = (__nv_bfloat16*)pf_smem;                 // [64][HD]
@@ -251,7 +252,7 @@ static int launch_prefill(const PrefillArgs& a, int n_seqs, int max_len, cudaStr
         configured = true;
     }
     dim3 grid((max_len + PF_ROWS - 1) / PF_ROWS, a.n_heads, n_seqs);
-    attention_prefill_mma_kernel<HD><<<grid, PF_WARPS * 32, smem, stream>>>(a);
+    mf_launch(attention_prefill_mma_kernel<HD>, dim3(grid), dim3(PF_WARPS * 32), smem, stream, a);
     return MF_LAUNCH_CHECK();
 }
 

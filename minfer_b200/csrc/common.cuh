@@ -79,4 +79,55 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// ---- programmatic dependent launch ---------------------------------------------------------
+// Every kernel is launched so that it may start while the kernel before it in the stream is
+// still running: the earlier kernel says "dependents may launch" as its first instruction,
+// the later one waits for the earlier grid to have completed (and its writes to be visible)
+// before it touches any memory that is not constant over the step.  What is hidden is the
+// launch latency and a kernel's prologue (and, in the tensor-core GEMM, the first weight
+// tiles, which no kernel of the step writes).  EVERY kernel executes the wait, needed or not,
+// so that completion stays transitive along the stream.  MINFER_B200_PDL=0 turns the launch
+// attribute off; the instructions are then no-ops.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_prologue() {
+    pdl_launch_dependents();
+    pdl_wait();
+}
+
+#ifdef __CUDACC__
+#include <cstdlib>
+#include <utility>
+static inline bool mf_pdl_enabled() {
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char* e = getenv("MINFER_B200_PDL");
+        enabled = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return enabled == 1;
+}
+
+static inline bool mf_launch_serial = false;   // set around a launch that must not start early
+
+template <typename... KArgs, typename... Args>
+static inline void mf_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = (mf_pdl_enabled() && !mf_launch_serial) ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#endif
+
 #define MF_LAUNCH_CHECK() ((int)cudaGetLastError())

@@ -20,6 +20,7 @@ __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W, const float* __restrict__ bias,
                  TC* __restrict__ C, int M, int N, int K, long long lda, long long ldw,
                  long long ldc, int accumulate) {
+    pdl_prologue();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -88,7 +89,7 @@ extern "C" int mf_gemm_simt(const void* A, int a_dtype, const void* W, int w_dty
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return MF_ERR_UNSUPPORTED;
 #define MF_GEMM(TA, TW, TC)                                                                  \
-    gemm_simt_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, bias,  \
+    mf_launch(gemm_simt_kernel<TA, TW, TC>, dim3(grid), dim3(256), 0, stream, (const TA*)A, (const TW*)W, bias,  \
                                                            (TC*)C, M, N, K, lda, ldw, ldc,   \
                                                            accumulate)
     typedef __nv_bfloat16 bf16;

@@ -152,6 +152,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
+    pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m0 = blockIdx.x * NT;                  // first token of this tile
     const int n0 = blockIdx.y * TILE_N;              // first row of W
@@ -183,7 +184,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
     if (warp == 0 && lane == 0) {
         // ---- TMA producer ------------------------------------------------------------
-        for (int i = 0; i < n_iter; ++i) {
+        // The weights are constant over the step: their first tiles are requested before the
+        // kernel waits for the one before it, so that they stream in while that one finishes.
+        const int pre = n_iter < STAGES ? n_iter : STAGES;
+        for (int i = 0; i < pre; ++i) {
+            const uint32_t full = smem_u32(&bars[i]);
+            mbar_expect_tx(full, STAGE_BYTES);
+            tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_w, (kb0 + i) * TILE_K, n0, full);
+        }
+        pdl_wait();
+        for (int i = 0; i < pre; ++i)
+            tma_load_2d(smem_u32(smem + i * STAGE_BYTES) + A_BYTES, &map_x, (kb0 + i) * TILE_K, m0,
+                        smem_u32(&bars[i]));
+        for (int i = pre; i < n_iter; ++i) {
             const int s = i % STAGES;
             const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
             if (!mbar_wait(smem_u32(&bars[STAGES + s]), ph ^ 1u, abort_flag)) break;
@@ -193,7 +206,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             tma_load_2d(dst, &map_w, (kb0 + i) * TILE_K, n0, full);
             tma_load_2d(dst + A_BYTES, &map_x, (kb0 + i) * TILE_K, m0, full);
         }
-    } else if (warp == 1 && lane == 0) {
+    } else {
+        pdl_wait();          // every other thread: nothing below may run ahead of the kernel before
+    }
+    if (warp == 1 && lane == 0) {
         // ---- MMA issuer --------------------------------------------------------------
         constexpr uint32_t idesc = umma_idesc(NT);
         bool ok = true;
@@ -294,6 +310,7 @@ template <typename TO>
 __global__ void splitk_reduce_kernel(const float* __restrict__ partial, const float* __restrict__ bias,
                                      TO* __restrict__ out, long long ldo, int M, int N, int splits,
                                      int accumulate) {
+    pdl_prologue();
     const long long total = (long long)M * N;
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
@@ -382,7 +399,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& 
         configured = true;
     }
     dim3 grid((a.M + NT - 1) / NT, (a.N + TILE_N - 1) / TILE_N, splits);
-    gemm_tc_kernel<NT, STAGES><<<grid, 128, smem, stream>>>(mw, mx, a);
+    mf_launch(gemm_tc_kernel<NT, STAGES>, dim3(grid), dim3(128), smem, stream, mw, mx, a);
     return MF_LAUNCH_CHECK();
 }
 
@@ -459,10 +476,10 @@ extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long
     const int blocks = (int)((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads
                                                                        : 148 * 8);
     if (out_dtype == MF_DTYPE_F32)
-        splitk_reduce_kernel<float><<<blocks, threads, 0, stream>>>(
+        mf_launch(splitk_reduce_kernel<float>, dim3(blocks), dim3(threads), 0, stream, 
             workspace, bias, (float*)out, ldo, M, N, splits, epi == EPI_ACCUM);
     else
-        splitk_reduce_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+        mf_launch(splitk_reduce_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, 
             workspace, bias, (__nv_bfloat16*)out, ldo, M, N, splits, 0);
     return MF_LAUNCH_CHECK();
 }
@@ -480,10 +497,10 @@ extern "C" int mf_splitk_reduce(const float* partial, int splits, const float* b
     const int blocks = (int)((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads
                                                                        : 148 * 8);
     if (out_dtype == MF_DTYPE_F32)
-        splitk_reduce_kernel<float><<<blocks, threads, 0, stream>>>(partial, bias, (float*)out, ldo, M,
+        mf_launch(splitk_reduce_kernel<float>, dim3(blocks), dim3(threads), 0, stream, partial, bias, (float*)out, ldo, M,
                                                                     N, splits, accumulate);
     else if (out_dtype == MF_DTYPE_BF16)
-        splitk_reduce_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+        mf_launch(splitk_reduce_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, 
             partial, bias, (__nv_bfloat16*)out, ldo, M, N, splits, 0);
     else
         return MF_ERR_UNSUPPORTED;

@@ -16,6 +16,7 @@ template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ out, int width, int vocab,
                              unsigned* __restrict__ status) {
+    pdl_prologue();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * width;
@@ -34,10 +35,10 @@ extern "C" int mf_embed(const void* table, int table_dtype, const int* ids, floa
     if (n_tokens <= 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     if (table_dtype == MF_DTYPE_F32)
-        embed_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)table, ids, out, width,
+        mf_launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, out, width,
                                                              vocab, status);
     else if (table_dtype == MF_DTYPE_BF16)
-        embed_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        mf_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, 
             (const __nv_bfloat16*)table, ids, out, width, vocab, status);
     else
         return MF_ERR_UNSUPPORTED;
@@ -52,6 +53,7 @@ template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                const int* __restrict__ rows, TO* __restrict__ y, int width,
                                float eps) {
+    pdl_prologue();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const float* xr = x + (size_t)(rows ? rows[r] : r) * width;
@@ -73,9 +75,9 @@ extern "C" int mf_rmsnorm(const float* x, const float* w, const int* rows, void*
     int threads = 32;
     while (threads < 512 && threads * 4 < width) threads <<= 1;
     if (out_dtype == MF_DTYPE_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, stream>>>(x, w, rows, (float*)y, width, eps);
+        mf_launch(rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, w, rows, (float*)y, width, eps);
     else if (out_dtype == MF_DTYPE_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(x, w, rows, (__nv_bfloat16*)y,
+        mf_launch(rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, w, rows, (__nv_bfloat16*)y,
                                                                       width, eps);
     else
         return MF_ERR_UNSUPPORTED;
@@ -92,6 +94,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const float* __restric
                                    int n_partials, const float* __restrict__ bias,
                                    const float* __restrict__ w, TO* __restrict__ y, int n_rows,
                                    int width, float eps) {
+    pdl_prologue();
     extern __shared__ float row_s[];                  // the updated row
     __shared__ float scratch[33];
     const int r = blockIdx.x;
@@ -121,6 +124,7 @@ __global__ void __launch_bounds__(1024)
 add_rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ partial, int n_partials,
                        const float* __restrict__ bias, const float* __restrict__ w,
                        TO* __restrict__ y, int n_rows, int width, float eps) {
+    pdl_prologue();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int nv = width >> 2;                         // float4 per row
@@ -179,10 +183,10 @@ extern "C" int mf_add_rmsnorm(float* h, const float* partial, int n_partials, co
         int threads = 32;
         while (threads < 1024 && threads * 4 < width) threads <<= 1;
         if (out_dtype == MF_DTYPE_F32)
-            add_rmsnorm_vec_kernel<float><<<n_rows, threads, 0, stream>>>(
+            mf_launch(add_rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, 
                 h, partial, n_partials, bias, w, (float*)y, n_rows, width, eps);
         else
-            add_rmsnorm_vec_kernel<__nv_bfloat16><<<n_rows, threads, 0, stream>>>(
+            mf_launch(add_rmsnorm_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, 
                 h, partial, n_partials, bias, w, (__nv_bfloat16*)y, n_rows, width, eps);
         return MF_LAUNCH_CHECK();
     }
@@ -194,13 +198,13 @@ extern "C" int mf_add_rmsnorm(float* h, const float* partial, int n_partials, co
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_kernel<float>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<float><<<n_rows, threads, smem, stream>>>(h, partial, n_partials, bias, w,
+        mf_launch(add_rmsnorm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, h, partial, n_partials, bias, w,
                                                                     (float*)y, n_rows, width, eps);
     } else if (out_dtype == MF_DTYPE_BF16) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(add_rmsnorm_kernel<__nv_bfloat16>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        add_rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, smem, stream>>>(
+        mf_launch(add_rmsnorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), smem, stream, 
             h, partial, n_partials, bias, w, (__nv_bfloat16*)y, n_rows, width, eps);
     } else {
         return MF_ERR_UNSUPPORTED;
@@ -239,6 +243,7 @@ __global__ void rope_kvstore_kernel(const float* __restrict__ qkv, int n_partial
                                     const int* __restrict__ page_table, int table_stride, int ring,
                                     int n_heads, int n_kv, int hd, int rotary_dim, int style,
                                     unsigned* __restrict__ status) {
+    pdl_prologue();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int b = token_row[t];
@@ -336,12 +341,12 @@ extern "C" int mf_rope_kvstore(const float* qkv, int n_partials, const float* bi
     if (gy < 1) gy = 1;
     const dim3 grid(n_tokens, gy);
     if (dtype == MF_DTYPE_F32)
-        rope_kvstore_kernel<float><<<grid, threads, 0, stream>>>(
+        mf_launch(rope_kvstore_kernel<float>, dim3(grid), dim3(threads), 0, stream, 
             qkv, n_partials, n_tokens, bias, positions, token_row, seq_end, inv_freq, (float*)q_out, (float*)k_out,
             (float*)v_out, (float*)k_cache, (float*)v_cache, page_table, table_stride, ring,
             n_heads, n_kv, hd, rotary_dim, style, status);
     else if (dtype == MF_DTYPE_BF16)
-        rope_kvstore_kernel<__nv_bfloat16><<<grid, threads, 0, stream>>>(
+        mf_launch(rope_kvstore_kernel<__nv_bfloat16>, dim3(grid), dim3(threads), 0, stream, 
             qkv, n_partials, n_tokens, bias, positions, token_row, seq_end, inv_freq, (__nv_bfloat16*)q_out,
             (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, (__nv_bfloat16*)k_cache,
             (__nv_bfloat16*)v_cache, page_table, table_stride, ring, n_heads, n_kv, hd,
@@ -359,6 +364,7 @@ extern "C" int mf_rope_kvstore(const float* qkv, int n_partials, const float* bi
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int nf,
                               long long total, int interleaved) {
+    pdl_prologue();
     for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long t = idx / nf;
@@ -377,7 +383,7 @@ extern "C" int mf_swiglu(const void* gu, int in_dtype, void* out, int out_dtype,
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16
                                  ? (total + threads - 1) / threads : 148 * 16);
 #define MF_SWIGLU(TI, TO) \
-    swiglu_kernel<TI, TO><<<blocks, threads, 0, stream>>>((const TI*)gu, (TO*)out, nf, total, \
+    mf_launch(swiglu_kernel<TI, TO>, dim3(blocks), dim3(threads), 0, stream, (const TI*)gu, (TO*)out, nf, total, \
                                                           interleaved)
     if (in_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_F32) MF_SWIGLU(float, float);
     else if (in_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_BF16) MF_SWIGLU(float, __nv_bfloat16);
@@ -393,6 +399,7 @@ extern "C" int mf_swiglu(const void* gu, int in_dtype, void* out, int out_dtype,
 // ------------------------------------------------------------------------------------
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                    float* __restrict__ out, int width) {
+    pdl_prologue();
     const float* xr = x + (size_t)rows[blockIdx.x] * width;
     float* o = out + (size_t)blockIdx.x * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = xr[i];
@@ -401,7 +408,7 @@ __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __res
 extern "C" int mf_gather_rows(const float* x, const int* rows, float* out, int n_rows, int width,
                               cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    gather_rows_kernel<<<n_rows, 256, 0, stream>>>(x, rows, out, width);
+    mf_launch(gather_rows_kernel, dim3(n_rows), dim3(256), 0, stream, x, rows, out, width);
     return MF_LAUNCH_CHECK();
 }
 
@@ -410,6 +417,7 @@ extern "C" int mf_gather_rows(const float* x, const int* rows, float* out, int n
 // ------------------------------------------------------------------------------------
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, long long n) {
+    pdl_prologue();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
          i += (long long)gridDim.x * blockDim.x)
         out[i] = from_f32<TO>(to_f32(in[i]));
@@ -422,10 +430,10 @@ extern "C" int mf_cast(const void* in, int in_dtype, void* out, int out_dtype, l
     const long long want = (n + threads - 1) / threads;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
     if (in_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_BF16)
-        cast_kernel<float, __nv_bfloat16><<<blocks, threads, 0, stream>>>(
+        mf_launch(cast_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, 
             (const float*)in, (__nv_bfloat16*)out, n);
     else if (in_dtype == MF_DTYPE_BF16 && out_dtype == MF_DTYPE_F32)
-        cast_kernel<__nv_bfloat16, float><<<blocks, threads, 0, stream>>>(
+        mf_launch(cast_kernel<__nv_bfloat16, float>, dim3(blocks), dim3(threads), 0, stream, 
             (const __nv_bfloat16*)in, (float*)out, n);
     else
         return MF_ERR_UNSUPPORTED;
@@ -437,6 +445,7 @@ extern "C" int mf_cast(const void* in, int in_dtype, void* out, int out_dtype, l
 // positions[b] += 1 and seq_end[b] += 1 for live rows.
 // ------------------------------------------------------------------------------------
 __global__ void advance_kernel(int* __restrict__ positions, int* __restrict__ seq_end, int n) {
+    pdl_prologue();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         positions[i] += 1;
@@ -446,6 +455,6 @@ __global__ void advance_kernel(int* __restrict__ positions, int* __restrict__ se
 
 extern "C" int mf_advance_positions(int* positions, int* seq_end, int n, cudaStream_t stream) {
     if (n <= 0) return 0;
-    advance_kernel<<<(n + 127) / 128, 128, 0, stream>>>(positions, seq_end, n);
+    mf_launch(advance_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, positions, seq_end, n);
     return MF_LAUNCH_CHECK();
 }

@@ -105,6 +105,7 @@ __device__ double block_sum_double(double v, double* buf) {
 }
 
 __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleArgs a) {
+    pdl_prologue();
     __shared__ double dbuf[SMP_THREADS];
     __shared__ float fscratch[33];
     __shared__ int ibuf[SMP_THREADS];
@@ -405,7 +406,7 @@ extern "C" int mf_sample(float* logits, long long ld, int rows, int vocab, const
     a.stream_ids = stream_ids; a.out = out; a.temp = temp; a.top_k = top_k; a.top_p = top_p;
     a.repeat = repeat; a.frequency = frequency; a.presence = presence; a.seed = seed;
     a.update_state = update_state;
-    sample_kernel<<<rows, SMP_THREADS, 0, stream>>>(a);
+    mf_launch(sample_kernel, dim3(rows), dim3(SMP_THREADS), 0, stream, a);
     return MF_LAUNCH_CHECK();
 }
 
