@@ -217,14 +217,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+#define DEC_WARPS 8           // warps per CTA; each takes DEC_KEYS keys of the 256-key chunk
+#define DEC_KEYS 32
+
 template <int HD>
-__global__ void __launch_bounds__(128) attention_decode_mma_kernel(AttnArgs a) {
+__global__ void __launch_bounds__(DEC_WARPS * 32, 2) attention_decode_mma_kernel(AttnArgs a) {
     pdl_prologue();
     constexpr int CPR = HD / 8;                       // 16-byte chunks per row
     extern __shared__ __align__(128) uint8_t dec_smem[];
-    __nv_bfloat16* v_s = (__nv_bfloat16*)dec_smem;                      // [4][64][HD], swizzled
-    float* o_s = (float*)(dec_smem + 4 * 64 * HD * 2);                   // [4][16][HD]
-    float* ml_s = o_s + 4 * 16 * HD;                                     // [4][16][2]
+    // values [DEC_WARPS][DEC_KEYS][HD] bf16, swizzled; once every warp is done with its values
+    // the same memory holds the warps' results [DEC_WARPS][16][HD] float32
+    __nv_bfloat16* v_s = (__nv_bfloat16*)dec_smem;
+    float* o_s = (float*)dec_smem;
+    float* ml_s = (float*)(dec_smem + DEC_WARPS * 16 * HD * 4);          // [DEC_WARPS][16][2]
+    float* f_s = ml_s + DEC_WARPS * 16 * 2;                              // [DEC_WARPS][16] merge factors
 
     const int chunk_id = blockIdx.x, hk = blockIdx.y, row = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -245,8 +251,8 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(AttnArgs a) {
         return;
     }
 
-    const int j0 = c_lo + warp * 64;                  // first position of this warp's page
-    const int w_lo = max(lo, j0), w_hi = min(hi, j0 + 64);
+    const int j0 = c_lo + warp * DEC_KEYS;            // first position of this warp's keys
+    const int w_lo = max(lo, j0), w_hi = min(hi, j0 + DEC_KEYS);
     const bool active = w_lo < w_hi;
     float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
     float o[HD / 8][4];
@@ -256,16 +262,23 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(AttnArgs a) {
     if (active) {
         const int p_eff = a.ring > 0 ? j0 % a.ring : j0;
         const int page = a.page_table[(size_t)b * a.table_stride + (p_eff >> 6)];
-        const __nv_bfloat16* kp = (const __nv_bfloat16*)a.k + ((size_t)page * a.n_kv + hk) * MF_PAGE * HD;
-        const __nv_bfloat16* vp = (const __nv_bfloat16*)a.v + ((size_t)page * a.n_kv + hk) * MF_PAGE * HD;
-        __nv_bfloat16* vw = v_s + (size_t)warp * 64 * HD;
+        const size_t tile = (((size_t)page * a.n_kv + hk) * MF_PAGE + (j0 & (MF_PAGE - 1))) * HD;
+        const __nv_bfloat16* kp = (const __nv_bfloat16*)a.k + tile;
+        const __nv_bfloat16* vp = (const __nv_bfloat16*)a.v + tile;
+        __nv_bfloat16* vw = v_s + (size_t)warp * DEC_KEYS * HD;
         // values -> shared memory (asynchronously; the scores are computed meanwhile)
-        for (int i = lane; i < 64 * CPR; i += 32) {
-            const int r = i / CPR, c = i % CPR;
-            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(vw + (r * CPR + (c ^ (r & 7))) * 8);
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(vp + (size_t)i * 8) : "memory");
+        {
+            const uint32_t vw_addr = (uint32_t)__cvta_generic_to_shared(vw);
+#pragma unroll
+            for (int it = 0; it < DEC_KEYS * CPR / 32; ++it) {
+                const int i = it * 32 + lane;
+                const int r = i / CPR, c = i % CPR;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;"
+                             ::"r"(vw_addr + (uint32_t)((r * CPR + (c ^ (r & 7))) * 16)),
+                               "l"(vp + (size_t)i * 8) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
 
         // query fragments: rows g and g+8 of the group (zero beyond the group's heads)
         uint32_t qa[HD / 16][4];
@@ -279,26 +292,33 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(AttnArgs a) {
             qa[2 * s + 1][0] = q0.z; qa[2 * s + 1][1] = q1.z; qa[2 * s + 1][2] = q0.w; qa[2 * s + 1][3] = q1.w;
         }
 
-        // scores S[16 heads][64 keys]
-        float sacc[8][4];
+        // scores S[16 heads][32 keys]: all key loads first (16 independent 16-byte loads a thread)
+        constexpr int NT = DEC_KEYS / 8;
+        float sacc[NT][4];
+        uint4 kv[NT][HD / 32];
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-            sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.0f;
+        for (int nt = 0; nt < NT; ++nt) {
             const __nv_bfloat16* kr = kp + (size_t)(nt * 8 + g) * HD + 8 * t;
 #pragma unroll
+            for (int s = 0; s < HD / 32; ++s) kv[nt][s] = __ldg(reinterpret_cast<const uint4*>(kr + 32 * s));
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.0f;
+#pragma unroll
             for (int s = 0; s < HD / 32; ++s) {
-                const uint4 kv = *reinterpret_cast<const uint4*>(kr + 32 * s);
-                mma_bf16_16816(sacc[nt], qa[2 * s], kv.x, kv.y);
-                mma_bf16_16816(sacc[nt], qa[2 * s + 1], kv.z, kv.w);
+                mma_bf16_16816(sacc[nt], qa[2 * s], kv[nt][s].x, kv[nt][s].y);
+                mma_bf16_16816(sacc[nt], qa[2 * s + 1], kv[nt][s].z, kv[nt][s].w);
             }
         }
-        // scale, mask by position, row maxima
+        // scale (to base 2), mask by position, row maxima
+        const float sl2 = a.scale * 1.4426950408889634f;
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = j0 + nt * 8 + 2 * t + (e & 1);
-                const float sv = (key >= w_lo && key < w_hi) ? sacc[nt][e] * a.scale : -INFINITY;
+                const float sv = (key >= w_lo && key < w_hi) ? sacc[nt][e] * sl2 : -INFINITY;
                 sacc[nt][e] = sv;
                 m_r[e >> 1] = fmaxf(m_r[e >> 1], sv);
             }
@@ -308,13 +328,13 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(AttnArgs a) {
             m_r[r] = fmaxf(m_r[r], __shfl_xor_sync(0xffffffffu, m_r[r], 1));
             m_r[r] = fmaxf(m_r[r], __shfl_xor_sync(0xffffffffu, m_r[r], 2));
         }
-        uint32_t pa[4][4];
+        uint32_t pa[NT / 2][4];
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < NT; ++nt) {
             float p[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                p[e] = expf(sacc[nt][e] - m_r[e >> 1]);
+                p[e] = exp2f(sacc[nt][e] - m_r[e >> 1]);
                 l_r[e >> 1] += p[e];
             }
             pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
@@ -328,10 +348,10 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(AttnArgs a) {
 
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncwarp();
-        // O[16 heads][HD] = P[16][64] V[64][HD]
+        // O[16 heads][HD] = P[16][32] V[32][HD]
         const uint32_t vbase = (uint32_t)__cvta_generic_to_shared(vw);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
+        for (int ks = 0; ks < DEC_KEYS / 16; ++ks) {
             const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
 #pragma unroll
             for (int np = 0; np < HD / 16; ++np) {
@@ -345,10 +365,30 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(AttnArgs a) {
             }
         }
     }
-    // hand the warp's result over: rows g and g+8
+    // maxima (base-2 units) and sums of every warp, then the factors that bring them to the
+    // chunk's maximum
     if (t == 0) {
         ml_s[(warp * 16 + g) * 2 + 0] = m_r[0]; ml_s[(warp * 16 + g) * 2 + 1] = l_r[0];
         ml_s[(warp * 16 + g + 8) * 2 + 0] = m_r[1]; ml_s[(warp * 16 + g + 8) * 2 + 1] = l_r[1];
+    }
+    __syncthreads();                                  // also: every warp is done reading its values
+    if (tid < 16) {
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) m = fmaxf(m, ml_s[(w * 16 + tid) * 2]);
+        float l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < DEC_WARPS; ++w) {
+            const float mw = ml_s[(w * 16 + tid) * 2];
+            const float f = mw > -INFINITY ? exp2f(mw - m) : 0.0f;
+            f_s[w * 16 + tid] = f;
+            l += ml_s[(w * 16 + tid) * 2 + 1] * f;
+        }
+        if (tid < G) {
+            float* p = part0 + (size_t)tid * a.n_chunks * part_stride;
+            p[0] = m * 0.6931471805599453f;           // back to natural-log units for the merge
+            p[1] = l;
+        }
     }
     float* ow = o_s + (size_t)warp * 16 * HD;
 #pragma unroll
@@ -357,30 +397,20 @@ __global__ void __launch_bounds__(128) attention_decode_mma_kernel(AttnArgs a) {
         *reinterpret_cast<float2*>(ow + (size_t)(g + 8) * HD + nt * 8 + 2 * t) = make_float2(o[nt][2], o[nt][3]);
     }
     __syncthreads();
-    for (int idx = tid; idx < G * HD; idx += 128) {
+    for (int idx = tid; idx < G * HD; idx += DEC_WARPS * 32) {
         const int r = idx / HD, d = idx - r * HD;
-        float m = -INFINITY;
+        float acc = 0.0f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) m = fmaxf(m, ml_s[(w * 16 + r) * 2]);
-        float l = 0.0f, acc = 0.0f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float mw = ml_s[(w * 16 + r) * 2];
-            if (mw > -INFINITY) {
-                const float f = expf(mw - m);
-                l += ml_s[(w * 16 + r) * 2 + 1] * f;
-                acc += o_s[((size_t)w * 16 + r) * HD + d] * f;
-            }
-        }
-        float* p = part0 + (size_t)r * a.n_chunks * part_stride;
-        p[2 + d] = acc;
-        if (d == 0) { p[0] = m; p[1] = l; }
+        for (int w = 0; w < DEC_WARPS; ++w) acc = fmaf(o_s[((size_t)w * 16 + r) * HD + d], f_s[w * 16 + r], acc);
+        part0[(size_t)r * a.n_chunks * part_stride + 2 + d] = acc;
     }
 }
 
 template <int HD>
 static int launch_decode_mma(const AttnArgs& a, cudaStream_t stream) {
-    constexpr int smem = 4 * 64 * HD * 2 + 4 * 16 * HD * 4 + 4 * 16 * 2 * 4;
+    constexpr int smem = DEC_WARPS * 16 * HD * 4 + DEC_WARPS * 16 * 3 * 4;
+    static_assert(DEC_WARPS * DEC_KEYS * HD * 2 <= DEC_WARPS * 16 * HD * 4, "values fit the staging area");
+    static_assert(DEC_WARPS * DEC_KEYS == 256, "a CTA covers one 256-key chunk");
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD>,
@@ -389,7 +419,7 @@ static int launch_decode_mma(const AttnArgs& a, cudaStream_t stream) {
         configured = true;
     }
     dim3 grid(a.n_chunks, a.n_kv, a.rows);
-    mf_launch(attention_decode_mma_kernel<HD>, dim3(grid), dim3(128), smem, stream, a);
+    mf_launch(attention_decode_mma_kernel<HD>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, a);
     return MF_LAUNCH_CHECK();
 }
 

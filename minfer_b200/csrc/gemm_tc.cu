@@ -140,7 +140,7 @@ __host__ __device__ constexpr uint32_t umma_idesc(int nt) {
 template <int NT> struct TmemCols { static constexpr int value = NT < 32 ? 32 : NT; };
 
 template <int NT, int STAGES>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(128)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                const GemmArgs a) {
     constexpr int B_BYTES = NT * TILE_K * 2;
@@ -410,9 +410,14 @@ extern "C" int mf_gemm_tc_plan(int M, int N, int K, int epi, int* token_tile, in
     const int tiles = ((M + nt - 1) / nt) * ((N + TILE_N - 1) / TILE_N);
     const int kblocks = (K + TILE_K - 1) / TILE_K;
     int s = 1;
-    if (epi != EPI_SWIGLU && tiles < 100 && kblocks >= 8) {
-        s = 148 / tiles;                               // at most one wave of 148 CTAs
-        if (s > kblocks / 4) s = kblocks / 4;          // at least 4 k-blocks per split
+    if (epi != EPI_SWIGLU && tiles < 200 && kblocks >= 8) {
+        // up to two CTAs per SM (the small-token kernels are sized for that), each with at
+        // least 4 k-blocks; the partial sums (written and read once) stay under half of the
+        // weight bytes: splits * M * N * 8 <= N * K  =>  splits <= K / (8 M)
+        const int slots = nt <= 64 ? 296 : 148;
+        s = slots / tiles;
+        if (s > kblocks / 4) s = kblocks / 4;
+        if (s > K / (8 * M)) s = K / (8 * M);
         if (s > 16) s = 16;
         if (s < 1) s = 1;
     }
@@ -460,9 +465,11 @@ extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long
     a.epi = splits > 1 ? EPI_PARTIAL : epi;
     int e;
     switch (nt) {
-        case 16: e = launch<16, 8>(mw, mx, a, splits, stream); break;
-        case 32: e = launch<32, 8>(mw, mx, a, splits, stream); break;
-        case 64: e = launch<64, 8>(mw, mx, a, splits, stream); break;
+        // few tokens: stages sized so that two CTAs share an SM (one's epilogue and prologue
+        // overlap the other's stream of weight tiles)
+        case 16: e = launch<16, 6>(mw, mx, a, splits, stream); break;
+        case 32: e = launch<32, 5>(mw, mx, a, splits, stream); break;
+        case 64: e = launch<64, 4>(mw, mx, a, splits, stream); break;
         case 128: e = launch<128, 6>(mw, mx, a, splits, stream); break;
         default: e = launch<256, 4>(mw, mx, a, splits, stream); break;
     }
