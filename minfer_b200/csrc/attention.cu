@@ -303,13 +303,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 2) attention_decode_mma_kernel
             for (int s = 0; s < HD / 32; ++s) kv[nt][s] = __ldg(reinterpret_cast<const uint4*>(kr + 32 * s));
         }
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.0f;
+        for (int nt = 0; nt < NT; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.0f;
+        // k-step outermost: consecutive MMAs go to different accumulators
 #pragma unroll
-            for (int s = 0; s < HD / 32; ++s) {
-                mma_bf16_16816(sacc[nt], qa[2 * s], kv[nt][s].x, kv[nt][s].y);
-                mma_bf16_16816(sacc[nt], qa[2 * s + 1], kv[nt][s].z, kv[nt][s].w);
-            }
+        for (int s = 0; s < HD / 32; ++s) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma_bf16_16816(sacc[nt], qa[2 * s], kv[nt][s].x, kv[nt][s].y);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma_bf16_16816(sacc[nt], qa[2 * s + 1], kv[nt][s].z, kv[nt][s].w);
         }
         // scale (to base 2), mask by position, row maxima
         const float sl2 = a.scale * 1.4426950408889634f;

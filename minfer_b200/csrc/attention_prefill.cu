@@ -69,12 +69,11 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* tile, const __nv_bfloat
 }
 
 template <int HD>
-__global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_mma_kernel(PrefillArgs a) {
+__global__ void __launch_bounds__(PF_WARPS * 32, 3) attention_prefill_mma_kernel(PrefillArgs a) {
     pdl_prologue();
     constexpr int CPR = HD / 8;
     extern __shared__ __align__(128) uint8_t pf_smem[];
-    __nv_bfloat16* q_s = (__nv_bfloat16*)pf_smem;                 // [64][HD]
-    __nv_bfloat16* k_s = q_s + 64 * HD;                           // [2][64][HD]
+    __nv_bfloat16* k_s = (__nv_bfloat16*)pf_smem;                 // [2][64][HD]
     __nv_bfloat16* v_s = k_s + 2 * 64 * HD;                       // [2][64][HD]
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -95,7 +94,6 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_mma_kernel(Pr
     const int kt_begin = a.window > 0 ? max(0, q0 - a.window + 1) / PF_KEYS : 0;
     const int kt_end = q_last / PF_KEYS;                          // inclusive
 
-    load_tile<HD>(q_s, qb, q_stride, len - q0, tid);
     load_tile<HD>(k_s, kb + (long long)kt_begin * PF_KEYS * kv_stride, kv_stride,
                   len - kt_begin * PF_KEYS, tid);
     load_tile<HD>(v_s, vb + (long long)kt_begin * PF_KEYS * kv_stride, kv_stride,
@@ -106,8 +104,21 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_mma_kernel(Pr
     float o[HD / 8][4];
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
-    uint32_t qa[HD / 16][4];
     const int row_g = q0 + warp * 16 + g;                         // this thread's rows: row_g, row_g + 8
+    // query fragments straight from global memory (once per CTA; rows beyond the end are zero)
+    uint32_t qa[HD / 16][4];
+    {
+        const __nv_bfloat16* q_lo = qb + (long long)(warp * 16 + g) * q_stride + 2 * t;
+        const __nv_bfloat16* q_hi = q_lo + 8 * q_stride;
+        const bool lo_ok = row_g < len, hi_ok = row_g + 8 < len;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            qa[ks][0] = lo_ok ? *reinterpret_cast<const uint32_t*>(q_lo + 16 * ks) : 0u;
+            qa[ks][1] = hi_ok ? *reinterpret_cast<const uint32_t*>(q_hi + 16 * ks) : 0u;
+            qa[ks][2] = lo_ok ? *reinterpret_cast<const uint32_t*>(q_lo + 16 * ks + 8) : 0u;
+            qa[ks][3] = hi_ok ? *reinterpret_cast<const uint32_t*>(q_hi + 16 * ks + 8) : 0u;
+        }
+    }
 
     for (int kt = kt_begin; kt <= kt_end; ++kt) {
         const int buf = (kt - kt_begin) & 1;
@@ -123,28 +134,19 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_mma_kernel(Pr
         }
         __syncthreads();
 
-        if (kt == kt_begin) {                                     // query fragments, once
-            const uint32_t qs = (uint32_t)__cvta_generic_to_shared(q_s);
-            const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-#pragma unroll
-            for (int ks = 0; ks < HD / 16; ++ks) {
-                const int c = 2 * ks + (lane >> 4);
-                ldsm_x4(qs + (uint32_t)((r * CPR + (c ^ (r & 7))) * 16), qa[ks][0], qa[ks][1],
-                        qa[ks][2], qa[ks][3]);
-            }
-        }
-
         // S[16][64] = Q K^T
         float s[8][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
         const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(k_s + buf * 64 * HD);
+        // k-step outermost: consecutive MMAs go to different accumulators, so none waits for
+        // the one before it
 #pragma unroll
-        for (int np = 0; np < 4; ++np) {                          // pairs of 8-key tiles
-            const int key = np * 16 + (lane >> 4) * 8 + (lane & 7);
+        for (int ks = 0; ks < HD / 16; ++ks) {
+            const int c = 2 * ks + ((lane >> 3) & 1);
 #pragma unroll
-            for (int ks = 0; ks < HD / 16; ++ks) {
-                const int c = 2 * ks + ((lane >> 3) & 1);
+            for (int np = 0; np < 4; ++np) {                      // pairs of 8-key tiles
+                const int key = np * 16 + (lane >> 4) * 8 + (lane & 7);
                 uint32_t b0, b1, b2, b3;
                 ldsm_x4(ks_base + (uint32_t)((key * CPR + (c ^ (key & 7))) * 16), b0, b1, b2, b3);
                 mma16816(s[2 * np], qa[ks], b0, b1);
@@ -243,7 +245,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_mma_kernel(Pr
 
 template <int HD>
 static int launch_prefill(const PrefillArgs& a, int n_seqs, int max_len, cudaStream_t stream) {
-    constexpr int smem = 5 * 64 * HD * 2;
+    constexpr int smem = 4 * 64 * HD * 2;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_mma_kernel<HD>,

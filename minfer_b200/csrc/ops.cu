@@ -68,9 +68,60 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int i = threadIdx.x; i < width; i += blockDim.x) yr[i] = from_f32<TO>(xr[i] * scale * w[i]);
 }
 
+// the same with float4 accesses and the row kept in registers (one pass over memory), for
+// widths that are multiples of 4 up to 16384
+template <typename TO>
+__global__ void __launch_bounds__(1024)
+rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                   const int* __restrict__ rows, TO* __restrict__ y, int width, float eps) {
+    pdl_prologue();
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const int nv = width >> 2;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * width);
+    float4 row[4];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            const float4 v = xr[i];
+            row[j] = v;
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    TO* yr = y + (size_t)r * width;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) {
+            const float4 g = reinterpret_cast<const float4*>(w)[i];
+            const float4 v = row[j];
+            yr[4 * i + 0] = from_f32<TO>(v.x * scale * g.x);
+            yr[4 * i + 1] = from_f32<TO>(v.y * scale * g.y);
+            yr[4 * i + 2] = from_f32<TO>(v.z * scale * g.z);
+            yr[4 * i + 3] = from_f32<TO>(v.w * scale * g.w);
+        }
+    }
+}
+
 extern "C" int mf_rmsnorm(const float* x, const float* w, const int* rows, void* y, int out_dtype,
                           int n_rows, int width, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (width % 4 == 0 && width <= 16384 && (out_dtype == MF_DTYPE_F32 || out_dtype == MF_DTYPE_BF16)) {
+        int threads = 32;
+        while (threads < 1024 && threads * 4 < width) threads <<= 1;
+        if (out_dtype == MF_DTYPE_F32)
+            mf_launch(rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, w, rows,
+                      (float*)y, width, eps);
+        else
+            mf_launch(rmsnorm_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, w,
+                      rows, (__nv_bfloat16*)y, width, eps);
+        return MF_LAUNCH_CHECK();
+    }
     // the block size is a function of the width only, so a row's sum never depends on the batch
     int threads = 32;
     while (threads < 512 && threads * 4 < width) threads <<= 1;
@@ -280,6 +331,16 @@ __global__ void rope_kvstore_kernel(const float* __restrict__ qkv, int n_partial
         }
     }
 
+    // the token's rotation (cos, sin) per pair, once per block: every head uses the same
+    __shared__ float2 cs_table[128];
+    if (inv_freq != nullptr) {
+        for (int i = threadIdx.x; i < rhalf; i += blockDim.x) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            cs_table[i] = make_float2(cs, sn);
+        }
+    }
+    __syncthreads();
     // blockIdx.y spreads a token's pairs over several blocks when there are few tokens
     for (int s = blockIdx.y * blockDim.x + threadIdx.x; s < n_slots; s += gridDim.y * blockDim.x) {
         const int head = s / half;      // 0..n_heads-1: q, then k heads, then v heads
@@ -291,8 +352,7 @@ __global__ void rope_kvstore_kernel(const float* __restrict__ qkv, int n_partial
         if (!is_v && inv_freq != nullptr && i < rhalf) {
             if (style == 0) { d0 = i; d1 = i + rhalf; } else { d0 = 2 * i; d1 = 2 * i + 1; }
             const float a = value(hbase + d0), c = value(hbase + d1);
-            float sn, cs;
-            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float cs = cs_table[i].x, sn = cs_table[i].y;
             x0 = a * cs - c * sn;
             x1 = a * sn + c * cs;
         } else {
@@ -329,7 +389,7 @@ extern "C" int mf_rope_kvstore(const float* qkv, int n_partials, const float* bi
                                int hd, int rotary_dim, int style, int dtype, unsigned* status,
                                cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (hd % 2 != 0 || rotary_dim % 2 != 0 || rotary_dim > hd || rotary_dim < 0)
+    if (hd % 2 != 0 || rotary_dim % 2 != 0 || rotary_dim > hd || rotary_dim < 0 || rotary_dim > 256)
         return MF_ERR_UNSUPPORTED;
     if (ring % MF_PAGE != 0) return MF_ERR_ARGUMENT;
     const int n_slots = (n_heads + 2 * n_kv) * (hd / 2);

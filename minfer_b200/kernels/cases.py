@@ -1,0 +1,168 @@
+"""Small, named workloads of single kernels and of short model steps, for timing and for
+profilers:
+
+    python -m minfer_b200.kernels.cases LIST
+    python -m minfer_b200.kernels.cases <case> [--reps N]
+
+Each case builds inputs larger than L2 but at most a few GB, runs its kernel a few times
+and prints the mean CUDA-event time with the bytes or flops it stands for.  The sizes are
+those of the Qwen2.5-7B shape (hidden 3584, 28 heads / 4 KV heads of 128, intermediate
+18944).
+"""
+from __future__ import annotations
+
+import argparse
+import math
+import sys
+
+import torch
+
+from . import api as K
+
+NE, NH, NK, HD, NF, VOCAB = 3584, 28, 4, 128, 18944, 152064
+
+
+def _time(fn, reps):
+    fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps * 1e3      # microseconds
+
+
+def _gemm(m, n, k, epi, reps):
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    x = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+    n_w = max(2, min(8, int(1.2e9 // (n * k * 2))))         # rotate weights: no L2 reuse
+    ws = [(torch.randn(n, k, device="cuda") * 0.05).bfloat16() for _ in range(n_w)]
+    out = (torch.zeros(m, n // 2, dtype=torch.bfloat16, device="cuda") if epi == K.EPI_SWIGLU
+           else torch.zeros(m, n, device="cuda"))
+    state = {"i": 0}
+
+    def run():
+        K.gemm_tc(x, ws[state["i"] % n_w], None, out, epi, st)
+        state["i"] += 1
+    us = _time(run, reps)
+    print(f"gemm_tc m={m} n={n} k={k} epi={epi} plan={K.gemm_tc_plan(m, n, k, epi)}: {us:.1f} us, "
+          f"{2.0 * m * n * k / us / 1e6:.1f} TFLOP/s, {n * k * 2 / us / 1e3:.1f} GB/s of weights")
+
+
+def gemm_decode(reps):
+    """The gate|up projection with fused SwiGLU for 8 tokens: streams 271.6 MB of weights."""
+    _gemm(8, 2 * NF, NE, K.EPI_SWIGLU, reps)
+
+
+def gemm_decode_split(reps):
+    """The down projection for 8 tokens (split along K, partial sums reduced)."""
+    _gemm(8, NE, NF, K.EPI_ACCUM, reps)
+
+
+def gemm_prefill(reps):
+    """The gate|up projection with fused SwiGLU for 2,048 tokens: 556 GFLOP."""
+    _gemm(2048, 2 * NF, NE, K.EPI_SWIGLU, reps)
+
+
+def gemm_prefill_down(reps):
+    """The down projection for 2,048 tokens, accumulated into the residual: 278 GFLOP."""
+    _gemm(2048, NE, NF, K.EPI_ACCUM, reps)
+
+
+def attention_decode(reps, batch=64, ctx=2048):
+    """Decode attention of 64 sequences at 2,048 cached positions: reads 268 MB of K and V."""
+    pos = torch.full((batch,), ctx, dtype=torch.int32, device="cuda")
+    rows = torch.arange(batch, dtype=torch.int32, device="cuda")
+    q = torch.randn(batch, NH, HD, device="cuda").bfloat16()
+    pages_per = (ctx + 64) // 64
+    n_pages = batch * pages_per
+    kc = torch.randn(n_pages, NK, 64, HD, device="cuda").bfloat16()
+    vc = torch.randn(n_pages, NK, 64, HD, device="cuda").bfloat16()
+    table = torch.arange(n_pages, dtype=torch.int32, device="cuda").reshape(batch, pages_per)
+    out = torch.empty(batch, NH * HD, dtype=torch.bfloat16, device="cuda")
+    n_chunks = (ctx + 256) // 256
+    partial = torch.empty(batch * NH * n_chunks * (HD + 2), device="cuda")
+    us = _time(lambda: K.attention_paged(q, kc, vc, rows, pos, table, pages_per, 0, out, partial,
+                                         NH, NK, HD, 0, 256, n_chunks, 1 / math.sqrt(HD)), reps)
+    nbytes = batch * (ctx + 1) * NK * HD * 2 * 2
+    print(f"attention decode batch={batch} ctx={ctx}: {us:.1f} us (kernel + merge), "
+          f"{nbytes / us / 1e3:.1f} GB/s of cache")
+
+
+def attention_decode_b8(reps):
+    """Decode attention of 8 sequences at 2,048 cached positions (latency-bound)."""
+    attention_decode(reps, batch=8)
+
+
+def attention_prefill(reps, tokens=2048):
+    """Causal attention of one 2,048-token prompt, 28 heads: 30 GFLOP."""
+    q = torch.randn(tokens, NH, HD, device="cuda").bfloat16()
+    k = torch.randn(tokens, NK, HD, device="cuda").bfloat16()
+    v = torch.randn(tokens, NK, HD, device="cuda").bfloat16()
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device="cuda")
+    out = torch.empty(tokens, NH * HD, dtype=torch.bfloat16, device="cuda")
+    us = _time(lambda: K.attention_prefill(q, k, v, cu, out, 1, tokens, NH, NK, HD, 0,
+                                           1 / math.sqrt(HD)), reps)
+    flops = NH * 4 * HD * tokens * (tokens + 1) / 2
+    print(f"attention prefill tokens={tokens}: {us:.1f} us, {flops / us / 1e6:.1f} TFLOP/s (causal)")
+
+
+def _engine(layers):
+    from ..engine.step import Engine
+    from ..model import Model
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "vocab_size": VOCAB, "hidden_size": NE,
+           "num_hidden_layers": layers, "num_attention_heads": NH, "num_key_value_heads": NK,
+           "intermediate_size": NF, "rope_theta": 1e6, "rms_norm_eps": 1e-6,
+           "tie_word_embeddings": False, "max_position_embeddings": 32768}
+    model = Model.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0", make_on="device")
+    return Engine(model, max_tokens=8 * 4096, max_seqs=8), cfg
+
+
+def step_prefill(reps, layers=4):
+    """One 2,048-token prompt through 4 layers of the 7B shape plus the head."""
+    eng, cfg = _engine(layers)
+    ids = torch.randint(0, VOCAB, (2048,)).tolist()
+
+    def run():
+        s = eng.acquire()
+        eng.step([s], [ids])
+        eng.release(s)
+    us = _time(run, reps)
+    print(f"prefill step, {layers} layers, 2048 tokens: {us / 1e3:.2f} ms")
+
+
+def step_decode(reps, layers=4):
+    """Decode steps of 8 sequences at 2,048 positions through 4 layers plus the head."""
+    eng, cfg = _engine(layers)
+    slots = [eng.acquire() for _ in range(8)]
+    eng.step(slots, [torch.randint(0, VOCAB, (2048,)).tolist() for _ in range(8)])
+    tokens = torch.randint(0, VOCAB, (8,), dtype=torch.int32, device="cuda")
+    us = _time(lambda: eng.decode_on_device(slots, tokens), reps)
+    print(f"decode step, {layers} layers, batch 8: {us:.1f} us")
+
+
+CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_prefill, gemm_prefill_down,
+                                 attention_decode, attention_decode_b8, attention_prefill,
+                                 step_prefill, step_decode)}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="python -m minfer_b200.kernels.cases")
+    ap.add_argument("case", help="a case name, or LIST")
+    ap.add_argument("--reps", type=int, default=3)
+    args = ap.parse_args(argv)
+    if args.case == "LIST":
+        for name, fn in CASES.items():
+            print(f"{name:22s} {fn.__doc__.strip()}")
+        return 0
+    if args.case not in CASES:
+        print(f"unknown case {args.case!r}; try LIST", file=sys.stderr)
+        return 2
+    CASES[args.case](args.reps)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
