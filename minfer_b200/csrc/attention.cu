@@ -227,9 +227,11 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 2) attention_decode_mma_kernel
     extern __shared__ __align__(128) uint8_t dec_smem[];
     // values [DEC_WARPS][DEC_KEYS][HD] bf16, swizzled; once every warp is done with its values
     // the same memory holds the warps' results [DEC_WARPS][16][HD] float32
+    // (rows padded by 8 floats: a warp's float2 stores of 8 rows then spread over all banks)
+    constexpr int OS = HD + 8;
     __nv_bfloat16* v_s = (__nv_bfloat16*)dec_smem;
     float* o_s = (float*)dec_smem;
-    float* ml_s = (float*)(dec_smem + DEC_WARPS * 16 * HD * 4);          // [DEC_WARPS][16][2]
+    float* ml_s = (float*)(dec_smem + DEC_WARPS * 16 * OS * 4);          // [DEC_WARPS][16][2]
     float* f_s = ml_s + DEC_WARPS * 16 * 2;                              // [DEC_WARPS][16] merge factors
 
     const int chunk_id = blockIdx.x, hk = blockIdx.y, row = blockIdx.z;
@@ -391,26 +393,26 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 2) attention_decode_mma_kernel
             p[1] = l;
         }
     }
-    float* ow = o_s + (size_t)warp * 16 * HD;
+    float* ow = o_s + (size_t)warp * 16 * OS;
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt) {
-        *reinterpret_cast<float2*>(ow + (size_t)g * HD + nt * 8 + 2 * t) = make_float2(o[nt][0], o[nt][1]);
-        *reinterpret_cast<float2*>(ow + (size_t)(g + 8) * HD + nt * 8 + 2 * t) = make_float2(o[nt][2], o[nt][3]);
+        *reinterpret_cast<float2*>(ow + (size_t)g * OS + nt * 8 + 2 * t) = make_float2(o[nt][0], o[nt][1]);
+        *reinterpret_cast<float2*>(ow + (size_t)(g + 8) * OS + nt * 8 + 2 * t) = make_float2(o[nt][2], o[nt][3]);
     }
     __syncthreads();
     for (int idx = tid; idx < G * HD; idx += DEC_WARPS * 32) {
         const int r = idx / HD, d = idx - r * HD;
         float acc = 0.0f;
 #pragma unroll
-        for (int w = 0; w < DEC_WARPS; ++w) acc = fmaf(o_s[((size_t)w * 16 + r) * HD + d], f_s[w * 16 + r], acc);
+        for (int w = 0; w < DEC_WARPS; ++w) acc = fmaf(o_s[((size_t)w * 16 + r) * OS + d], f_s[w * 16 + r], acc);
         part0[(size_t)r * a.n_chunks * part_stride + 2 + d] = acc;
     }
 }
 
 template <int HD>
 static int launch_decode_mma(const AttnArgs& a, cudaStream_t stream) {
-    constexpr int smem = DEC_WARPS * 16 * HD * 4 + DEC_WARPS * 16 * 3 * 4;
-    static_assert(DEC_WARPS * DEC_KEYS * HD * 2 <= DEC_WARPS * 16 * HD * 4, "values fit the staging area");
+    constexpr int smem = DEC_WARPS * 16 * (HD + 8) * 4 + DEC_WARPS * 16 * 3 * 4;
+    static_assert(DEC_WARPS * DEC_KEYS * HD * 2 <= DEC_WARPS * 16 * (HD + 8) * 4, "values fit the staging area");
     static_assert(DEC_WARPS * DEC_KEYS == 256, "a CTA covers one 256-key chunk");
     static bool configured = false;
     if (!configured) {

@@ -22,16 +22,30 @@ from . import api as K
 NE, NH, NK, HD, NF, VOCAB = 3584, 28, 4, 128, 18944, 152064
 
 
-def _time(fn, reps):
-    fn()
+def _time(fn, reps, graph=True):
+    """Mean device time of one call in microseconds.  With ``graph`` the calls are captured
+    into one CUDA graph and replayed, so that host launch overhead is not in the number."""
+    for _ in range(3):
+        fn()
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(reps):
-        fn()
-    b.record()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        a.record()
+        g.replay()
+        b.record()
+    else:
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
     torch.cuda.synchronize()
-    return a.elapsed_time(b) / reps * 1e3      # microseconds
+    return a.elapsed_time(b) / reps * 1e3
 
 
 def _gemm(m, n, k, epi, reps):
@@ -129,7 +143,7 @@ def step_prefill(reps, layers=4):
         s = eng.acquire()
         eng.step([s], [ids])
         eng.release(s)
-    us = _time(run, reps)
+    us = _time(run, reps, graph=False)
     print(f"prefill step, {layers} layers, 2048 tokens: {us / 1e3:.2f} ms")
 
 
@@ -139,7 +153,7 @@ def step_decode(reps, layers=4):
     slots = [eng.acquire() for _ in range(8)]
     eng.step(slots, [torch.randint(0, VOCAB, (2048,)).tolist() for _ in range(8)])
     tokens = torch.randint(0, VOCAB, (8,), dtype=torch.int32, device="cuda")
-    us = _time(lambda: eng.decode_on_device(slots, tokens), reps)
+    us = _time(lambda: eng.decode_on_device(slots, tokens), reps, graph=False)
     print(f"decode step, {layers} layers, batch 8: {us:.1f} us")
 
 
@@ -151,7 +165,7 @@ CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_prefill, g
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m minfer_b200.kernels.cases")
     ap.add_argument("case", help="a case name, or LIST")
-    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--reps", type=int, default=10)
     args = ap.parse_args(argv)
     if args.case == "LIST":
         for name, fn in CASES.items():
