@@ -381,6 +381,133 @@ __global__ void rope_kvstore_kernel(const float* __restrict__ qkv, int n_partial
     }
 }
 
+// The common case in wide accesses: pairs (i, i + hd/2), the whole head rotated, head sizes
+// that are multiples of 8.  A thread takes 4 neighbouring pairs of a q or k head (two float4
+// loads per split, two 4-element stores per destination) or 8 elements of a v head.
+template <typename T> struct Pack4;
+template <> struct Pack4<float> {
+    static __device__ __forceinline__ void store(float* p, float a, float b, float c, float d) {
+        *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+    }
+};
+template <> struct Pack4<__nv_bfloat16> {
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b, float c, float d) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 v;
+        v.x = *reinterpret_cast<unsigned*>(&lo);
+        v.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(p) = v;
+    }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+rope_kvstore_vec_kernel(const float* __restrict__ qkv, int n_partials, int n_tokens,
+                        const float* __restrict__ bias, const int* __restrict__ positions,
+                        const int* __restrict__ token_row, const int* __restrict__ seq_end,
+                        const float* __restrict__ inv_freq, T* __restrict__ q_out,
+                        T* __restrict__ k_out, T* __restrict__ v_out, T* __restrict__ k_cache,
+                        T* __restrict__ v_cache, const int* __restrict__ page_table,
+                        int table_stride, int ring, int n_heads, int n_kv, int hd,
+                        unsigned* __restrict__ status) {
+    pdl_prologue();
+    __shared__ float2 cs_table[128];
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int b = token_row[t];
+    const int half = hd >> 1;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        cs_table[i] = make_float2(cs, sn);
+    }
+    const size_t in_width = (size_t)(n_heads + 2 * n_kv) * hd;
+    const float* in = qkv + (size_t)t * in_width;
+    const size_t plane = (size_t)n_tokens * in_width;
+    auto load4 = [&](int col) -> float4 {
+        float4 v = *reinterpret_cast<const float4*>(in + col);
+        for (int sp = 1; sp < n_partials; ++sp) {
+            const float4 p = *reinterpret_cast<const float4*>(in + sp * plane + col);
+            v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+        }
+        if (bias != nullptr) {
+            const float4 bb = *reinterpret_cast<const float4*>(bias + col);
+            v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
+        }
+        return v;
+    };
+    long long cache_row = -1;
+    if (k_cache != nullptr) {
+        bool keep = true;
+        int p_eff = pos;
+        if (ring > 0) {
+            keep = pos >= seq_end[b] - ring;
+            p_eff = pos % ring;
+        }
+        if (keep) {
+            const int page = page_table[(size_t)b * table_stride + (p_eff >> 6)];
+            if (page < 0) {
+                if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(status, MF_STATUS_BAD_POSITION);
+            } else {
+                cache_row = ((long long)page * n_kv * MF_PAGE + (pos & (MF_PAGE - 1))) * hd;
+            }
+        }
+    }
+    __syncthreads();
+    const int upr = half >> 2;                         // units per rotated head
+    const int n_rot = (n_heads + n_kv) * upr;
+    const int upv = hd >> 3;                           // units per value head
+    const int n_units = n_rot + n_kv * upv;
+    for (int u = blockIdx.y * blockDim.x + threadIdx.x; u < n_units; u += gridDim.y * blockDim.x) {
+        if (u < n_rot) {
+            const int head = u / upr;
+            const int i0 = (u - head * upr) << 2;
+            const float4 a = load4(head * hd + i0), c = load4(head * hd + half + i0);
+            const float av[4] = {a.x, a.y, a.z, a.w}, cv[4] = {c.x, c.y, c.z, c.w};
+            float lo[4], hi[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float cs = cs_table[i0 + j].x, sn = cs_table[i0 + j].y;
+                lo[j] = av[j] * cs - cv[j] * sn;
+                hi[j] = av[j] * sn + cv[j] * cs;
+            }
+            if (head < n_heads) {
+                T* o = q_out + ((size_t)t * n_heads + head) * hd + i0;
+                Pack4<T>::store(o, lo[0], lo[1], lo[2], lo[3]);
+                Pack4<T>::store(o + half, hi[0], hi[1], hi[2], hi[3]);
+            } else {
+                const int hk = head - n_heads;
+                if (k_out != nullptr) {
+                    T* o = k_out + ((size_t)t * n_kv + hk) * hd + i0;
+                    Pack4<T>::store(o, lo[0], lo[1], lo[2], lo[3]);
+                    Pack4<T>::store(o + half, hi[0], hi[1], hi[2], hi[3]);
+                }
+                if (cache_row >= 0) {
+                    T* o = k_cache + cache_row + (long long)hk * MF_PAGE * hd + i0;
+                    Pack4<T>::store(o, lo[0], lo[1], lo[2], lo[3]);
+                    Pack4<T>::store(o + half, hi[0], hi[1], hi[2], hi[3]);
+                }
+            }
+        } else {
+            const int idx = u - n_rot;
+            const int hk = idx / upv;
+            const int e0 = (idx - hk * upv) << 3;
+            const int col = (n_heads + n_kv + hk) * hd + e0;
+            const float4 a = load4(col), c = load4(col + 4);
+            if (v_out != nullptr) {
+                T* o = v_out + ((size_t)t * n_kv + hk) * hd + e0;
+                Pack4<T>::store(o, a.x, a.y, a.z, a.w);
+                Pack4<T>::store(o + 4, c.x, c.y, c.z, c.w);
+            }
+            if (cache_row >= 0) {
+                T* o = v_cache + cache_row + (long long)hk * MF_PAGE * hd + e0;
+                Pack4<T>::store(o, a.x, a.y, a.z, a.w);
+                Pack4<T>::store(o + 4, c.x, c.y, c.z, c.w);
+            }
+        }
+    }
+}
+
 extern "C" int mf_rope_kvstore(const float* qkv, int n_partials, const float* bias,
                                const int* positions, const int* token_row,
                                const int* seq_end, const float* inv_freq, void* q_out, void* k_out,
@@ -400,6 +527,27 @@ extern "C" int mf_rope_kvstore(const float* qkv, int n_partials, const float* bi
     if (gy > gy_max) gy = gy_max;
     if (gy < 1) gy = 1;
     const dim3 grid(n_tokens, gy);
+    if (inv_freq != nullptr && style == 0 && rotary_dim == hd && hd % 8 == 0 &&
+        (dtype == MF_DTYPE_F32 || dtype == MF_DTYPE_BF16)) {
+        const int n_units = (n_heads + n_kv) * (hd / 8) + n_kv * (hd / 8);
+        int vy = (592 + n_tokens - 1) / n_tokens;
+        const int vy_max = (n_units + threads - 1) / threads;
+        if (vy > vy_max) vy = vy_max;
+        if (vy < 1) vy = 1;
+        const dim3 vgrid(n_tokens, vy);
+        if (dtype == MF_DTYPE_F32)
+            mf_launch(rope_kvstore_vec_kernel<float>, vgrid, dim3(threads), 0, stream, qkv, n_partials,
+                      n_tokens, bias, positions, token_row, seq_end, inv_freq, (float*)q_out,
+                      (float*)k_out, (float*)v_out, (float*)k_cache, (float*)v_cache, page_table,
+                      table_stride, ring, n_heads, n_kv, hd, status);
+        else
+            mf_launch(rope_kvstore_vec_kernel<__nv_bfloat16>, vgrid, dim3(threads), 0, stream, qkv,
+                      n_partials, n_tokens, bias, positions, token_row, seq_end, inv_freq,
+                      (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out,
+                      (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_table, table_stride,
+                      ring, n_heads, n_kv, hd, status);
+        return MF_LAUNCH_CHECK();
+    }
     if (dtype == MF_DTYPE_F32)
         mf_launch(rope_kvstore_kernel<float>, dim3(grid), dim3(threads), 0, stream, 
             qkv, n_partials, n_tokens, bias, positions, token_row, seq_end, inv_freq, (float*)q_out, (float*)k_out,
