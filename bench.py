@@ -239,7 +239,7 @@ def main() -> int:
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, cfg["vocab_size"], (PROMPT,), generator=g).tolist()
                for _ in range(BATCH)]
-    e2e_new = min(steps, 16) + 1
+    e2e_new = max(steps, 32) + 1
     gen.stats.__init__()
     engine.h2d_bytes = engine.d2h_bytes = 0
     gen.generate(prompts, e2e_new, SamplingParams.greedy(), stop_token_ids=[])

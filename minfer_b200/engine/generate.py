@@ -119,6 +119,84 @@ def run_batch(engine: Any, sampler: Any, prompts: Sequence[Sequence[int]], strea
     return results
 
 
+def run_batch_pipelined(engine: Any, sampler: Any, prompts: Sequence[Sequence[int]],
+                        streams: Sequence[int], max_new_tokens: int,
+                        stop_token_ids: Sequence[int], max_positions: int,
+                        stats: Optional[GenerationStats] = None) -> List[GenerationResult]:
+    """The same decisions as ``run_batch`` with the host one step behind the device: the next
+    decode step is launched from the sampled tokens while they are still on the device, and
+    only then are the previous step's tokens read.  Ends by length are known in advance from
+    the counts; an end by a stop token is seen one step late, and the step that sequence ran
+    in the meantime is dropped (a row's result never depends on the other rows, so the tokens
+    are those of ``run_batch``).
+
+    Needs ``engine.decode_on_device(slots, tokens)`` and ``sampler.sample_on_device`` /
+    ``sampler.fetch``."""
+    import torch
+    stats = stats if stats is not None else GenerationStats()
+    stop = set(int(t) for t in stop_token_ids)
+    n = len(prompts)
+    results = [GenerationResult([], "length", len(p)) for p in prompts]
+    if max_new_tokens <= 0:
+        return results
+    slots = [engine.acquire() for _ in range(n)]
+    try:
+        sampler.begin(slots, prompts)
+        t0 = time.perf_counter()
+        logits = engine.step(list(slots), [list(p) for p in prompts])
+        cur = list(range(n))                       # sequences in the order of `tokens`
+        tokens = sampler.sample_on_device(logits, slots, list(streams))
+        fetch = sampler.fetch(tokens)
+        drawn = [1] * n                            # tokens drawn so far (the last may be unread)
+        stopped = [False] * n
+        first = True
+        while cur:
+            # who goes on is known from the counts alone: a token is fed if it is not the last
+            # one allowed and there is a position left for it
+            nxt = [i for i in cur if not stopped[i] and drawn[i] < max_new_tokens
+                   and len(prompts[i]) + drawn[i] <= max_positions]
+            next_tokens = next_fetch = None
+            if nxt:
+                feed = tokens
+                if nxt != cur:
+                    where = {i: k for k, i in enumerate(cur)}
+                    index = torch.tensor([where[i] for i in nxt], dtype=torch.long,
+                                         device=tokens.device)
+                    feed = tokens.index_select(0, index)
+                logits = engine.decode_on_device([slots[i] for i in nxt], feed)
+                next_tokens = sampler.sample_on_device(logits, [slots[i] for i in nxt],
+                                                       [streams[i] for i in nxt])
+                next_fetch = sampler.fetch(next_tokens)
+            host = fetch.get()                     # the step before the one just launched
+            now = time.perf_counter()
+            if first:
+                stats.prefill_tokens += sum(len(p) for p in prompts)
+                stats.prefill_seconds += now - t0
+                first = False
+            else:
+                stats.decode_tokens += len(cur)
+                stats.decode_seconds += now - t0
+            t0 = now
+            stats.steps += 1
+            for i, tok in zip(cur, host):
+                if stopped[i]:
+                    continue                       # the extra step of a sequence that had stopped
+                tok = int(tok)
+                if tok in stop:
+                    results[i].finish_reason = "stop"
+                    stopped[i] = True
+                    continue
+                results[i].tokens.append(tok)
+            for i in nxt:
+                drawn[i] += 1
+            cur, tokens, fetch = nxt, next_tokens, next_fetch
+    finally:
+        for s in slots:
+            engine.release(s)
+    stats.batches += 1
+    return results
+
+
 class Generator:
     """A model with its cache, ready to generate.
 
@@ -128,7 +206,7 @@ class Generator:
     """
 
     def __init__(self, model, max_tokens: int = 16384, max_batch: int = 64,
-                 cuda_graphs: bool = True):
+                 cuda_graphs: bool = True, pipelined: bool = True):
         from .step import Engine
         self.model = model
         self.max_batch = int(max_batch)
@@ -136,6 +214,7 @@ class Generator:
                              cuda_graphs=cuda_graphs)
         self.max_tokens = self.engine.cache.max_tokens
         self.stats = GenerationStats()
+        self.pipelined = bool(pipelined)    # host one step behind the device (same tokens)
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 512,
                  sampling: Optional[SamplingParams] = None,
@@ -156,9 +235,10 @@ class Generator:
                                self.max_tokens)
         sampler = DeviceSampler(self.engine, sampling)
         results: List[Optional[GenerationResult]] = [None] * len(prompts)
+        loop = run_batch_pipelined if self.pipelined else run_batch
         for batch in batches:
-            out = run_batch(self.engine, sampler, [prompts[i] for i in batch], batch,
-                            max_new_tokens, stop_token_ids, plan.max_positions, self.stats)
+            out = loop(self.engine, sampler, [prompts[i] for i in batch], batch,
+                       max_new_tokens, stop_token_ids, plan.max_positions, self.stats)
             for i, r in zip(batch, out):
                 results[i] = r
         self.engine.check_status()

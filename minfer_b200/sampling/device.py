@@ -29,6 +29,10 @@ class DeviceSampler:
         self.state = pool.tensors[STATE_NAME]
         if K.sampler_state_ints() != self.width:
             raise K.KernelError("the sampler kernel and its state layout disagree")
+        self._meta_key = None
+        self._meta_dev = None
+        self._meta_host = None
+        self._copy_stream = torch.cuda.Stream(device=self.device)
 
     def begin(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> None:
         """Seeds each sequence's window with the tail of its prompt (src/main.rs:537-540) and
@@ -41,17 +45,57 @@ class DeviceSampler:
         index = torch.tensor(list(slots), dtype=torch.long, device=self.device)
         self.state.index_copy_(0, index, rows.to(self.device))
 
-    def sample(self, logits: torch.Tensor, slots: Sequence[int],
-               streams: Sequence[int]) -> List[int]:
-        """One token per row of ``logits`` (changed in place); returns them on the host."""
+    def _meta(self, slots: Sequence[int], streams: Sequence[int]) -> torch.Tensor:
+        """Slots and RNG streams of the rows on the device; kept while the rows stay the same."""
+        key = (tuple(slots), tuple(streams))
+        if self._meta_key != key:
+            host = torch.tensor(list(slots) + list(streams), dtype=torch.int32).pin_memory()
+            self._meta_dev = host.to(self.device, non_blocking=True)
+            self._meta_host = host                      # keep the pinned buffer alive
+            self._meta_key = key
+            self.engine.h2d_bytes += host.numel() * 4
+        return self._meta_dev
+
+    def sample_on_device(self, logits: torch.Tensor, slots: Sequence[int],
+                         streams: Sequence[int]) -> torch.Tensor:
+        """One token per row of ``logits`` (changed in place); the tokens stay on the device
+        (int32 [rows]), so that the next step can be launched without waiting for them."""
         p = self.params
         n = logits.shape[0]
-        meta = torch.tensor(list(slots) + list(streams), dtype=torch.int32).to(self.device)
+        meta = self._meta(slots, streams)
         out = torch.empty(n, dtype=torch.int32, device=self.device)
         K.sample(logits, out, temperature=p.temperature, top_k=p.top_k, top_p=p.top_p,
                  repeat_penalty=p.repeat_penalty, frequency_penalty=p.frequency_penalty,
                  presence_penalty=p.presence_penalty, seed=p.seed, slots=meta[:n],
                  state=self.state, stream_ids=meta[n:], update_state=True)
-        self.engine.h2d_bytes += meta.numel() * 4
-        self.engine.d2h_bytes += n * 4
-        return out.cpu().tolist()
+        return out
+
+    def fetch(self, tokens: torch.Tensor) -> "TokenFetch":
+        """Starts copying ``tokens`` to the host on a side stream; ``.get()`` waits for that
+        copy only, not for whatever was launched after it."""
+        self.engine.d2h_bytes += tokens.numel() * 4
+        return TokenFetch(tokens, self._copy_stream)
+
+    def sample(self, logits: torch.Tensor, slots: Sequence[int],
+               streams: Sequence[int]) -> List[int]:
+        """One token per row of ``logits`` (changed in place); returns them on the host."""
+        return self.fetch(self.sample_on_device(logits, slots, streams)).get()
+
+
+class TokenFetch:
+    """A device-to-host copy of a few token ids that does not wait for later work."""
+
+    def __init__(self, tokens: torch.Tensor, copy_stream: torch.cuda.Stream):
+        self.host = torch.empty(tokens.shape, dtype=tokens.dtype).pin_memory()
+        self.done = torch.cuda.Event()
+        ready = torch.cuda.Event()
+        ready.record()                                  # after the sampling kernel
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(ready)
+            self.host.copy_(tokens, non_blocking=True)
+            self.done.record()
+        self._keep = tokens                             # not freed before the copy has run
+
+    def get(self) -> List[int]:
+        self.done.synchronize()
+        return self.host.tolist()

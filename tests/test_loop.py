@@ -101,3 +101,49 @@ def test_batches_one_after_another_fit_the_cache():
     with pytest.raises(ValueError, match="request 1"):
         plan_batches([10, 500], 20, 4, 256)
     assert plan_batches([], 5, 4, 256) == []
+
+
+class TensorSampler(ScriptedSampler):
+    """The scripted sampler with the interface of the pipelined loop (tokens as tensors)."""
+
+    def sample_on_device(self, logits, slots, streams):
+        import torch
+        return torch.tensor(self.sample(logits, slots, streams), dtype=torch.int32)
+
+    def fetch(self, tokens):
+        class Fetch:
+            def get(self_inner):
+                return tokens.tolist()
+        return Fetch()
+
+
+class TensorEngine(MockEngine):
+    def __init__(self):
+        super().__init__()
+        self.device_steps = []
+
+    def decode_on_device(self, slots, tokens):
+        self.device_steps.append((list(slots), tokens.tolist()))
+        return self.step(slots, [[int(t)] for t in tokens.tolist()])
+
+
+@pytest.mark.parametrize("max_new,max_pos", [(4, 1000), (1, 1000), (6, 6), (3, 4)])
+def test_pipelined_loop_makes_the_same_decisions(max_new, max_pos):
+    from minfer_b200.engine.generate import run_batch_pipelined
+    script = {0: [10, 11, 99, 12, 13, 14, 15], 1: [20, 99, 21, 22, 23, 24, 25],
+              2: [30, 31, 32, 33, 34, 35, 36], 3: [99, 1, 2, 3, 4, 5, 6]}
+    prompts = [[1, 2, 3], [4], [5, 6], [7, 8]]
+    want = run_batch(MockEngine(), ScriptedSampler(script), prompts, [0, 1, 2, 3], max_new, [99],
+                     max_pos)
+    eng = TensorEngine()
+    stats = GenerationStats()
+    got = run_batch_pipelined(eng, TensorSampler(script), prompts, [0, 1, 2, 3], max_new, [99],
+                              max_pos, stats)
+    assert [r.tokens for r in got] == [r.tokens for r in want]
+    assert [r.finish_reason for r in got] == [r.finish_reason for r in want]
+    assert eng.lengths == {} and sorted(eng.released) == [0, 1, 2, 3]
+    # no sequence ever runs past the model's last position, and a stopped sequence runs at most
+    # one step more than in the plain loop
+    for slots, _ in eng.device_steps:
+        assert len(slots) == len(set(slots))
+    assert stats.batches == 1
