@@ -29,6 +29,7 @@
 #define TILE_K 64             // k per stage: 64 bf16 = 128 bytes = one swizzle row
 #define A_BYTES (TILE_N * TILE_K * 2)
 #define MAX_SPIN (1u << 24)
+#define MAX_WAIT_NS 2000000000ull   // two seconds
 
 #define EPI_STORE 0           // out = acc + bias          (float32 or bfloat16)
 #define EPI_ACCUM 1           // out += acc + bias         (float32)
@@ -72,10 +73,22 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // bounded wait; false = gave up (abort flag set)
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// (bounded both by a number of tries and by wall time: a try may itself block for a while)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    unsigned long long t0 = 0;
     for (uint32_t it = 0; it < MAX_SPIN; ++it) {
         if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
+        if ((it & 1023u) == 1023u) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > MAX_WAIT_NS) break;
+        }
     }
     *abort_flag = 1;
     return false;
@@ -135,6 +148,52 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
 __host__ __device__ constexpr uint32_t umma_idesc(int nt) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(nt >> 3) << 17) |
            ((uint32_t)(TILE_N >> 4) << 24);
+}
+
+// One chunk of the epilogue: this thread's 16 consecutive tokens (tok0 ..) of output row n.
+__device__ __forceinline__ void store_chunk(const GemmArgs& a, const uint32_t* r, int n, bool n_ok,
+                                            float bias, int tok0, int lane, int split) {
+    if (a.epi == EPI_SWIGLU) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int tok = tok0 + j;
+            const float v = __uint_as_float(r[j]);
+            const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+            if (tok < a.M && n_ok && (lane & 1) == 0) {
+                const float g = v, u = other;
+                ((__nv_bfloat16*)a.out)[(size_t)tok * a.ldo + (n >> 1)] =
+                    __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
+            }
+        }
+    } else if (a.epi == EPI_ACCUM) {
+        // all loads of the chunk first, so that they are in flight together
+        float old[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int tok = tok0 + j;
+            old[j] = (tok < a.M && n_ok) ? ((const float*)a.out)[(size_t)tok * a.ldo + n] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int tok = tok0 + j;
+            if (tok < a.M && n_ok)
+                ((float*)a.out)[(size_t)tok * a.ldo + n] = old[j] + __uint_as_float(r[j]) + bias;
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int tok = tok0 + j;
+            const float v = __uint_as_float(r[j]) + bias;
+            if (tok < a.M && n_ok) {
+                if (a.epi == EPI_PARTIAL)
+                    a.partial[((size_t)split * a.M + tok) * a.N + n] = v;
+                else if (a.out_dtype == MF_DTYPE_F32)
+                    ((float*)a.out)[(size_t)tok * a.ldo + n] = v;
+                else
+                    ((__nv_bfloat16*)a.out)[(size_t)tok * a.ldo + n] = __float2bfloat16_rn(v);
+            }
+        }
+    }
 }
 
 template <int NT> struct TmemCols { static constexpr int value = NT < 32 ? 32 : NT; };
@@ -246,47 +305,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             uint32_t r[16];
             tc_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
             tc_wait_ld();
-            if (a.epi == EPI_SWIGLU) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int tok = m0 + c0 + j;
-                    const float v = __uint_as_float(r[j]);
-                    const float other = __shfl_xor_sync(0xffffffffu, v, 1);
-                    if (tok < a.M && n_ok && (lane & 1) == 0) {
-                        const float g = v, u = other;
-                        ((__nv_bfloat16*)a.out)[(size_t)tok * a.ldo + (n >> 1)] =
-                            __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
-                    }
-                }
-            } else if (a.epi == EPI_ACCUM) {
-                // all loads of the chunk first, so that they are in flight together
-                float old[16];
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int tok = m0 + c0 + j;
-                    old[j] = (tok < a.M && n_ok) ? ((const float*)a.out)[(size_t)tok * a.ldo + n] : 0.0f;
-                }
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int tok = m0 + c0 + j;
-                    if (tok < a.M && n_ok)
-                        ((float*)a.out)[(size_t)tok * a.ldo + n] = old[j] + __uint_as_float(r[j]) + bias;
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int tok = m0 + c0 + j;
-                    const float v = __uint_as_float(r[j]) + bias;
-                    if (tok < a.M && n_ok) {
-                        if (a.epi == EPI_PARTIAL)
-                            a.partial[((size_t)split * a.M + tok) * a.N + n] = v;
-                        else if (a.out_dtype == MF_DTYPE_F32)
-                            ((float*)a.out)[(size_t)tok * a.ldo + n] = v;
-                        else
-                            ((__nv_bfloat16*)a.out)[(size_t)tok * a.ldo + n] = __float2bfloat16_rn(v);
-                    }
-                }
-            }
+            store_chunk(a, r, n, n_ok, bias, m0 + c0, lane, split);
         }
     }
     tc_fence_before();
@@ -403,6 +422,227 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& 
     return MF_LAUNCH_CHECK();
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Many tokens: a PAIR of CTAs (a cluster of two SMs) works on one 256 x NT tile with
+// tcgen05.mma.cta_group::2.  Each CTA stages its own 128 weight rows and its own half of the
+// NT tokens, so an SM moves half the operand bytes per MMA clock of the one-CTA kernel; that
+// leaves room for a TMA ring that covers an L2 round trip.  The kernel is persistent (one pair
+// per two SMs walks over the tiles) and keeps two accumulators in tensor memory, so the four
+// epilogue warps of a tile run while the MMA thread is already on the next tile.
+//
+//   warp 0, one thread   TMA producer (both CTAs); both CTAs' copies complete on the
+//                        LEADER's (rank 0) "full" barrier, which the leader arms for both
+//   warp 1, one thread   MMA issuer, leader CTA only; tcgen05.commit multicasts to both CTAs'
+//                        "empty" barriers (stage free) and "accumulator full" barriers
+//   warps 2-5            epilogue of the CTA's own 128 accumulator rows; when done they arrive
+//                        on the leader's "accumulator empty" barrier (remote for rank 1)
+// No load is multicast: each CTA fetches its own tiles.
+// ------------------------------------------------------------------------------------------
+#define PAIR_THREADS 192
+#define PEER_BIT_MASK 0xFEFFFFFFu      // clears the CTA-rank bit of a shared::cluster address
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(leader_bar)
+        : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                            uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {   // arrives in both CTAs
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+        " [%0], %1;"
+        ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t cta_rank) {
+    asm volatile(
+        "{\n .reg .b32 ra;\n mapa.shared::cluster.u32 ra, %0, %1;\n"
+        " mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n}\n"
+        ::"r"(bar), "r"(cta_rank) : "memory");
+}
+
+template <int NT, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                 const GemmArgs a, int tiles_m, int total_tiles) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int B_BYTES = (NT / 2) * TILE_K * 2;           // this CTA's half of the tokens
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int TMEM_COLS = 2 * NT;                         // two accumulators
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
+    uint64_t* full = bars;                    // [STAGES]  leader's are used
+    uint64_t* empty = bars + STAGES;          // [STAGES]  each CTA waits on its own
+    uint64_t* acc_full = bars + 2 * STAGES;   // [2]       each CTA waits on its own
+    uint64_t* acc_empty = acc_full + 2;       // [2]       leader's are used
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int kblocks = (a.K + TILE_K - 1) / TILE_K;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&full[s]), 1);
+            mbar_init(smem_u32(&empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full[b]), 1);
+            mbar_init(smem_u32(&acc_empty[b]), 8);            // 4 epilogue warps of each CTA
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                       // both CTAs' barriers exist
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer ------------------------------------------------------------
+        int it = 0;
+        bool ok = true;
+        for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
+            const int m0 = (tile % tiles_m) * NT, n0 = (tile / tiles_m) * 256;
+            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
+                const uint32_t leader_full = smem_u32(&full[s]) & PEER_BIT_MASK;
+                if (rank == 0) mbar_expect_tx(smem_u32(&full[s]), 2 * STAGE_BYTES);
+                const uint32_t dst = smem_u32(smem + s * STAGE_BYTES);
+                tma_load_2d_pair(dst, &map_w, kb * TILE_K, n0 + (int)rank * TILE_N, leader_full);
+                tma_load_2d_pair(dst + A_BYTES, &map_x, kb * TILE_K, m0 + (int)rank * (NT / 2),
+                                 leader_full);
+            }
+        }
+    } else if (warp == 1 && lane == 0 && rank == 0) {
+        // ---- MMA issuer (leader) -------------------------------------------------------
+        constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NT >> 3) << 17) |
+                                   ((uint32_t)(256 >> 4) << 24);
+        int it = 0, tile_i = 0;
+        bool ok = true;
+        for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++tile_i) {
+            const int b = tile_i & 1;
+            const uint32_t u = (uint32_t)(tile_i >> 1);
+            ok = mbar_wait(smem_u32(&acc_empty[b]), (u & 1u) ^ 1u, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t tmem_d = tmem_base + (uint32_t)(b * NT);
+            for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
+                ok = mbar_wait(smem_u32(&full[s]), ph, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+                const uint64_t da = umma_desc(sa), db = umma_desc(sa + A_BYTES);
+#pragma unroll
+                for (int k = 0; k < TILE_K / 16; ++k)
+                    tc_mma_pair(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                                (kb > 0 || k > 0) ? 1u : 0u);
+                tc_commit_pair(smem_u32(&empty[s]));
+            }
+            if (ok) tc_commit_pair(smem_u32(&acc_full[b]));
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue: this CTA's 128 rows; warp w reads TMEM lanes 32*(w%4) .. ------------
+        const int q = warp & 3;
+        int tile_i = 0;
+        for (int tile = pair; tile < total_tiles; tile += n_pairs, ++tile_i) {
+            const int b = tile_i & 1;
+            const uint32_t u = (uint32_t)(tile_i >> 1);
+            const int m0 = (tile % tiles_m) * NT, n0 = (tile / tiles_m) * 256;
+            if (!mbar_wait(smem_u32(&acc_full[b]), u & 1u, abort_flag)) break;
+            tc_fence_after();
+            const int n = n0 + (int)rank * TILE_N + q * 32 + lane;
+            const bool n_ok = n < a.N;
+            const float bias = (a.bias != nullptr && n_ok) ? a.bias[n] : 0.0f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < NT; c0 += 16) {
+                if (m0 + c0 >= a.M) break;
+                uint32_t r[16];
+                tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * NT + c0), r);
+                tc_wait_ld();
+                store_chunk(a, r, n, n_ok, bias, m0 + c0, lane, 0);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(smem_u32(&acc_empty[b]), 0);
+        }
+    }
+    __syncwarp();
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0) {
+        atomicOr(a.status, MF_STATUS_WAIT_TIMEOUT);
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    cluster_sync_all();              // the partner no longer reads this CTA's memory or barriers
+    tc_fence_after();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+template <int NT, int STAGES>
+static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
+                       cudaStream_t stream) {
+    constexpr int smem = STAGES * (A_BYTES + (NT / 2) * TILE_K * 2) + 1024 + 256;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<NT, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int tiles_m = (a.M + NT - 1) / NT, tiles_n = (a.N + 255) / 256;
+    const int total = tiles_m * tiles_n;
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms < 2) sms = 2;
+    }
+    int pairs = sms / 2;
+    if (pairs > total) pairs = total;
+    mf_launch(gemm_pair_kernel<NT, STAGES>, dim3(2 * pairs), dim3(PAIR_THREADS), smem, stream, mw, mx,
+              a, tiles_m, total);
+    return MF_LAUNCH_CHECK();
+}
+
 // How a product of these sizes is cut: the token tile and the number of K splits.  A
 // function of the sizes only (never of the data), so results are reproducible.
 extern "C" int mf_gemm_tc_plan(int M, int N, int K, int epi, int* token_tile, int* splits) {
@@ -463,6 +703,16 @@ extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long
     if (splits > 1 && workspace == nullptr) return MF_ERR_ARGUMENT;
     CUtensorMap mw, mx;
     if (int e = weight_map(&mw, w, N, K, ldw)) return e;
+    static int pair_mode = -1;            // MINFER_B200_GEMM_PAIR=0 keeps the one-CTA kernel
+    if (pair_mode < 0) { const char* ev = getenv("MINFER_B200_GEMM_PAIR"); pair_mode = ev ? atoi(ev) : 1; }
+    if (pair_mode && M >= 256 && splits == 1) {
+        if (int e = make_map(&mx, x, M, K, ldx, 128)) return e;
+        GemmArgs pa;
+        pa.out = out; pa.partial = nullptr; pa.bias = bias; pa.status = status; pa.ldo = ldo;
+        pa.M = M; pa.N = N; pa.K = K; pa.out_dtype = out_dtype; pa.kblocks_per_split = 0;
+        pa.epi = epi;
+        return launch_pair<256, 6>(mw, mx, pa, stream);
+    }
     if (int e = make_map(&mx, x, M, K, ldx, nt)) return e;
     const int kblocks = (K + TILE_K - 1) / TILE_K;
     GemmArgs a;
