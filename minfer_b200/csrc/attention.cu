@@ -482,10 +482,8 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
         if (e) return e;
         // measured: started early, the merge of the chunks costs 5 us more than it saves (its
         // blocks sit on the SMs while the last attention blocks still look for room)
-        mf_launch_serial = true;
-        mf_launch(attention_combine_kernel<__nv_bfloat16>, dim3(rows * n_heads), dim3(hd), 0, stream, 
-            partial, (__nv_bfloat16*)out, n_chunks, hd);
-        mf_launch_serial = false;
+        mf_launch_ex(false, attention_combine_kernel<__nv_bfloat16>, dim3(rows * n_heads), dim3(hd), 0,
+                     stream, partial, (__nv_bfloat16*)out, n_chunks, hd);
         return MF_LAUNCH_CHECK();
     }
     const long long items = (long long)rows * n_heads * n_chunks;

@@ -111,11 +111,10 @@ static inline bool mf_pdl_enabled() {
     return enabled == 1;
 }
 
-static inline bool mf_launch_serial = false;   // set around a launch that must not start early
-
+// early = false: an ordinary launch that starts when the kernel before it has completed
 template <typename... KArgs, typename... Args>
-static inline void mf_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                             cudaStream_t stream, Args&&... args) {
+static inline void mf_launch_ex(bool early, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                size_t smem, cudaStream_t stream, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -125,8 +124,14 @@ static inline void mf_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
-    cfg.numAttrs = (mf_pdl_enabled() && !mf_launch_serial) ? 1 : 0;
+    cfg.numAttrs = (early && mf_pdl_enabled()) ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+static inline void mf_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args&&... args) {
+    mf_launch_ex(true, kernel, grid, block, smem, stream, std::forward<Args>(args)...);
 }
 #endif
 

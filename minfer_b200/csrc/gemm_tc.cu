@@ -650,11 +650,6 @@ extern "C" int mf_gemm_tc_plan(int M, int N, int K, int epi, int* token_tile, in
     // epilogue overlaps the other's main loop (measured faster than 256-token tiles with one
     // CTA per SM for K = 3584: 958 against 847 TFLOP/s)
     int nt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
-    if (M > 128) {
-        static int forced = -1;
-        if (forced < 0) { const char* e = getenv("MINFER_B200_GEMM_TILE"); forced = e ? atoi(e) : 0; }
-        if (forced == 128 || forced == 256) nt = forced;
-    }
     const int tiles = ((M + nt - 1) / nt) * ((N + TILE_N - 1) / TILE_N);
     const int kblocks = (K + TILE_K - 1) / TILE_K;
     int s = 1;
@@ -728,8 +723,7 @@ extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long
         case 16: e = launch<16, 6>(mw, mx, a, splits, stream); break;
         case 32: e = launch<32, 5>(mw, mx, a, splits, stream); break;
         case 64: e = launch<64, 4>(mw, mx, a, splits, stream); break;
-        case 128: e = launch<128, 3>(mw, mx, a, splits, stream); break;
-        default: e = launch<256, 4>(mw, mx, a, splits, stream); break;
+        default: e = launch<128, 3>(mw, mx, a, splits, stream); break;
     }
     if (e || splits == 1) return e;
     if (deferred) {

@@ -647,22 +647,3 @@ extern "C" int mf_cast(const void* in, int in_dtype, void* out, int out_dtype, l
         return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();
 }
-
-// ------------------------------------------------------------------------------------
-// decode bookkeeping on the device, so that a captured decode step can be replayed:
-// positions[b] += 1 and seq_end[b] += 1 for live rows.
-// ------------------------------------------------------------------------------------
-__global__ void advance_kernel(int* __restrict__ positions, int* __restrict__ seq_end, int n) {
-    pdl_prologue();
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) {
-        positions[i] += 1;
-        seq_end[i] += 1;
-    }
-}
-
-extern "C" int mf_advance_positions(int* positions, int* seq_end, int n, cudaStream_t stream) {
-    if (n <= 0) return 0;
-    mf_launch(advance_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, positions, seq_end, n);
-    return MF_LAUNCH_CHECK();
-}

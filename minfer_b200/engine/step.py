@@ -15,7 +15,6 @@ kernel's result for one row depends on what else is in the batch.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
 import torch
@@ -28,11 +27,6 @@ from ..parts.base import CacheView, CallBinding, StepContext, settle_pending
 
 class StepError(RuntimeError):
     pass
-
-
-@dataclass
-class StepResult:
-    logits: torch.Tensor            # float32 [n_wanted, vocab] on the device
 
 
 class Engine:
@@ -195,12 +189,6 @@ class Engine:
             self.cache.set_length(slots[b], starts[b] + 1)
         self.steps_run += 1
         return logits
-
-    def assume_filled(self, slot: int, length: int) -> None:
-        """Benchmarks only: gives the sequence ``length`` positions of cache without running
-        the model; whatever the pages hold stands in for keys and values."""
-        self.cache.reserve(slot, length)
-        self.cache.set_length(slot, length)
 
     # ---- metadata -----------------------------------------------------------------------
     def _host_fields(self, slots, tokens, counts, starts, want, widths):

@@ -93,7 +93,6 @@ def _sig_ops(lib: ctypes.CDLL) -> None:
     lib.mf_swiglu.argtypes = [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
     lib.mf_gather_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
     lib.mf_cast.argtypes = [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p]
-    lib.mf_advance_positions.argtypes = [c_void_p, c_void_p, c_int, c_void_p]
 
 
 def _sig_gemm_simt(lib: ctypes.CDLL) -> None:
@@ -235,11 +234,6 @@ def cast(src: torch.Tensor, out: torch.Tensor) -> None:
         raise KernelError("cast: sizes differ")
     _check(_lib("ops").mf_cast(_ptr(src, "src"), dtype_code(src.dtype), _ptr(out, "out"),
                                dtype_code(out.dtype), src.numel(), _stream()), "cast")
-
-
-def advance_positions(positions: torch.Tensor, seq_end: torch.Tensor, n: int) -> None:
-    _check(_lib("ops").mf_advance_positions(_i32(positions, "positions"), _i32(seq_end, "seq_end"),
-                                            n, _stream()), "advance_positions")
 
 
 # ---------------------------------------------------------------------------------------

@@ -119,6 +119,14 @@ def compile_library(name: str, verbose: bool = True) -> str:
             pass
         raise KernelBuildError(f"nvcc failed for {source}:\n{' '.join(cmd)}\n{log}")
     os.replace(tmp, out)
+    # older builds of the same library (other source hashes) are of no use any more
+    prefix = f"libmf_{name}_"
+    for other in os.listdir(os.path.dirname(out)):
+        if other.startswith(prefix) and other.endswith(".so") and other != os.path.basename(out):
+            try:
+                os.remove(os.path.join(os.path.dirname(out), other))
+            except OSError:
+                pass
     if verbose:
         print(f"[minfer_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s",
               file=sys.stderr, flush=True)

@@ -189,7 +189,8 @@ def attention_reference(q, k, v, scale, window):
 
 
 @pytest.mark.parametrize("hd,nh,nk,window", [(16, 4, 1, 0), (32, 6, 2, 16), (48, 3, 3, 70),
-                                             (64, 14, 2, 0), (128, 7, 1, 33), (256, 2, 2, 0)])
+                                             (64, 14, 2, 0), (128, 7, 1, 33), (256, 2, 2, 0),
+                                             (80, 5, 5, 0), (112, 9, 3, 50), (128, 34, 2, 0)])
 def test_attention_packed_unequal_sequences(hd, nh, nk, window):
     from minfer_b200.kernels import api as K
     lens = [37, 1, 100, 65]
@@ -244,7 +245,8 @@ def test_attention_finds_a_far_key_among_hundreds():
 
 @pytest.mark.parametrize("hd,nh,nk,window,ring", [(16, 4, 1, 0, 0), (32, 6, 2, 16, 64),
                                                   (48, 3, 3, 70, 128), (128, 28, 4, 0, 0),
-                                                  (64, 2, 1, 100, 0)])
+                                                  (64, 2, 1, 100, 0), (96, 6, 3, 0, 0),
+                                                  (128, 34, 2, 0, 0), (240, 3, 1, 0, 0)])
 def test_attention_paged_matches_packed_history(hd, nh, nk, window, ring):
     """Queries at the ends of sequences of unequal lengths over a scattered paged cache."""
     from minfer_b200.kernels import api as K
