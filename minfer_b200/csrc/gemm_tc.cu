@@ -154,16 +154,21 @@ __host__ __device__ constexpr uint32_t umma_idesc(int nt) {
 __device__ __forceinline__ void store_chunk(const GemmArgs& a, const uint32_t* r, int n, bool n_ok,
                                             float bias, int tok0, int lane, int split) {
     if (a.epi == EPI_SWIGLU) {
+        // Lanes come in pairs: the even lane holds the gate row, the odd lane the up row of the
+        // same output column, both for these 16 tokens.  They swap halves (one shuffle per two
+        // tokens), then the even lane finishes the even tokens and the odd lane the odd ones, so
+        // every lane does half of the work instead of every other lane doing all of it.
+        const bool even = (lane & 1) == 0;
+        __nv_bfloat16* o = (__nv_bfloat16*)a.out + (size_t)(tok0 + (even ? 0 : 1)) * a.ldo + (n >> 1);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const int tok = tok0 + j;
-            const float v = __uint_as_float(r[j]);
-            const float other = __shfl_xor_sync(0xffffffffu, v, 1);
-            if (tok < a.M && n_ok && (lane & 1) == 0) {
-                const float g = v, u = other;
-                ((__nv_bfloat16*)a.out)[(size_t)tok * a.ldo + (n >> 1)] =
-                    __float2bfloat16_rn(g / (1.0f + __expf(-g)) * u);
-            }
+        for (int jj = 0; jj < 8; ++jj) {
+            const float keep = __uint_as_float(even ? r[2 * jj] : r[2 * jj + 1]);
+            const float send = __uint_as_float(even ? r[2 * jj + 1] : r[2 * jj]);
+            const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+            const float g = even ? keep : recv, u = even ? recv : keep;
+            const int tok = tok0 + 2 * jj + (even ? 0 : 1);
+            if (tok < a.M && n_ok)
+                o[(size_t)(2 * jj) * a.ldo] = __float2bfloat16_rn(__fdividef(g * u, 1.0f + __expf(-g)));
         }
     } else if (a.epi == EPI_ACCUM) {
         // all loads of the chunk first, so that they are in flight together
