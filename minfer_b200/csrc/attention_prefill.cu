@@ -52,21 +52,36 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint3
 }
 
 // copies rows [row0, row0+64) of a packed [tokens][heads][HD] tensor (one head) into a
-// swizzled [64][HD] tile; rows at or beyond `n_valid` (relative to row0) are zero-filled
+// swizzled [64][HD] tile; rows at or beyond `n_valid` (relative to row0) are zero-filled.
+// A thread always copies the same 16-byte column of rows r0, r0 + RPP, ...: its swizzled
+// column and its offsets are computed once (TileCopy) and only advanced here.
 template <int HD>
-__device__ __forceinline__ void load_tile(__nv_bfloat16* tile, const __nv_bfloat16* base,
-                                          long long row_stride, int n_valid, int tid) {
-    constexpr int CPR = HD / 8;
-    for (int i = tid; i < 64 * CPR; i += PF_WARPS * 32) {
-        const int r = i / CPR, c = i % CPR;
-        const bool ok = r < n_valid;
-        const __nv_bfloat16* src = base + (ok ? (long long)r * row_stride + c * 8 : 0);
-        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(tile + (r * CPR + (c ^ (r & 7))) * 8);
-        const int bytes = ok ? 16 : 0;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes)
-                     : "memory");
+struct TileCopy {
+    static constexpr int CPR = HD / 8;                    // 16-byte chunks per row
+    static constexpr int RPP = PF_WARPS * 32 / CPR;       // rows per pass of the CTA (8 or 16)
+    int r0;                                               // first row of this thread
+    uint32_t dst_off;                                     // bytes into the tile
+    int src_col;                                          // elements into the row
+    __device__ __forceinline__ TileCopy(int tid) {
+        r0 = tid / CPR;
+        const int c = tid % CPR;
+        dst_off = (uint32_t)((r0 * CPR + (c ^ (r0 & 7))) * 16);
+        src_col = c * 8;
     }
-}
+    __device__ __forceinline__ void load(__nv_bfloat16* tile, const __nv_bfloat16* base,
+                                         long long row_stride, int n_valid) const {
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(tile) + dst_off;
+        const __nv_bfloat16* src = base + (long long)r0 * row_stride + src_col;
+#pragma unroll
+        for (int j = 0; j < 64 / RPP; ++j) {
+            const bool ok = r0 + j * RPP < n_valid;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                         ::"r"(dst + (uint32_t)(j * RPP * CPR * 16)),
+                           "l"(ok ? src + (long long)j * RPP * row_stride : base), "r"(ok ? 16 : 0)
+                         : "memory");
+        }
+    }
+};
 
 template <int HD>
 __global__ void __launch_bounds__(PF_WARPS * 32, 3) attention_prefill_mma_kernel(PrefillArgs a) {
@@ -94,10 +109,9 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 3) attention_prefill_mma_kernel
     const int kt_begin = a.window > 0 ? max(0, q0 - a.window + 1) / PF_KEYS : 0;
     const int kt_end = q_last / PF_KEYS;                          // inclusive
 
-    load_tile<HD>(k_s, kb + (long long)kt_begin * PF_KEYS * kv_stride, kv_stride,
-                  len - kt_begin * PF_KEYS, tid);
-    load_tile<HD>(v_s, vb + (long long)kt_begin * PF_KEYS * kv_stride, kv_stride,
-                  len - kt_begin * PF_KEYS, tid);
+    const TileCopy<HD> copy(tid);
+    copy.load(k_s, kb + (long long)kt_begin * PF_KEYS * kv_stride, kv_stride, len - kt_begin * PF_KEYS);
+    copy.load(v_s, vb + (long long)kt_begin * PF_KEYS * kv_stride, kv_stride, len - kt_begin * PF_KEYS);
     asm volatile("cp.async.commit_group;" ::: "memory");
 
     float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
@@ -120,13 +134,26 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 3) attention_prefill_mma_kernel
         }
     }
 
+    // ldmatrix addresses: a lane's row offset and its swizzled 16-byte column per k-step (keys)
+    // or per pair of output columns (values), computed once
+    const uint32_t k_lane = (uint32_t)((((lane >> 4) * 8 + (lane & 7)) * CPR) * 16);
+    const uint32_t v_lane = (uint32_t)(((((lane >> 3) & 1) * 8 + (lane & 7)) * CPR) * 16);
+    uint32_t k_col[HD / 16], v_col[HD / 16];
+#pragma unroll
+    for (int i = 0; i < HD / 16; ++i) {
+        k_col[i] = (uint32_t)(((2 * i + ((lane >> 3) & 1)) ^ (lane & 7)) * 16);
+        v_col[i] = (uint32_t)(((2 * i + (lane >> 4)) ^ (lane & 7)) * 16);
+    }
+    const uint32_t k_s_addr = (uint32_t)__cvta_generic_to_shared(k_s);
+    const uint32_t v_s_addr = (uint32_t)__cvta_generic_to_shared(v_s);
+
     for (int kt = kt_begin; kt <= kt_end; ++kt) {
         const int buf = (kt - kt_begin) & 1;
         if (kt < kt_end) {                                        // prefetch the next tile
             const int nb = buf ^ 1;
             const long long off = (long long)(kt + 1) * PF_KEYS * kv_stride;
-            load_tile<HD>(k_s + nb * 64 * HD, kb + off, kv_stride, len - (kt + 1) * PF_KEYS, tid);
-            load_tile<HD>(v_s + nb * 64 * HD, vb + off, kv_stride, len - (kt + 1) * PF_KEYS, tid);
+            copy.load(k_s + nb * 64 * HD, kb + off, kv_stride, len - (kt + 1) * PF_KEYS);
+            copy.load(v_s + nb * 64 * HD, vb + off, kv_stride, len - (kt + 1) * PF_KEYS);
             asm volatile("cp.async.commit_group;" ::: "memory");
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
@@ -138,17 +165,15 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 3) attention_prefill_mma_kernel
         float s[8][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i) { s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f; }
-        const uint32_t ks_base = (uint32_t)__cvta_generic_to_shared(k_s + buf * 64 * HD);
+        const uint32_t ks_base = k_s_addr + (uint32_t)(buf * 64 * HD * 2) + k_lane;
         // k-step outermost: consecutive MMAs go to different accumulators, so none waits for
         // the one before it
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks) {
-            const int c = 2 * ks + ((lane >> 3) & 1);
 #pragma unroll
             for (int np = 0; np < 4; ++np) {                      // pairs of 8-key tiles
-                const int key = np * 16 + (lane >> 4) * 8 + (lane & 7);
                 uint32_t b0, b1, b2, b3;
-                ldsm_x4(ks_base + (uint32_t)((key * CPR + (c ^ (key & 7))) * 16), b0, b1, b2, b3);
+                ldsm_x4(ks_base + k_col[ks] + (uint32_t)(np * 16 * CPR * 16), b0, b1, b2, b3);
                 mma16816(s[2 * np], qa[ks], b0, b1);
                 mma16816(s[2 * np + 1], qa[ks], b2, b3);
             }
@@ -208,15 +233,13 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 3) attention_prefill_mma_kernel
             pa[nt >> 1][(nt & 1) * 2 + 1] = pack2(p[2], p[3]);
         }
         // O += P V
-        const uint32_t vs_base = (uint32_t)__cvta_generic_to_shared(v_s + buf * 64 * HD);
+        const uint32_t vs_base = v_s_addr + (uint32_t)(buf * 64 * HD * 2) + v_lane;
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-            const int key = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
 #pragma unroll
             for (int np = 0; np < HD / 16; ++np) {
-                const int c = 2 * np + (lane >> 4);
                 uint32_t r0, r1, r2, r3;
-                ldsm_x4_trans(vs_base + (uint32_t)((key * CPR + (c ^ (key & 7))) * 16), r0, r1, r2, r3);
+                ldsm_x4_trans(vs_base + v_col[np] + (uint32_t)(ks * 16 * CPR * 16), r0, r1, r2, r3);
                 mma16816(o[2 * np], pa[ks], r0, r1);
                 mma16816(o[2 * np + 1], pa[ks], r2, r3);
             }

@@ -70,6 +70,12 @@ def _f32(t: Optional[torch.Tensor], what: str) -> Optional[int]:
     return _ptr(t, what)
 
 
+def _f64(t: Optional[torch.Tensor], what: str) -> Optional[int]:
+    if t is not None and t.dtype != torch.float64:
+        raise KernelError(f"{what} must be float64, got {t.dtype}")
+    return _ptr(t, what)
+
+
 _configured: set[str] = set()
 
 
@@ -202,7 +208,7 @@ def rope_kvstore(qkv: torch.Tensor, positions: torch.Tensor, token_row: torch.Te
     _check(_lib("ops").mf_rope_kvstore(
         _f32(qkv, "qkv"), int(n_partials), _f32(bias, "bias"), _i32(positions, "positions"),
         _i32(token_row, "token_row"),
-        _i32(seq_end, "seq_end"), _f32(inv_freq, "inv_freq"), _ptr(q_out, "q_out"),
+        _i32(seq_end, "seq_end"), _f64(inv_freq, "inv_freq"), _ptr(q_out, "q_out"),
         _ptr(k_out, "k_out"), _ptr(v_out, "v_out"), _ptr(k_cache, "k_cache"),
         _ptr(v_cache, "v_cache"), _i32(page_table, "page_table"), int(table_stride), int(ring),
         n, n_heads, n_kv, head_dim, rotary_dim, style, dtype_code(dt), _i32(status, "status"),

@@ -148,7 +148,7 @@ class Norm(Part):
 
 class PositionEncoding(Part):
     def fused_rotary(self, device: torch.device) -> Optional[Tuple[torch.Tensor, int, int]]:
-        """(inv_freq float32 [rotary_dim/2], rotary_dim, style) for the fused rotary kernel,
+        """(inv_freq float64 [rotary_dim/2], rotary_dim, style) for the fused rotary kernel,
         or None if this encoding is not a rotation of pairs."""
         return None
 

@@ -3,9 +3,10 @@
 
 The reference (src/graph/cpu_backend.rs:403-434) rotates the whole head, pairs
 ``(i, i + hd/2)`` for its ``NonInterleaved`` style (Qwen2, src/models/qwen2/loader.rs:144)
-or ``(2i, 2i+1)`` for ``Interleaved`` (src/vec_ops.rs:6-14).  The inverse frequencies are
-made once in float64 and rounded to float32; the angle and its sine and cosine are float32
-on the device.
+or ``(2i, 2i+1)`` for ``Interleaved`` (src/vec_ops.rs:6-14).  The reference forms the angle
+``pos * freq`` in float32, which is off by about 1e-4 rad at position 2,000; here the inverse
+frequencies are kept in float64, the angle is formed and reduced modulo 2 pi in float64 on the
+device, and its sine and cosine are float32.
 """
 from __future__ import annotations
 
@@ -36,8 +37,8 @@ class Rotary(PositionEncoding):
 
     def inverse_frequencies(self) -> torch.Tensor:
         i = torch.arange(self.rotary_dim // 2, dtype=torch.float64)
-        return (self.frequency_scale / torch.pow(
-            torch.tensor(self.theta, dtype=torch.float64), 2.0 * i / self.rotary_dim)).to(torch.float32)
+        return self.frequency_scale / torch.pow(
+            torch.tensor(self.theta, dtype=torch.float64), 2.0 * i / self.rotary_dim)
 
     def fused_rotary(self, device: torch.device) -> Optional[Tuple[torch.Tensor, int, int]]:
         key = str(device)

@@ -40,7 +40,7 @@ TINY_D = {
     "num_attention_heads": 4, "num_key_value_heads": 2, "intermediate_size": 384,
     "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
     "use_sliding_window": True, "sliding_window": 40, "max_window_layers": 1,
-    "max_position_embeddings": 2048,
+    "max_position_embeddings": 4096,
 }
 TINY_E = {
     "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",

@@ -124,3 +124,30 @@ def test_decode_through_cuda_graphs_equals_kernel_by_kernel(tiny, dtype):
     want = P.forward(tiny["cfg"], P.load_folder(tiny["folder"])[1], ids)
     assert rel_err(outs[0][-1, 2], want[-1]) < TOL[dtype]
     assert rel_err(outs[0][150, 2], want[200 + 149]) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_sequence_many_tiles_and_chunks(dtype):
+    """2,100 tokens (33 query tiles, 9 key chunks, a window edge far from the start) whole,
+    then 40 more tokens one by one, with a second, short sequence beside it; against the
+    plain implementation at the places asked for."""
+    from minfer_b200.engine.step import Engine
+    from minfer_b200.model import Model
+    folder = make_folder("D")
+    cfg, w = P.load_folder(folder)
+    V = cfg["vocab_size"]
+    long_ids = random_ids(2140, V, 4242)
+    short_ids = random_ids(47, V, 4243)
+    want_long = P.forward(cfg, w, long_ids)
+    want_short = P.forward(cfg, w, short_ids)
+    eng = Engine(Model.from_folder(folder, dtype, "cuda:0"), max_tokens=2304 + 128)
+    a, b = eng.acquire(), eng.acquire()
+    places = [0, 63, 64, 1000, 2047, 2099]
+    out = eng.step([a, b], [long_ids[:2100], short_ids[:7]], [places, [6]])
+    assert rel_err(out[:6], want_long[places]) < TOL[dtype]
+    assert rel_err(out[6:], want_short[6:7]) < TOL[dtype]
+    for t in range(40):
+        out = eng.step([a, b], [[long_ids[2100 + t]], [short_ids[7 + t]]])
+        assert rel_err(out[0], want_long[2100 + t]) < TOL[dtype], t
+        assert rel_err(out[1], want_short[7 + t]) < TOL[dtype], t
+    eng.check_status()

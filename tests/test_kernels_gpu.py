@@ -116,7 +116,7 @@ def test_rope_kvstore_pages_and_rotation(hd, rotary_dim, style):
     rows = torch.tensor([0, 0, 0, 0, 0, 1, 1], dtype=torch.int32)
     T = 7
     qkv = torch.randn(T, (nh + 2 * nk) * hd)
-    inv_freq = (1.0 / (10000.0 ** (torch.arange(rotary_dim // 2).double() * 2 / rotary_dim))).float()
+    inv_freq = 1.0 / (10000.0 ** (torch.arange(rotary_dim // 2).double() * 2 / rotary_dim))
     n_pages = 6
     table = torch.tensor([[4, 2, -1], [5, 0, -1]], dtype=torch.int32)   # logical page -> physical
     for dt in DTYPES:
@@ -524,7 +524,7 @@ def test_deferred_split_sums_feed_the_next_kernel():
     pos = torch.arange(100, 100 + m, dtype=torch.int32, device="cuda")
     rows = torch.zeros(m, dtype=torch.int32, device="cuda")
     end = torch.tensor([100 + m], dtype=torch.int32, device="cuda")
-    inv_freq = (1.0 / (1e6 ** (torch.arange(hd // 2).double() * 2 / hd))).float().cuda()
+    inv_freq = (1.0 / (1e6 ** (torch.arange(hd // 2).double() * 2 / hd))).cuda()
     outs = []
     for src, npart, b in ((red, 0, None), (partial, partial.shape[0], bias)):
         q = torch.empty(m, nh, hd, dtype=torch.bfloat16, device="cuda")
