@@ -245,15 +245,19 @@ class Engine:
     # ---- decode steps replayed as CUDA graphs -------------------------------------------------
     def _graph_step(self, slots, tokens, starts, device_tokens: Optional[torch.Tensor]):
         """A one-token-per-sequence step through a captured graph.  The graph is keyed by the
-        number of rows and by a power-of-two bound on the sequences' lengths (which fixes the
+        number of rows and by a coarse bound on the sequences' lengths (which fixes the
         page tables' width and the number of key chunks); positions, slots, tokens and page
         tables are data in a buffer the graph reads, as positions are in the reference
         (src/graph/params.rs:10-60: the reuse identity has no n_past)."""
         n_rows = len(slots)
         max_end = max(starts) + 1
+        # a bound on the lengths: 256, 512, 1024, then multiples of 1024 (a new graph every 1024
+        # positions; key chunks beyond a sequence's end cost a launch and nothing else)
         cap = 256
-        while cap < max_end:
+        while cap < max_end and cap < 1024:
             cap *= 2
+        if cap < max_end:
+            cap = ((max_end + 1023) // 1024) * 1024
         key = (n_rows, cap)
         entry = self._graphs.get(key)
         if entry is None and key not in self._seen_shapes:

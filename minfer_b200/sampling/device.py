@@ -17,6 +17,8 @@ STATE_NAME = "sampler"
 
 
 class DeviceSampler:
+    RING = 8        # pinned token buffers in rotation
+
     def __init__(self, engine, params: SamplingParams):
         params.validate()
         self.engine = engine
@@ -33,6 +35,8 @@ class DeviceSampler:
         self._meta_dev = None
         self._meta_host = None
         self._copy_stream = torch.cuda.Stream(device=self.device)
+        self._pinned: list = []
+        self._next_pinned = 0
 
     def begin(self, slots: Sequence[int], prompts: Sequence[Sequence[int]]) -> None:
         """Seeds each sequence's window with the tail of its prompt (src/main.rs:537-540) and
@@ -74,7 +78,16 @@ class DeviceSampler:
         """Starts copying ``tokens`` to the host on a side stream; ``.get()`` waits for that
         copy only, not for whatever was launched after it."""
         self.engine.d2h_bytes += tokens.numel() * 4
-        return TokenFetch(tokens, self._copy_stream)
+        # pinned buffers are made once and reused in turn (allocating pinned memory is slow and
+        # synchronises with the device); a buffer comes around again after RING fetches, long
+        # after its tokens were read
+        n = tokens.numel()
+        if not self._pinned or self._pinned[0].numel() < n:
+            self._pinned = [torch.empty(max(n, 64), dtype=torch.int32).pin_memory()
+                            for _ in range(self.RING)]
+        host = self._pinned[self._next_pinned % self.RING][:n]
+        self._next_pinned += 1
+        return TokenFetch(tokens, self._copy_stream, host)
 
     def sample(self, logits: torch.Tensor, slots: Sequence[int],
                streams: Sequence[int]) -> List[int]:
@@ -85,8 +98,8 @@ class DeviceSampler:
 class TokenFetch:
     """A device-to-host copy of a few token ids that does not wait for later work."""
 
-    def __init__(self, tokens: torch.Tensor, copy_stream: torch.cuda.Stream):
-        self.host = torch.empty(tokens.shape, dtype=tokens.dtype).pin_memory()
+    def __init__(self, tokens: torch.Tensor, copy_stream: torch.cuda.Stream, host: torch.Tensor):
+        self.host = host
         self.done = torch.cuda.Event()
         ready = torch.cuda.Event()
         ready.record()                                  # after the sampling kernel
