@@ -176,8 +176,83 @@ def time_decode(engine, torch, K, batch, steps, warmup, prompt_len, seed=0):
     return ms / steps, launched
 
 
+CONFIG_05B = dict(CONFIG_7B, vocab_size=151936, hidden_size=896, num_hidden_layers=24,
+                  num_attention_heads=14, num_key_value_heads=2, intermediate_size=4864,
+                  tie_word_embeddings=True)
+CONFIG_14B = dict(CONFIG_7B, hidden_size=5120, num_hidden_layers=48, num_attention_heads=40,
+                  num_key_value_heads=8, intermediate_size=13824, rms_norm_eps=1e-5)
+
+
+def other_workload(name: str, steps: int) -> int:
+    """The two side workloads of the baseline: not the contract line, one JSON line of their own.
+    0.5b: 64 sequences with prompt lengths uniform in [16, 1024], 256 decoded tokens each,
+          through Generator.generate (host ids in and out).
+    14b:  prefill of one 8,192-token prompt, then decode at batch 8 from 8,192-token contexts."""
+    import torch
+    from minfer_b200.engine.generate import Generator
+    from minfer_b200.kernels import api as K
+    from minfer_b200.model import Model
+    from minfer_b200.sampling.params import SamplingParams
+    pk, pk_kind = peaks()
+    torch.cuda.set_device(0)
+    if name == "0.5b":
+        cfg = dict(CONFIG_05B)
+        model = Model.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0", make_on="device")
+        g = torch.Generator().manual_seed(3)
+        lens = torch.randint(16, 1025, (64,), generator=g).tolist()
+        prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+        gen = Generator(model, max_tokens=64 * 1280, max_batch=64)
+        gen.generate(prompts, 8, SamplingParams.greedy(), stop_token_ids=[])      # warm-up
+        gen.stats.__init__()
+        t0 = time.perf_counter()
+        out = gen.generate(prompts, 256, SamplingParams.greedy(), stop_token_ids=[])
+        wall = time.perf_counter() - t0
+        st = gen.stats
+        ms_step = st.decode_seconds / max(st.steps - 1, 1) * 1e3
+        mean_ctx = sum(lens) / 64 + 128
+        step_bytes = decode_bytes(model, 64, mean_ctx)
+        print(json.dumps({
+            "workload": "Qwen2.5-0.5B shape, 64 ragged prompts [16,1024], 256 new tokens each",
+            "decode_tokens_per_s": round(st.decode_tokens / st.decode_seconds, 1),
+            "ms_per_step": round(ms_step, 3), "prefill_tokens": st.prefill_tokens,
+            "prefill_tokens_per_s": round(st.prefill_tokens / st.prefill_seconds, 1),
+            "generated": sum(len(r.tokens) for r in out), "wall_s": round(wall, 3),
+            "roofline_frac": round(step_bytes / (ms_step * 1e-3) / 1e9 / pk["hbm_gbs"], 4),
+            "of": pk_kind}))
+        return 0
+    cfg = dict(CONFIG_14B)
+    model = Model.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0", make_on="device")
+    gen = Generator(model, max_tokens=8 * (8192 + 256), max_batch=8)
+    engine = gen.engine
+    g = torch.Generator().manual_seed(4)
+    ids = torch.randint(0, cfg["vocab_size"], (8192,), generator=g).tolist()
+    times = []
+    for _ in range(3):
+        s = engine.acquire()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        engine.step([s], [ids])
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+        engine.release(s)
+    ms_prefill = min(times[1:])
+    ms_step, _ = time_decode(engine, torch, K, 8, steps, 3, 8192)
+    step_bytes = decode_bytes(model, 8, 8192 + 3 + steps / 2)
+    print(json.dumps({
+        "workload": "Qwen2.5-14B shape, prefill 1 x 8192, decode batch 8 at 8192-token contexts",
+        "prefill_ms": round(ms_prefill, 2), "prefill_tokens_per_s": round(8192e3 / ms_prefill, 1),
+        "prefill_frac": round(prefill_flops(cfg, 8192) / (ms_prefill * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+        "decode_tokens_per_s": round(8e3 / ms_step, 1), "ms_per_step": round(ms_step, 3),
+        "roofline_frac": round(step_bytes / (ms_step * 1e-3) / 1e9 / pk["hbm_gbs"], 4), "of": pk_kind}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="7b", choices=["7b", "0.5b", "14b"],
+                    help="7b: the contract line; 0.5b and 14b: the baseline's side workloads")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
     ap.add_argument("--warmup", type=int, default=3)
@@ -196,6 +271,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.workload != "7b":
+        return other_workload(args.workload, max(1, args.steps))
 
     import torch
     from minfer_b200.engine.generate import Generator

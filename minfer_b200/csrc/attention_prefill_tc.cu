@@ -1,0 +1,456 @@
+// Attention of whole prompts on the 5th-generation tensor cores (bfloat16, head size 64 or 128):
+// causal, grouped query heads, optional window, sequences of unequal lengths packed one after
+// another.  Same formula as the other attention kernels (src/graph/cpu_backend.rs:437-494 in
+// the reference): scores * scale, mask by position, softmax in float32, weighted sum of values.
+//
+// A CTA owns 128 queries of one head and walks the keys in tiles of 128:
+//   S = Q K^T     tcgen05.mma, both operands in shared memory (TMA, 128-byte swizzle), S in
+//                 tensor memory; two S buffers, so the product for the next key tile runs
+//                 while the softmax of this one is still at work
+//   softmax       four warps, one thread per query row: the row of S comes out of tensor
+//                 memory, maximum / exp2 / sum in float32, and the probabilities go back into
+//                 the same columns as packed bfloat16
+//   O += P V      tcgen05.mma with P read from tensor memory as the A operand and V from
+//                 shared memory as an MN-major B operand; O stays in tensor memory and is
+//                 rescaled there by the softmax threads only when a row's maximum has grown
+//   warp 0: TMA producer (Q once, K and V double-buffered); warp 1: MMA issuer; warps 2-5:
+//   softmax and the final O / sum.
+// Rows of the packed tensors that lie beyond a sequence's end belong to the next sequence;
+// they are masked by position, never used.  Every mbarrier wait is bounded.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define FA_Q 128              // queries per CTA
+#define FA_KEYS 128           // keys per tile
+#define FA_THREADS 192
+#define FA_MAX_SPIN (1u << 24)
+#define FA_MAX_WAIT_NS 2000000000ull
+
+#define MF_ERR_NO_TENSORMAP 2003
+#define MF_ERR_TENSORMAP 2004
+
+struct FaArgs {
+    const int* cu_seqlens;
+    __nv_bfloat16* out;       // [tokens][n_heads * HD]
+    unsigned* status;
+    int n_heads, n_kv, window;
+    float scale_log2;         // scale * log2(e)
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t fa_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void fa_bar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void fa_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void fa_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool fa_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool fa_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    unsigned long long t0 = 0;
+    for (uint32_t it = 0; it < FA_MAX_SPIN; ++it) {
+        if (fa_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if ((it & 1023u) == 1023u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > FA_MAX_WAIT_NS) break;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void fa_tma(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fa_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fa_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fa_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void fa_mma_ss(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void fa_mma_ts(uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+        ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void fa_ld32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void fa_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void fa_st32(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void fa_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fa_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile whose rows are 128 bytes (64 bf16), 128-byte swizzle: 8-row groups
+// 1024 bytes apart.
+__device__ __forceinline__ uint64_t fa_desc_kmajor(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand (the values: rows are keys = the K dimension, 64 head dimensions = 128
+// bytes per row, 128-byte swizzle): the next 64 head dimensions lie `lbo` bytes further
+// (leading offset), 8-key groups 1024 bytes apart (stride offset).
+__device__ __forceinline__ uint64_t fa_desc_mnmajor(uint32_t addr, uint32_t lbo) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+__device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(FA_THREADS, 1)
+attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, const FaArgs a) {
+    pdl_prologue();
+    constexpr int NB = HD / 64;                         // 64-column blocks per row
+    constexpr int BLOCK = 128 * 128;                    // bytes of a [128 rows][64 cols] block
+    constexpr int Q_BYTES = NB * BLOCK, KV_BYTES = 2 * NB * BLOCK;
+    constexpr int TM_S0 = 0, TM_S1 = 128, TM_O = 256;   // tensor memory columns
+    extern __shared__ uint8_t fa_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)fa_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_s = smem;                                // [NB][128][64]
+    uint8_t* kv_s = smem + Q_BYTES;                     // [2 stages][K: NB blocks | V: NB blocks]
+    uint64_t* bars = (uint64_t*)(kv_s + 2 * KV_BYTES);
+    uint64_t* q_full = bars;                            // 1
+    uint64_t* kv_full = bars + 1;                       // [2]
+    uint64_t* kv_empty = bars + 3;                      // [2]
+    uint64_t* s_full = bars + 5;                        // [2]
+    uint64_t* p_full = bars + 7;                        // [2]  128 arrivals
+    uint64_t* pv_done = bars + 9;                       // 1
+    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int seq = blockIdx.z, head = blockIdx.y;
+    const int tok0 = a.cu_seqlens[seq];
+    const int len = a.cu_seqlens[seq + 1] - tok0;
+    const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;     // heavy tiles first
+    const int q0 = q_tile * FA_Q;
+    if (q0 >= len) return;
+    const int hk = head / (a.n_heads / a.n_kv);
+    const int q_last = min(q0 + FA_Q, len) - 1;
+    const int kt_begin = a.window > 0 ? max(0, q0 - a.window + 1) / FA_KEYS : 0;
+    const int n_tiles = q_last / FA_KEYS - kt_begin + 1;
+
+    if (tid == 0) {
+        fa_bar_init(fa_smem(q_full), 1);
+        for (int i = 0; i < 2; ++i) {
+            fa_bar_init(fa_smem(&kv_full[i]), 1);
+            fa_bar_init(fa_smem(&kv_empty[i]), 1);
+            fa_bar_init(fa_smem(&s_full[i]), 1);
+            fa_bar_init(fa_smem(&p_full[i]), 128);
+        }
+        fa_bar_init(fa_smem(pv_done), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(fa_smem(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    fa_fence_before();
+    __syncthreads();
+    fa_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer ---------------------------------------------------------------
+        fa_expect_tx(fa_smem(q_full), Q_BYTES);
+        for (int c = 0; c < NB; ++c)
+            fa_tma(fa_smem(q_s + c * BLOCK), &map_q, head * HD + 64 * c, tok0 + q0, fa_smem(q_full));
+        for (int j = 0; j < n_tiles; ++j) {
+            const int st = j & 1;
+            if (!fa_wait(fa_smem(&kv_empty[st]), (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag)) break;
+            const uint32_t full = fa_smem(&kv_full[st]);
+            fa_expect_tx(full, KV_BYTES);
+            const int key0 = tok0 + (kt_begin + j) * FA_KEYS;
+            uint8_t* dst = kv_s + st * KV_BYTES;
+            for (int c = 0; c < NB; ++c) {
+                fa_tma(fa_smem(dst + c * BLOCK), &map_k, hk * HD + 64 * c, key0, full);
+                fa_tma(fa_smem(dst + (NB + c) * BLOCK), &map_v, hk * HD + 64 * c, key0, full);
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer -------------------------------------------------------------------
+        // S: M = 128 queries, N = 128 keys, both operands K-major
+        constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FA_KEYS >> 3) << 17) |
+                                     ((uint32_t)(128 >> 4) << 24);
+        // O: M = 128 queries, N = HD, A from tensor memory, B MN-major
+        constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                                     ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        bool ok = fa_wait(fa_smem(q_full), 0u, abort_flag);
+        auto issue_qk = [&](int j) {
+            const int st = j & 1;
+            const uint32_t k_addr = fa_smem(kv_s + st * KV_BYTES);
+            const uint32_t d = tmem + (uint32_t)((j & 1) ? TM_S1 : TM_S0);
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks) {
+                const uint32_t off = (uint32_t)((ks >> 2) * BLOCK + (ks & 3) * 32);
+                fa_mma_ss(d, fa_desc_kmajor(fa_smem(q_s) + off), fa_desc_kmajor(k_addr + off), idesc_s,
+                          ks > 0 ? 1u : 0u);
+            }
+            fa_commit(fa_smem(&s_full[j & 1]));
+        };
+        if (ok) ok = fa_wait(fa_smem(&kv_full[0]), 0u, abort_flag);
+        if (ok) {
+            fa_fence_after();
+            issue_qk(0);
+        }
+        for (int j = 0; j < n_tiles && ok; ++j) {
+            if (j + 1 < n_tiles) {
+                ok = fa_wait(fa_smem(&kv_full[(j + 1) & 1]), (uint32_t)(((j + 1) >> 1) & 1), abort_flag);
+                if (!ok) break;
+                fa_fence_after();
+                issue_qk(j + 1);
+            }
+            ok = fa_wait(fa_smem(&p_full[j & 1]), (uint32_t)((j >> 1) & 1), abort_flag);
+            if (!ok) break;
+            fa_fence_after();
+            const uint32_t v_addr = fa_smem(kv_s + (j & 1) * KV_BYTES + NB * BLOCK);
+            const uint32_t p_tmem = tmem + (uint32_t)((j & 1) ? TM_S1 : TM_S0);
+#pragma unroll
+            for (int ks = 0; ks < FA_KEYS / 16; ++ks)
+                fa_mma_ts(tmem + TM_O, p_tmem + (uint32_t)(ks * 8),
+                          fa_desc_mnmajor(v_addr + (uint32_t)(ks * 16 * 128), BLOCK), idesc_o,
+                          (j > 0 || ks > 0) ? 1u : 0u);
+            fa_commit(fa_smem(&kv_empty[j & 1]));
+            fa_commit(fa_smem(pv_done));
+        }
+    } else if (warp >= 2) {
+        // ---- softmax: one thread per query row ----------------------------------------------
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;             // row of the tile = TMEM lane
+        const int qpos = q0 + row;
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        float m = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_tiles; ++j) {
+            const int key0 = (kt_begin + j) * FA_KEYS;
+            const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) ? TM_S1 : TM_S0);
+            if (!fa_wait(fa_smem(&s_full[j & 1]), (uint32_t)((j >> 1) & 1), abort_flag)) { ok = false; break; }
+            fa_fence_after();
+            const bool need_mask = key0 + FA_KEYS - 1 > q0 + quarter * 32 || key0 + FA_KEYS > len ||
+                                   (a.window > 0 && key0 < q0 + quarter * 32 + 31 - a.window + 1);
+            // the whole row of S (128 scores) into registers, masked by position where the tile
+            // touches the diagonal, the window's edge or the sequence's end
+            uint32_t sr[FA_KEYS];
+#pragma unroll
+            for (int c0 = 0; c0 < FA_KEYS; c0 += 32) fa_ld32(s_addr + (uint32_t)c0, sr + c0);
+            fa_wait_ld();
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < FA_KEYS; ++i) {
+                    const int key = key0 + i;
+                    const bool vis = key <= qpos && key < len && (a.window == 0 || qpos - key < a.window);
+                    if (!vis) sr[i] = 0xff800000u;            // -inf
+                }
+            }
+            // the maximum with four independent chains
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < FA_KEYS; i += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
+            }
+            const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            const float m_new = fmaxf(m, m_tile);
+            const float m_off = m_new == -INFINITY ? 0.0f : m_new * a.scale_log2;
+            const float corr = m == -INFINITY ? 0.0f : exp2f(m * a.scale_log2 - m_off);
+            // the output so far is rescaled only if some row of this warp has a new maximum
+            const bool grow = m_new > m;
+            if (j > 0) {
+                if (!fa_wait(fa_smem(pv_done), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; break; }
+                fa_fence_after();
+                if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        uint32_t r[32];
+                        fa_ld32(lane_addr + (uint32_t)(TM_O + c0), r);
+                        fa_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+                        fa_st32(lane_addr + (uint32_t)(TM_O + c0), r);
+                    }
+                }
+            }
+            m = m_new;
+            // probabilities (ex2.approx of the scaled difference), their sum with four chains,
+            // packed as bfloat16 pairs into the first 64 columns of this S buffer
+            float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+            uint32_t pk[FA_KEYS / 2];
+#pragma unroll
+            for (int i = 0; i < FA_KEYS; i += 4) {
+                float p0, p1, p2, p3;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(sr[i]), a.scale_log2, -m_off)));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -m_off)));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p2) : "f"(fmaf(__uint_as_float(sr[i + 2]), a.scale_log2, -m_off)));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p3) : "f"(fmaf(__uint_as_float(sr[i + 3]), a.scale_log2, -m_off)));
+                l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+                pk[i >> 1] = fa_pack(p0, p1);
+                pk[(i >> 1) + 1] = fa_pack(p2, p3);
+            }
+            l = l * corr + ((l0 + l1) + (l2 + l3));
+#pragma unroll
+            for (int c0 = 0; c0 < FA_KEYS / 2; c0 += 32) fa_st32(s_addr + (uint32_t)c0, pk + c0);
+            fa_wait_st();
+            fa_fence_before();
+            fa_arrive(fa_smem(&p_full[j & 1]));
+        }
+        // ---- the result: O / sum -------------------------------------------------------------
+        if (ok && fa_wait(fa_smem(pv_done), (uint32_t)((n_tiles - 1) & 1), abort_flag)) {
+            fa_fence_after();
+            const float inv = 1.0f / l;
+            __nv_bfloat16* o = a.out + ((long long)(tok0 + qpos) * a.n_heads + head) * HD;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t r[32];
+                fa_ld32(lane_addr + (uint32_t)(TM_O + c0), r);
+                fa_wait_ld();
+                if (qpos < len) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        v.x = fa_pack(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                        v.y = fa_pack(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                        v.z = fa_pack(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                        v.w = fa_pack(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(o + c0 + i) = v;
+                    }
+                }
+            }
+        }
+    }
+    __syncwarp();
+    fa_fence_before();
+    __syncthreads();
+    if (*abort_flag && tid == 0) {
+        atomicOr(a.status, MF_STATUS_WAIT_TIMEOUT);
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+    }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+typedef CUresult (*FaEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                               CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                               CUtensorMapFloatOOBfill);
+
+static FaEncodeFn fa_encode_fn() {
+    static FaEncodeFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (FaEncodeFn)p;
+    }
+    return fn;
+}
+
+// [tokens][width] bf16, box = [128 rows][64 columns]
+static int fa_map(CUtensorMap* map, const void* ptr, long long tokens, long long width) {
+    FaEncodeFn fn = fa_encode_fn();
+    if (!fn) return MF_ERR_NO_TENSORMAP;
+    cuuint64_t dims[2] = {(cuuint64_t)width, (cuuint64_t)tokens};
+    cuuint64_t strides[1] = {(cuuint64_t)width * 2};
+    cuuint32_t box[2] = {64, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : MF_ERR_TENSORMAP;
+}
+
+template <int HD>
+static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaArgs& a,
+                     int n_seqs, int max_len, cudaStream_t stream) {
+    constexpr int smem = (HD / 64) * 16384 * 5 + 1024 + 256;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid((max_len + FA_Q - 1) / FA_Q, a.n_heads, n_seqs);
+    mf_launch(attention_prefill_tc_kernel<HD>, grid, dim3(FA_THREADS), smem, stream, mq, mk, mv, a);
+    return MF_LAUNCH_CHECK();
+}
+
+// q [tokens][n_heads][hd], k/v [tokens][n_kv][hd], out [tokens][n_heads*hd], all bfloat16 and
+// contiguous; sequence b holds tokens cu_seqlens[b] .. cu_seqlens[b+1]-1 at positions 0, 1, ...
+extern "C" int mf_attention_prefill_tc(const void* q, const void* k, const void* v, const int* cu_seqlens,
+                                       void* out, int n_tokens, int n_seqs, int max_len, int n_heads,
+                                       int n_kv, int hd, int window, float scale, unsigned* status,
+                                       cudaStream_t stream) {
+    if (n_seqs <= 0 || max_len <= 0 || n_tokens <= 0) return 0;
+    if ((hd != 64 && hd != 128) || n_kv <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
+    if (n_heads > 65535 || n_seqs > 65535) return MF_ERR_UNSUPPORTED;
+    if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || ((uintptr_t)out & 15))
+        return MF_ERR_UNSUPPORTED;
+    CUtensorMap mq, mk, mv;
+    if (int e = fa_map(&mq, q, n_tokens, (long long)n_heads * hd)) return e;
+    if (int e = fa_map(&mk, k, n_tokens, (long long)n_kv * hd)) return e;
+    if (int e = fa_map(&mv, v, n_tokens, (long long)n_kv * hd)) return e;
+    FaArgs a;
+    a.cu_seqlens = cu_seqlens; a.out = (__nv_bfloat16*)out; a.status = status;
+    a.n_heads = n_heads; a.n_kv = n_kv; a.window = window;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    return hd == 64 ? fa_launch<64>(mq, mk, mv, a, n_seqs, max_len, stream)
+                    : fa_launch<128>(mq, mk, mv, a, n_seqs, max_len, stream);
+}

@@ -135,7 +135,12 @@ def _sig_attention_prefill(lib: ctypes.CDLL) -> None:
     lib.mf_attention_prefill_mma.argtypes = [c_void_p] * 5 + [c_int] * 6 + [c_float, c_void_p]
 
 
-_SIGNATURES = {"attention_prefill": _sig_attention_prefill, "gemm_tc": _sig_gemm_tc, "ops": _sig_ops, "gemm_simt": _sig_gemm_simt, "attention": _sig_attention,
+def _sig_attention_prefill_tc(lib: ctypes.CDLL) -> None:
+    lib.mf_attention_prefill_tc.argtypes = [c_void_p] * 5 + [c_int] * 7 + [c_float, c_void_p, c_void_p]
+
+
+_SIGNATURES = {"attention_prefill_tc": _sig_attention_prefill_tc,
+               "attention_prefill": _sig_attention_prefill, "gemm_tc": _sig_gemm_tc, "ops": _sig_ops, "gemm_simt": _sig_gemm_simt, "attention": _sig_attention,
                "sampling": _sig_sampling}
 
 
@@ -380,6 +385,19 @@ def attention_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seql
         _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v"), _i32(cu_seqlens, "cu_seqlens"), _ptr(out, "out"),
         int(n_seqs), int(max_len), n_heads, n_kv, head_dim, int(window), float(scale), _stream()),
         "attention_prefill")
+
+
+def attention_prefill_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor,
+                         out: torch.Tensor, n_seqs: int, max_len: int, n_heads: int, n_kv: int,
+                         head_dim: int, window: int, scale: float, status: torch.Tensor) -> None:
+    """The same attention of whole sequences on tcgen05 (S and O in tensor memory)."""
+    for t in (q, k, v, out):
+        if t.dtype != torch.bfloat16:
+            raise KernelError("attention_prefill_tc takes bfloat16")
+    _check(_lib("attention_prefill_tc").mf_attention_prefill_tc(
+        _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v"), _i32(cu_seqlens, "cu_seqlens"), _ptr(out, "out"),
+        int(q.shape[0]), int(n_seqs), int(max_len), n_heads, n_kv, head_dim, int(window), float(scale),
+        _i32(status, "status"), _stream()), "attention_prefill_tc")
 
 
 def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -34,6 +34,7 @@ LIBRARIES = {
     "sampling": ("sampling.cu", []),
     "gemm_tc": ("gemm_tc.cu", []),
     "attention_prefill": ("attention_prefill.cu", []),
+    "attention_prefill_tc": ("attention_prefill_tc.cu", []),
 }
 
 

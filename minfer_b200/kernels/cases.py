@@ -123,6 +123,41 @@ def attention_prefill(reps, tokens=2048):
     print(f"attention prefill tokens={tokens}: {us:.1f} us, {flops / us / 1e6:.1f} TFLOP/s (causal)")
 
 
+def attention_prefill_tc(reps, tokens=2048, heads=NH, kv=NK):
+    """The same prompt attention on tcgen05 (S and O in tensor memory)."""
+    q = torch.randn(tokens, heads, HD, device="cuda").bfloat16()
+    k = torch.randn(tokens, kv, HD, device="cuda").bfloat16()
+    v = torch.randn(tokens, kv, HD, device="cuda").bfloat16()
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device="cuda")
+    out = torch.empty(tokens, heads * HD, dtype=torch.bfloat16, device="cuda")
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    us = _time(lambda: K.attention_prefill_tc(q, k, v, cu, out, 1, tokens, heads, kv, HD, 0,
+                                              1 / math.sqrt(HD), st), reps)
+    flops = heads * 4 * HD * tokens * (tokens + 1) / 2
+    print(f"attention prefill (tcgen05) tokens={tokens} heads={heads}: {us:.1f} us, "
+          f"{flops / us / 1e6:.1f} TFLOP/s (causal)")
+
+
+def attention_prefill_tc_8k(reps):
+    """Prompt attention on tcgen05 at 8,192 tokens, 40 heads / 8 KV heads (the 14B shape)."""
+    attention_prefill_tc(reps, tokens=8192, heads=40, kv=8)
+
+
+def attention_prefill_8k(reps):
+    """Prompt attention on mma.sync at 8,192 tokens, 40 heads / 8 KV heads (the 14B shape)."""
+    tokens, heads, kv = 8192, 40, 8
+    q = torch.randn(tokens, heads, HD, device="cuda").bfloat16()
+    k = torch.randn(tokens, kv, HD, device="cuda").bfloat16()
+    v = torch.randn(tokens, kv, HD, device="cuda").bfloat16()
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device="cuda")
+    out = torch.empty(tokens, heads * HD, dtype=torch.bfloat16, device="cuda")
+    us = _time(lambda: K.attention_prefill(q, k, v, cu, out, 1, tokens, heads, kv, HD, 0,
+                                           1 / math.sqrt(HD)), reps)
+    flops = heads * 4 * HD * tokens * (tokens + 1) / 2
+    print(f"attention prefill (mma.sync) tokens={tokens} heads={heads}: {us:.1f} us, "
+          f"{flops / us / 1e6:.1f} TFLOP/s (causal)")
+
+
 def _engine(layers):
     from ..engine.step import Engine
     from ..model import Model
@@ -159,6 +194,7 @@ def step_decode(reps, layers=4):
 
 CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_prefill, gemm_prefill_down,
                                  attention_decode, attention_decode_b8, attention_prefill,
+                                 attention_prefill_tc, attention_prefill_tc_8k, attention_prefill_8k,
                                  step_prefill, step_decode)}
 
 
