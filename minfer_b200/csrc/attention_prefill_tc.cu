@@ -21,9 +21,10 @@
 
 #include "common.cuh"
 
-#define FA_Q 128              // queries per CTA
+#define FA_Q 128              // queries per tile
+#define FA_CTA_Q 256          // a CTA owns two query tiles that share every key tile
 #define FA_KEYS 128           // keys per tile
-#define FA_THREADS 192
+#define FA_THREADS 384        // warp 0 TMA, warp 1 MMA, warps 4-7 and 8-11 softmax of the two query tiles
 #define FA_MAX_SPIN (1u << 24)
 #define FA_MAX_WAIT_NS 2000000000ull
 
@@ -149,43 +150,59 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     pdl_prologue();
     constexpr int NB = HD / 64;                         // 64-column blocks per row
     constexpr int BLOCK = 128 * 128;                    // bytes of a [128 rows][64 cols] block
-    constexpr int Q_BYTES = NB * BLOCK, KV_BYTES = 2 * NB * BLOCK;
-    constexpr int TM_S0 = 0, TM_S1 = 128, TM_O = 256;   // tensor memory columns
+    constexpr int T_BYTES = NB * BLOCK;                 // a [128 rows][HD] tile
+    constexpr int TM_S = 0, TM_O = 256;                 // tensor memory columns; tile t: + 128 t
     extern __shared__ uint8_t fa_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)fa_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* q_s = smem;                                // [NB][128][64]
-    uint8_t* kv_s = smem + Q_BYTES;                     // [2 stages][K: NB blocks | V: NB blocks]
-    uint64_t* bars = (uint64_t*)(kv_s + 2 * KV_BYTES);
+    uint8_t* q_s = smem;                                // [2 query tiles][NB][128][64]
+    uint8_t* k_s = q_s + 2 * T_BYTES;                   // [2 stages]
+    uint8_t* v_s = k_s + 2 * T_BYTES;                   // [2 stages]
+    uint64_t* bars = (uint64_t*)(v_s + 2 * T_BYTES);
     uint64_t* q_full = bars;                            // 1
-    uint64_t* kv_full = bars + 1;                       // [2]
-    uint64_t* kv_empty = bars + 3;                      // [2]
-    uint64_t* s_full = bars + 5;                        // [2]
-    uint64_t* p_full = bars + 7;                        // [2]  128 arrivals
-    uint64_t* pv_done = bars + 9;                       // 1
-    uint32_t* tmem_slot = (uint32_t*)(bars + 10);
+    uint64_t* k_full = bars + 1;                        // [2 stages]
+    uint64_t* k_empty = bars + 3;
+    uint64_t* v_full = bars + 5;
+    uint64_t* v_empty = bars + 7;
+    uint64_t* s_full = bars + 9;                        // [2 query tiles]
+    uint64_t* p_full = bars + 11;                       // [2 query tiles], 128 arrivals
+    uint64_t* o_done = bars + 13;                       // [2 query tiles]
+    uint32_t* tmem_slot = (uint32_t*)(bars + 15);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int seq = blockIdx.z, head = blockIdx.y;
+    const int seq = blockIdx.z, head = blockIdx.x;
     const int tok0 = a.cu_seqlens[seq];
     const int len = a.cu_seqlens[seq + 1] - tok0;
-    const int q_tile = (int)gridDim.x - 1 - (int)blockIdx.x;     // heavy tiles first
-    const int q0 = q_tile * FA_Q;
+    const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * FA_CTA_Q;     // heavy tiles first
     if (q0 >= len) return;
     const int hk = head / (a.n_heads / a.n_kv);
-    const int q_last = min(q0 + FA_Q, len) - 1;
-    const int kt_begin = a.window > 0 ? max(0, q0 - a.window + 1) / FA_KEYS : 0;
-    const int n_tiles = q_last / FA_KEYS - kt_begin + 1;
+    // the key tiles of each query tile: [kb, ke); the second tile may be beyond the sequence
+    int kb[2], ke[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        const int q0t = q0 + t * FA_Q;
+        if (q0t < len) {
+            kb[t] = a.window > 0 ? max(0, q0t - a.window + 1) / FA_KEYS : 0;
+            ke[t] = (min(q0t + FA_Q, len) - 1) / FA_KEYS + 1;
+        } else {
+            kb[t] = ke[t] = 0;
+        }
+    }
+    const bool has1 = ke[1] > kb[1];
+    const int lo = kb[0], hi = has1 ? ke[1] : ke[0];
+    const int n_tiles = hi - lo;
 
     if (tid == 0) {
         fa_bar_init(fa_smem(q_full), 1);
         for (int i = 0; i < 2; ++i) {
-            fa_bar_init(fa_smem(&kv_full[i]), 1);
-            fa_bar_init(fa_smem(&kv_empty[i]), 1);
+            fa_bar_init(fa_smem(&k_full[i]), 1);
+            fa_bar_init(fa_smem(&k_empty[i]), 1);
+            fa_bar_init(fa_smem(&v_full[i]), 1);
+            fa_bar_init(fa_smem(&v_empty[i]), 1);
             fa_bar_init(fa_smem(&s_full[i]), 1);
             fa_bar_init(fa_smem(&p_full[i]), 128);
+            fa_bar_init(fa_smem(&o_done[i]), 1);
         }
-        fa_bar_init(fa_smem(pv_done), 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -200,24 +217,34 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     fa_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 0 && lane == 0) {
+    // Registers: the kernel is compiled for 168 a thread (three warps on a scheduler); the first
+    // warpgroup gives most of its share back and the softmax warpgroups, which hold a whole
+    // row of scores each, take it.
+    if (warp < 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      if (warp == 0 && lane == 0) {
         // ---- TMA producer ---------------------------------------------------------------
-        fa_expect_tx(fa_smem(q_full), Q_BYTES);
-        for (int c = 0; c < NB; ++c)
-            fa_tma(fa_smem(q_s + c * BLOCK), &map_q, head * HD + 64 * c, tok0 + q0, fa_smem(q_full));
-        for (int j = 0; j < n_tiles; ++j) {
-            const int st = j & 1;
-            if (!fa_wait(fa_smem(&kv_empty[st]), (uint32_t)((j >> 1) & 1) ^ 1u, abort_flag)) break;
-            const uint32_t full = fa_smem(&kv_full[st]);
-            fa_expect_tx(full, KV_BYTES);
-            const int key0 = tok0 + (kt_begin + j) * FA_KEYS;
-            uint8_t* dst = kv_s + st * KV_BYTES;
-            for (int c = 0; c < NB; ++c) {
-                fa_tma(fa_smem(dst + c * BLOCK), &map_k, hk * HD + 64 * c, key0, full);
-                fa_tma(fa_smem(dst + (NB + c) * BLOCK), &map_v, hk * HD + 64 * c, key0, full);
-            }
+        fa_expect_tx(fa_smem(q_full), has1 ? 2 * T_BYTES : T_BYTES);
+        for (int t = 0; t < (has1 ? 2 : 1); ++t)
+            for (int c = 0; c < NB; ++c)
+                fa_tma(fa_smem(q_s + t * T_BYTES + c * BLOCK), &map_q, head * HD + 64 * c,
+                       tok0 + q0 + t * FA_Q, fa_smem(q_full));
+        for (int i = 0; i < n_tiles; ++i) {
+            const int st = i & 1;
+            const uint32_t free_parity = (uint32_t)((i >> 1) & 1) ^ 1u;
+            const int key0 = tok0 + (lo + i) * FA_KEYS;
+            if (!fa_wait(fa_smem(&k_empty[st]), free_parity, abort_flag)) break;
+            fa_expect_tx(fa_smem(&k_full[st]), T_BYTES);
+            for (int c = 0; c < NB; ++c)
+                fa_tma(fa_smem(k_s + st * T_BYTES + c * BLOCK), &map_k, hk * HD + 64 * c, key0,
+                       fa_smem(&k_full[st]));
+            if (!fa_wait(fa_smem(&v_empty[st]), free_parity, abort_flag)) break;
+            fa_expect_tx(fa_smem(&v_full[st]), T_BYTES);
+            for (int c = 0; c < NB; ++c)
+                fa_tma(fa_smem(v_s + st * T_BYTES + c * BLOCK), &map_v, hk * HD + 64 * c, key0,
+                       fa_smem(&v_full[st]));
         }
-    } else if (warp == 1 && lane == 0) {
+      } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer -------------------------------------------------------------------
         // S: M = 128 queries, N = 128 keys, both operands K-major
         constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(FA_KEYS >> 3) << 17) |
@@ -225,59 +252,83 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // O: M = 128 queries, N = HD, A from tensor memory, B MN-major
         constexpr uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
                                      ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-        bool ok = fa_wait(fa_smem(q_full), 0u, abort_flag);
-        auto issue_qk = [&](int j) {
-            const int st = j & 1;
-            const uint32_t k_addr = fa_smem(kv_s + st * KV_BYTES);
-            const uint32_t d = tmem + (uint32_t)((j & 1) ? TM_S1 : TM_S0);
+        auto issue_qk = [&](int t, int i) {
+            const uint32_t q_addr = fa_smem(q_s + t * T_BYTES);
+            const uint32_t k_addr = fa_smem(k_s + (i & 1) * T_BYTES);
 #pragma unroll
             for (int ks = 0; ks < HD / 16; ++ks) {
                 const uint32_t off = (uint32_t)((ks >> 2) * BLOCK + (ks & 3) * 32);
-                fa_mma_ss(d, fa_desc_kmajor(fa_smem(q_s) + off), fa_desc_kmajor(k_addr + off), idesc_s,
-                          ks > 0 ? 1u : 0u);
+                fa_mma_ss(tmem + (uint32_t)(TM_S + t * 128), fa_desc_kmajor(q_addr + off),
+                          fa_desc_kmajor(k_addr + off), idesc_s, ks > 0 ? 1u : 0u);
             }
-            fa_commit(fa_smem(&s_full[j & 1]));
+            fa_commit(fa_smem(&s_full[t]));
         };
-        if (ok) ok = fa_wait(fa_smem(&kv_full[0]), 0u, abort_flag);
+        int done[2] = {0, 0};                            // products P V issued for each query tile
+        bool ok = fa_wait(fa_smem(q_full), 0u, abort_flag);
+        if (ok) ok = fa_wait(fa_smem(&k_full[0]), 0u, abort_flag);
         if (ok) {
             fa_fence_after();
-            issue_qk(0);
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+                if (lo >= kb[t] && lo < ke[t]) issue_qk(t, 0);
+            fa_commit(fa_smem(&k_empty[0]));
         }
-        for (int j = 0; j < n_tiles && ok; ++j) {
-            if (j + 1 < n_tiles) {
-                ok = fa_wait(fa_smem(&kv_full[(j + 1) & 1]), (uint32_t)(((j + 1) >> 1) & 1), abort_flag);
-                if (!ok) break;
-                fa_fence_after();
-                issue_qk(j + 1);
-            }
-            ok = fa_wait(fa_smem(&p_full[j & 1]), (uint32_t)((j >> 1) & 1), abort_flag);
+        // per key tile and query tile: O += P V for this key tile as soon as its probabilities
+        // are there, then at once S = Q K^T for the next key tile into the same columns; while
+        // one query tile is in its softmax the tensor cores work for the other
+        for (int i = 0; i < n_tiles && ok; ++i) {
+            const int j = lo + i;
+            const bool next = i + 1 < n_tiles;
+            ok = fa_wait(fa_smem(&v_full[i & 1]), (uint32_t)((i >> 1) & 1), abort_flag);
+            if (ok && next) ok = fa_wait(fa_smem(&k_full[(i + 1) & 1]), (uint32_t)(((i + 1) >> 1) & 1), abort_flag);
             if (!ok) break;
             fa_fence_after();
-            const uint32_t v_addr = fa_smem(kv_s + (j & 1) * KV_BYTES + NB * BLOCK);
-            const uint32_t p_tmem = tmem + (uint32_t)((j & 1) ? TM_S1 : TM_S0);
+            const uint32_t v_addr = fa_smem(v_s + (i & 1) * T_BYTES);
 #pragma unroll
-            for (int ks = 0; ks < FA_KEYS / 16; ++ks)
-                fa_mma_ts(tmem + TM_O, p_tmem + (uint32_t)(ks * 8),
-                          fa_desc_mnmajor(v_addr + (uint32_t)(ks * 16 * 128), BLOCK), idesc_o,
-                          (j > 0 || ks > 0) ? 1u : 0u);
-            fa_commit(fa_smem(&kv_empty[j & 1]));
-            fa_commit(fa_smem(pv_done));
+            for (int t = 0; t < 2; ++t) {
+                const bool cur = j >= kb[t] && j < ke[t];
+                const bool nxt = next && j + 1 >= kb[t] && j + 1 < ke[t];
+                if (cur) {
+                    ok = fa_wait(fa_smem(&p_full[t]), (uint32_t)(done[t] & 1), abort_flag);
+                    if (!ok) break;
+                    fa_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < FA_KEYS / 16; ++ks)
+                        fa_mma_ts(tmem + (uint32_t)(TM_O + t * 128), tmem + (uint32_t)(TM_S + t * 128 + ks * 8),
+                                  fa_desc_mnmajor(v_addr + (uint32_t)(ks * 16 * 128), BLOCK), idesc_o,
+                                  (done[t] > 0 || ks > 0) ? 1u : 0u);
+                    ++done[t];
+                }
+                if (nxt) issue_qk(t, i + 1);
+                else if (cur) fa_commit(fa_smem(&o_done[t]));
+            }
+            if (!ok) break;
+            fa_commit(fa_smem(&v_empty[i & 1]));
+            if (next) fa_commit(fa_smem(&k_empty[(i + 1) & 1]));
         }
-    } else if (warp >= 2) {
-        // ---- softmax: one thread per query row ----------------------------------------------
-        const int quarter = warp & 3;
+      }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        // ---- softmax: four warps for each query tile, one thread per query row ----------------
+        const int t = (warp - 4) >> 2;
+        const int quarter = warp & 3;                    // the 32 TMEM lanes this warp may touch
         const int row = quarter * 32 + lane;             // row of the tile = TMEM lane
-        const int qpos = q0 + row;
+        const int q0t = q0 + t * FA_Q;
+        const int qpos = q0t + row;
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t s_addr = lane_addr + (uint32_t)(TM_S + t * 128);
+        const uint32_t o_addr = lane_addr + (uint32_t)(TM_O + t * 128);
+        const int kb_t = t ? kb[1] : kb[0], ke_t = t ? ke[1] : ke[0];
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
-        for (int j = 0; j < n_tiles; ++j) {
-            const int key0 = (kt_begin + j) * FA_KEYS;
-            const uint32_t s_addr = lane_addr + (uint32_t)((j & 1) ? TM_S1 : TM_S0);
-            if (!fa_wait(fa_smem(&s_full[j & 1]), (uint32_t)((j >> 1) & 1), abort_flag)) { ok = false; break; }
+        for (int j = kb_t; j < ke_t; ++j) {
+            const int c = j - kb_t;
+            const int key0 = j * FA_KEYS;
+            // S of this key tile is complete, and with it every earlier product of this query tile
+            if (!fa_wait(fa_smem(&s_full[t]), (uint32_t)(c & 1), abort_flag)) { ok = false; break; }
             fa_fence_after();
-            const bool need_mask = key0 + FA_KEYS - 1 > q0 + quarter * 32 || key0 + FA_KEYS > len ||
-                                   (a.window > 0 && key0 < q0 + quarter * 32 + 31 - a.window + 1);
+            const bool need_mask = key0 + FA_KEYS - 1 > q0t + quarter * 32 || key0 + FA_KEYS > len ||
+                                   (a.window > 0 && key0 < q0t + quarter * 32 + 31 - a.window + 1);
             // the whole row of S (128 scores) into registers, masked by position where the tile
             // touches the diagonal, the window's edge or the sequence's end
             uint32_t sr[FA_KEYS];
@@ -307,19 +358,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const float corr = m == -INFINITY ? 0.0f : exp2f(m * a.scale_log2 - m_off);
             // the output so far is rescaled only if some row of this warp has a new maximum
             const bool grow = m_new > m;
-            if (j > 0) {
-                if (!fa_wait(fa_smem(pv_done), (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; break; }
-                fa_fence_after();
-                if (__any_sync(0xffffffffu, grow)) {
+            if (c > 0 && __any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < HD; c0 += 32) {
-                        uint32_t r[32];
-                        fa_ld32(lane_addr + (uint32_t)(TM_O + c0), r);
-                        fa_wait_ld();
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t r[32];
+                    fa_ld32(o_addr + (uint32_t)c0, r);
+                    fa_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-                        fa_st32(lane_addr + (uint32_t)(TM_O + c0), r);
-                    }
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+                    fa_st32(o_addr + (uint32_t)c0, r);
                 }
             }
             m = m_new;
@@ -343,17 +390,17 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int c0 = 0; c0 < FA_KEYS / 2; c0 += 32) fa_st32(s_addr + (uint32_t)c0, pk + c0);
             fa_wait_st();
             fa_fence_before();
-            fa_arrive(fa_smem(&p_full[j & 1]));
+            fa_arrive(fa_smem(&p_full[t]));
         }
         // ---- the result: O / sum -------------------------------------------------------------
-        if (ok && fa_wait(fa_smem(pv_done), (uint32_t)((n_tiles - 1) & 1), abort_flag)) {
+        if (ok && ke_t > kb_t && fa_wait(fa_smem(&o_done[t]), 0u, abort_flag)) {
             fa_fence_after();
             const float inv = 1.0f / l;
             __nv_bfloat16* o = a.out + ((long long)(tok0 + qpos) * a.n_heads + head) * HD;
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 32) {
                 uint32_t r[32];
-                fa_ld32(lane_addr + (uint32_t)(TM_O + c0), r);
+                fa_ld32(o_addr + (uint32_t)c0, r);
                 fa_wait_ld();
                 if (qpos < len) {
 #pragma unroll
@@ -419,7 +466,7 @@ static int fa_map(CUtensorMap* map, const void* ptr, long long tokens, long long
 template <int HD>
 static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaArgs& a,
                      int n_seqs, int max_len, cudaStream_t stream) {
-    constexpr int smem = (HD / 64) * 16384 * 5 + 1024 + 256;
+    constexpr int smem = (HD / 64) * 16384 * 6 + 1024 + 256;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>,
@@ -427,7 +474,7 @@ static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid((max_len + FA_Q - 1) / FA_Q, a.n_heads, n_seqs);
+    dim3 grid(a.n_heads, (max_len + FA_CTA_Q - 1) / FA_CTA_Q, n_seqs);
     mf_launch(attention_prefill_tc_kernel<HD>, grid, dim3(FA_THREADS), smem, stream, mq, mk, mv, a);
     return MF_LAUNCH_CHECK();
 }
@@ -440,7 +487,7 @@ extern "C" int mf_attention_prefill_tc(const void* q, const void* k, const void*
                                        cudaStream_t stream) {
     if (n_seqs <= 0 || max_len <= 0 || n_tokens <= 0) return 0;
     if ((hd != 64 && hd != 128) || n_kv <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
-    if (n_heads > 65535 || n_seqs > 65535) return MF_ERR_UNSUPPORTED;
+    if (n_seqs > 65535 || (max_len + FA_CTA_Q - 1) / FA_CTA_Q > 65535) return MF_ERR_UNSUPPORTED;
     if (((uintptr_t)q & 15) || ((uintptr_t)k & 15) || ((uintptr_t)v & 15) || ((uintptr_t)out & 15))
         return MF_ERR_UNSUPPORTED;
     CUtensorMap mq, mk, mv;

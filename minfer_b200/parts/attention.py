@@ -26,6 +26,8 @@ from .linear import Linear
 
 DECODE_CHUNK = 256     # keys per chunk when attending over the cache
 FORCE_GENERIC_ATTENTION = os.environ.get("MINFER_B200_GENERIC_ATTENTION", "0") == "1"
+# "tcgen05" (tensor memory, the default) or "mma" (the mma.sync twin) for whole prompts in bfloat16
+PROMPT_ATTENTION = os.environ.get("MINFER_B200_PROMPT_ATTENTION", "tcgen05")
 
 
 class Attention(Mixer):
@@ -138,8 +140,13 @@ class Attention(Mixer):
         o = torch.empty((n, nh * hd), dtype=act, device=dev)
         if own_kv:
             if K.attention_prefill_supported(q, nh, nk, hd) and not FORCE_GENERIC_ATTENTION:
-                K.attention_prefill(q, k_step, v_step, ctx.cu_seqlens, o, ctx.n_rows,
-                                    ctx.max_row_tokens, nh, nk, hd, self.window, self.scale)
+                if PROMPT_ATTENTION == "mma":
+                    K.attention_prefill(q, k_step, v_step, ctx.cu_seqlens, o, ctx.n_rows,
+                                        ctx.max_row_tokens, nh, nk, hd, self.window, self.scale)
+                else:
+                    K.attention_prefill_tc(q, k_step, v_step, ctx.cu_seqlens, o, ctx.n_rows,
+                                           ctx.max_row_tokens, nh, nk, hd, self.window, self.scale,
+                                           ctx.status)
             else:
                 K.attention_packed(q, k_step, v_step, ctx.token_row, ctx.positions,
                                    ctx.cu_seqlens, o, nh, nk, hd, self.window, self.scale)

@@ -479,6 +479,58 @@ def test_attention_prefill_tensor_core_kernel(hd, nh, nk, window):
         assert torch.allclose(out[cu[5] + 299, :hd].float().cpu(), v[cu[5] + 3, 0].float().cpu(), atol=2e-2)
 
 
+@pytest.mark.parametrize("hd,nh,nk,window", [(128, 7, 1, 0), (64, 14, 2, 0), (128, 4, 4, 33),
+                                             (64, 6, 2, 200), (128, 2, 1, 64), (64, 3, 1, 1),
+                                             (128, 3, 1, 129), (64, 2, 2, 300)])
+def test_attention_prefill_tcgen05_kernel(hd, nh, nk, window):
+    """Whole prompts of unequal lengths on the tcgen05 kernel (two query tiles of 128 per CTA,
+    key tiles of 128): one token, the edges of a query tile and of a pair of tiles, a second
+    query tile with one row, many key tiles; against float64 attention and the generic kernel.
+    Without a window one far key is made to dominate a late query."""
+    from minfer_b200.kernels import api as K
+    lens = [37, 1, 128, 129, 256, 257, 700, 383, 1000]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    g = torch.Generator().manual_seed(hd * 5 + nh)
+    dt = torch.bfloat16
+    q = torch.randn(T, nh, hd, generator=g).to(dt).cuda()
+    k = torch.randn(T, nk, hd, generator=g).to(dt).cuda()
+    v = torch.randn(T, nk, hd, generator=g).to(dt).cuda()
+    if window == 0:       # key 3 of the 1000-token sequence dominates its query 999
+        b0 = cu[8]
+        k[b0 + 3, 0] = 0.0; k[b0 + 3, 0, 7] = 30.0
+        q[b0 + 999, 0] = 0.0; q[b0 + 999, 0, 7] = 30.0
+    scale = 1.0 / math.sqrt(hd)
+    cu_t = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    out = torch.full((T, nh * hd), float("nan"), dtype=dt, device="cuda")
+    st = status()
+    K.attention_prefill_tc(q, k, v, cu_t, out, len(lens), max(lens), nh, nk, hd, window, scale, st)
+    assert int(st.item()) == 0
+    row_seq = torch.cat([torch.full((n,), b, dtype=torch.int32) for b, n in enumerate(lens)]).cuda()
+    row_pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens]).cuda()
+    gen = torch.empty_like(out)
+    K.attention_packed(q, k, v, row_seq, row_pos, cu_t, gen, nh, nk, hd, window, scale)
+    for b, n in enumerate(lens):
+        sl = slice(cu[b], cu[b + 1])
+        want = attention_reference(q[sl].double().cpu(), k[sl].double().cpu(), v[sl].double().cpu(),
+                                   scale, window)
+        close(out[sl].reshape(n, nh, hd), want, dt, scale=3.0)
+    close(out, gen.double(), dt, scale=3.0)
+    if window == 0:
+        assert torch.allclose(out[cu[8] + 999, :hd].float().cpu(), v[cu[8] + 3, 0].float().cpu(), atol=2e-2)
+
+
+def test_attention_prefill_tcgen05_refuses_other_head_sizes():
+    from minfer_b200.kernels import api as K
+    q = torch.zeros(4, 2, 96, dtype=torch.bfloat16, device="cuda")
+    cu = torch.tensor([0, 4], dtype=torch.int32, device="cuda")
+    with pytest.raises(K.KernelError):
+        K.attention_prefill_tc(q, q, q, cu, torch.empty(4, 192, dtype=torch.bfloat16, device="cuda"),
+                               1, 4, 2, 2, 96, 0, 0.1, status())
+
+
 def test_deferred_split_sums_feed_the_next_kernel():
     """A small projection leaves its K splits; add_rmsnorm and rope_kvstore add them (and the
     bias) themselves: the same numbers as reducing first."""
