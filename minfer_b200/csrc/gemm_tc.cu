@@ -493,7 +493,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     pdl_wait();
     constexpr int B_BYTES = (NT / 2) * TILE_K * 2;           // this CTA's half of the tokens
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr int TMEM_COLS = 2 * NT;                         // two accumulators
+    constexpr int TMEM_COLS = 2 * NT <= 256 ? 256 : 512;      // two accumulators of NT columns (a power of two is allocated)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
@@ -621,6 +621,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     }
 }
 
+static int sm_count();
+
 template <int NT, int STAGES>
 static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
                        cudaStream_t stream) {
@@ -634,6 +636,14 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmA
     }
     const int tiles_m = (a.M + NT - 1) / NT, tiles_n = (a.N + 255) / 256;
     const int total = tiles_m * tiles_n;
+    int pairs = sm_count() / 2;
+    if (pairs > total) pairs = total;
+    mf_launch(gemm_pair_kernel<NT, STAGES>, dim3(2 * pairs), dim3(PAIR_THREADS), smem, stream, mw, mx,
+              a, tiles_m, total);
+    return MF_LAUNCH_CHECK();
+}
+
+static int sm_count() {
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -641,11 +651,26 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmA
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms < 2) sms = 2;
     }
-    int pairs = sms / 2;
-    if (pairs > total) pairs = total;
-    mf_launch(gemm_pair_kernel<NT, STAGES>, dim3(2 * pairs), dim3(PAIR_THREADS), smem, stream, mw, mx,
-              a, tiles_m, total);
-    return MF_LAUNCH_CHECK();
+    return sms;
+}
+
+// The token tile of the CTA-pair kernel: the one whose tiles fill the fewest, shortest rounds
+// over the pairs (14 weight tiles x 8 token tiles of 256 are 112 tiles for 74 pairs: the second
+// round runs half empty; 10 token tiles of 208 are 140 tiles and two rounds of 208).  A tile
+// costs its tokens plus what of its epilogue is not hidden.  An element's sum does not depend
+// on the tile (k ascending, one accumulator), so the choice changes no bits.
+static int pair_token_tile(int M, int N) {
+    static const int candidates[] = {256, 224, 208, 192, 160};
+    const int pairs = sm_count() / 2, tiles_n = (N + 255) / 256;
+    int best = 256;
+    long long best_cost = -1;
+    for (int nt : candidates) {
+        const long long tiles = (long long)((M + nt - 1) / nt) * tiles_n;
+        const long long rounds = (tiles + pairs - 1) / pairs;
+        const long long cost = rounds * (nt + 16);
+        if (best_cost < 0 || cost < best_cost) { best = nt; best_cost = cost; }
+    }
+    return best;
 }
 
 // How a product of these sizes is cut: the token tile and the number of K splits.  A
@@ -706,12 +731,19 @@ extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long
     static int pair_mode = -1;            // MINFER_B200_GEMM_PAIR=0 keeps the one-CTA kernel
     if (pair_mode < 0) { const char* ev = getenv("MINFER_B200_GEMM_PAIR"); pair_mode = ev ? atoi(ev) : 1; }
     if (pair_mode && M >= 256 && splits == 1) {
-        if (int e = make_map(&mx, x, M, K, ldx, 128)) return e;
+        const int pnt = pair_token_tile(M, N);
+        if (int e = make_map(&mx, x, M, K, ldx, pnt / 2)) return e;
         GemmArgs pa;
         pa.out = out; pa.partial = nullptr; pa.bias = bias; pa.status = status; pa.ldo = ldo;
         pa.M = M; pa.N = N; pa.K = K; pa.out_dtype = out_dtype; pa.kblocks_per_split = 0;
         pa.epi = epi;
-        return launch_pair<256, 6>(mw, mx, pa, stream);
+        switch (pnt) {
+            case 224: return launch_pair<224, 6>(mw, mx, pa, stream);
+            case 208: return launch_pair<208, 6>(mw, mx, pa, stream);
+            case 192: return launch_pair<192, 6>(mw, mx, pa, stream);
+            case 160: return launch_pair<160, 6>(mw, mx, pa, stream);
+            default: return launch_pair<256, 6>(mw, mx, pa, stream);
+        }
     }
     if (int e = make_map(&mx, x, M, K, ldx, nt)) return e;
     const int kblocks = (K + TILE_K - 1) / TILE_K;
