@@ -73,7 +73,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -81,9 +81,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.samples.append(line.strip())
+            self.samples.append((time.time(), line.strip()))
 
-    def stop(self):
+    def stop(self, window=None):
+        """Summary of the samples; with ``window`` (host times of the timed region's start and
+        end) only of those taken inside it, if there are any."""
         if self.proc is not None:
             self.proc.terminate()
             try:
@@ -92,7 +94,12 @@ class ClockSampler:
                 self.proc.kill()
         sm, mx, reasons = [], 0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.samples:
+        lines = [line for _, line in self.samples]
+        if window is not None:
+            inside = [line for t, line in self.samples if window[0] <= t <= window[1]]
+            if inside:
+                lines = inside
+        for line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -135,6 +142,9 @@ def prefill_flops(cfg, tokens):
     return linear + attention
 
 
+SETTLE_S = 1.0
+
+
 def time_decode(engine, torch, K, batch, steps, warmup, prompt_len, seed=0):
     """CUDA-event time of `steps` decode steps at `batch`, after `warmup` untimed ones.  The
     sequences' caches come from a real prefill of `batch` random prompts of `prompt_len`
@@ -151,6 +161,11 @@ def time_decode(engine, torch, K, batch, steps, warmup, prompt_len, seed=0):
              frequency_penalty=0.0, presence_penalty=0.0, seed=0)
     tokens = out.clone()
     del logits, prompts
+    # the prefill that built the caches is a burst at over 1 PFLOP/s; for some twenty steps
+    # after it the GPU's power management holds the clocks down (3.9 ms, then 3.5, then the
+    # steady 3.26 ms a step).  That belongs to the prefill, not to a decode step: let it pass.
+    torch.cuda.synchronize()
+    time.sleep(SETTLE_S)
 
     def one_step(tok):
         logits = engine.decode_on_device(slots, tok)
@@ -163,11 +178,13 @@ def time_decode(engine, torch, K, batch, steps, warmup, prompt_len, seed=0):
     torch.cuda.synchronize()
     before = api.launches
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
     start.record()
     for _ in range(steps):
         tokens = one_step(tokens)
     end.record()
     torch.cuda.synchronize()
+    time_decode.window = (t0, time.time())
     ms = start.elapsed_time(end)
     launched = api.launches - before
     engine.check_status()
@@ -222,6 +239,7 @@ def other_workload(name: str, steps: int) -> int:
         return 0
     cfg = dict(CONFIG_14B)
     model = Model.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0", make_on="device")
+    steps = min(steps, 240)
     gen = Generator(model, max_tokens=8 * (8192 + 256), max_batch=8)
     engine = gen.engine
     g = torch.Generator().manual_seed(4)
@@ -254,7 +272,7 @@ def main() -> int:
     ap.add_argument("--workload", default="7b", choices=["7b", "0.5b", "14b"],
                     help="7b: the contract line; 0.5b and 14b: the baseline's side workloads")
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None,
@@ -282,7 +300,7 @@ def main() -> int:
     from minfer_b200.sampling.params import SamplingParams
 
     warmup = max(3, args.warmup)
-    steps = max(1, args.steps)
+    steps = max(1, min(args.steps, CONTEXT - PROMPT - warmup - 2))     # the context is 4,096
     cfg = dict(CONFIG_7B)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
@@ -302,7 +320,7 @@ def main() -> int:
     clocks = ClockSampler()
     clocks.start()
     ms_step, launched = time_decode(engine, torch, K, BATCH, steps, warmup, PROMPT)
-    clock_summary = clocks.stop()
+    clock_summary = clocks.stop(time_decode.window)
     value = BATCH * 1000.0 / ms_step
 
     # roofline of the decode step, mean context over the timed steps
@@ -345,6 +363,7 @@ def main() -> int:
             "intermediate_size": cfg["intermediate_size"], "vocab_size": cfg["vocab_size"],
             "l2": "inputs larger than L2 (weights read every step)",
             "cache": "decode starts from a real prefill of batch x 2048 random tokens",
+            "settle_s": SETTLE_S,
         },
         "clocks": clock_summary, "e2e": e2e, "gpu_launches": launched, "roofline": roofline,
     }

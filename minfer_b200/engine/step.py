@@ -240,6 +240,8 @@ class Engine:
         views = self._views(dev, sizes)
         ctx = self._make_ctx(views, widths, sum(counts), slots, from_start, single, max(counts),
                              max(starts[b] + counts[b] for b in range(len(slots))))
+        # every row wanted, in order (decoding): the last layer needs no row selection
+        ctx.extras["want_is_identity"] = fields[6] == list(range(sum(counts)))
         return ctx, (views[6] if sizes[6] else None)
 
     # ---- decode steps replayed as CUDA graphs -------------------------------------------------
@@ -297,6 +299,7 @@ class Engine:
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         ctx = self._make_ctx(views, widths, n_rows, slots, False, True, 1, cap)
+        ctx.extras["want_is_identity"] = True       # one token a row, each row's logits wanted
         before = K.launches
         with torch.cuda.graph(graph, pool=self._graph_pool):
             logits = self._run(ctx, views[6])
@@ -338,19 +341,20 @@ class Engine:
         bindings = self._bindings(ctx)
         last = len(plan.schedule) - 1
         n_want = 0 if want_rows is None else want_rows.numel()
+        all_rows = n_want == ctx.n_tokens and bool(ctx.extras.get("want_is_identity"))
         for i, call in enumerate(plan.schedule):
             block = model.blocks[call.layer]
             takes_pending = getattr(block, "accepts_pending", False)
             if not takes_pending:
                 settle_pending(ctx, h)
             block.mix(h, ctx, bindings[i])
-            if i == last or not takes_pending:
+            if not takes_pending or (i == last and not all_rows):
                 settle_pending(ctx, h)
             if i == last:
                 if n_want == 0:
                     return torch.empty((0, plan.vocab_size), dtype=torch.float32,
                                        device=self.device)
-                if not (n_want == ctx.n_tokens and ctx.extras.get("want_is_identity")):
+                if not all_rows:
                     picked = torch.empty((n_want, plan.hidden_size), dtype=torch.float32,
                                          device=self.device)
                     K.gather_rows(h, want_rows, picked)

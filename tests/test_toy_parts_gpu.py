@@ -189,3 +189,153 @@ def test_toy_architecture_is_registered_built_and_stepped(dtype):
         for b in range(3):
             assert rel_err(torch.cat(got[b]), want[b]) < tol, (round_, b)
     eng.check_status()
+
+
+# ---------------------------------------------------------------------------------------------
+# A toy feed-forward with routing: each token goes to the one of three small experts whose
+# router logit is largest (router in float32), y = W2_e (W1_e x)^2 * gate.  Layers alternate
+# between it and the gated MLP, and the run order names layer 0 twice.
+# ---------------------------------------------------------------------------------------------
+N_EXPERTS, EXPERT_INNER = 3, 16
+
+
+def _register_routed():
+    from minfer_b200 import registry
+    from minfer_b200.config.base import ConfigReader, LayerCall, LayerSpec, ModelPlan, PartSpec
+    from minfer_b200.kernels import api as K
+    from minfer_b200.parts.base import FeedForward
+    from minfer_b200.weights.spec import MATRIX, Init, TensorSpec
+
+    class RoutedSquare(FeedForward):
+        def __init__(self, width, inner, experts):
+            self.width, self.inner, self.experts = width, inner, experts
+
+        def tensor_specs(self, prefix):
+            specs = [TensorSpec(f"{prefix}moe.router", (self.experts, self.width), MATRIX, Init(0, 0.5))]
+            for e in range(self.experts):
+                specs.append(TensorSpec(f"{prefix}moe.{e}.w1", (self.inner, self.width), MATRIX, Init(0, 0.2)))
+                specs.append(TensorSpec(f"{prefix}moe.{e}.w2", (self.width, self.inner), MATRIX, Init(0, 0.2)))
+            return specs
+
+        def load(self, prefix, weights):
+            self.router = weights[f"{prefix}moe.router"]
+            self.w1 = [weights[f"{prefix}moe.{e}.w1"] for e in range(self.experts)]
+            self.w2 = [weights[f"{prefix}moe.{e}.w2"] for e in range(self.experts)]
+
+        def forward_add(self, x, ctx, residual):
+            n = x.shape[0]
+            logits = torch.empty((n, self.experts), dtype=torch.float32, device=x.device)
+            K.gemm_simt(x, self.router, None, logits)              # router logits in float32
+            gate = torch.softmax(logits, -1)
+            choice = logits.argmax(-1)
+            for e in range(self.experts):                          # each expert takes its own rows
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                xe = x[rows].contiguous()
+                u = torch.empty((rows.numel(), self.inner), dtype=torch.float32, device=x.device)
+                K.gemm_simt(xe, self.w1[e], None, u)
+                y = torch.empty((rows.numel(), self.width), dtype=torch.float32, device=x.device)
+                K.gemm_simt((u * u).to(x.dtype), self.w2[e], None, y)
+                residual[rows] += y * gate[rows, e][:, None]
+
+    class RoutedConfig:
+        def __init__(self, d):
+            r = ConfigReader(d)
+            self.vocab, self.width, self.layers = r.integer("vocab"), r.integer("width"), r.integer("layers")
+
+        def plan(self):
+            norm = PartSpec("rms_norm", {"size": self.width, "eps": 1e-5})
+            layers = []
+            for l in range(self.layers):
+                mixer = PartSpec("attention", dict(
+                    hidden_size=self.width, n_heads=2, n_kv_heads=2, head_dim=16, scale=0.25, window=0,
+                    qkv_bias=True, position=PartSpec("rotary", dict(head_dim=16, rotary_dim=16, theta=100.0))))
+                ffn = (PartSpec("toy_routed", dict(width=self.width, inner=EXPERT_INNER, experts=N_EXPERTS))
+                       if l % 2 == 0 else
+                       PartSpec("gated_mlp", dict(hidden_size=self.width, intermediate_size=24)))
+                layers.append(LayerSpec(f"r.{l}.", PartSpec("pre_norm", {}), mixer,
+                                        norm.with_params(name="n1"), ffn, norm.with_params(name="n2")))
+            # layer 0 runs twice: its second run has a cache entry of its own
+            order = [LayerCall(0, 0, True), LayerCall(1, 1, True), LayerCall(0, 2, True)]
+            return ModelPlan("ToyRoutedLM", self.vocab, self.width, "r.embed", None,
+                             norm.with_params(name="final"), "r.", layers, order, 4096, ())
+
+    registry.register_part("feed_forward", "toy_routed", RoutedSquare, replace=True)
+    registry.register_architecture("ToyRoutedLM", lambda d, where: RoutedConfig(d), replace=True)
+
+
+ROUTED_CONFIG = {"architectures": ["ToyRoutedLM"], "vocab": 61, "width": 32, "layers": 2}
+
+
+def _routed_reference(w, ids):
+    def norm(x, wt):
+        return x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5) * wt
+    T = len(ids)
+    h = w["r.embed"][torch.tensor(ids)]
+    pos = torch.arange(T, dtype=torch.float64)
+    inv = 100.0 ** (-torch.arange(0, 16, 2, dtype=torch.float64) / 16)
+    ang = pos[:, None] * inv[None, :]
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def rope(x):
+        a, b = x[..., :8], x[..., 8:]
+        return torch.cat([a * cos - b * sin, a * sin + b * cos], -1)
+    for l in (0, 1, 0):
+        p = f"r.{l}."
+        a = p + "self_attn."
+        x = norm(h, w[p + "n1.weight"])
+        q = rope((x @ w[a + "q_proj.weight"].t() + w[a + "q_proj.bias"]).reshape(T, 2, 16))
+        k = rope((x @ w[a + "k_proj.weight"].t() + w[a + "k_proj.bias"]).reshape(T, 2, 16))
+        v = (x @ w[a + "v_proj.weight"].t() + w[a + "v_proj.bias"]).reshape(T, 2, 16)
+        o = torch.zeros(T, 2, 16, dtype=torch.float64)
+        for hh in range(2):
+            sc = (q[:, hh] @ k[:, hh].t()) * 0.25
+            sc = sc.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+            o[:, hh] = torch.softmax(sc, -1) @ v[:, hh]
+        h = h + o.reshape(T, 32) @ w[a + "o_proj.weight"].t()
+        x = norm(h, w[p + "n2.weight"])
+        if l == 0:
+            logits = x @ w[p + "moe.router"].t()
+            gate, choice = torch.softmax(logits, -1), logits.argmax(-1)
+            y = torch.zeros_like(h)
+            for t in range(T):
+                e = int(choice[t])
+                y[t] = ((w[p + f"moe.{e}.w1"] @ x[t]) ** 2) @ w[p + f"moe.{e}.w2"].t() * gate[t, e]
+            h = h + y
+        else:
+            g, u = x @ w[p + "mlp.gate_proj.weight"].t(), x @ w[p + "mlp.up_proj.weight"].t()
+            h = h + (torch.nn.functional.silu(g) * u) @ w[p + "mlp.down_proj.weight"].t()
+    return norm(h, w["r.final.weight"]) @ w["r.embed"].t()
+
+
+def test_toy_routed_feed_forward_and_a_layer_that_runs_twice():
+    """float32 only: a routing decision is a comparison, so a bfloat16 rounding could flip it
+    against the float64 reference; the part itself works in either engine."""
+    _register_routed()
+    from minfer_b200.engine.step import Engine
+    from minfer_b200.model import Model
+    from minfer_b200.registry import read_config
+    from minfer_b200.weights.random_init import write_model_folder
+    from minfer_b200.weights.safetensors_io import load_all
+    with tempfile.TemporaryDirectory() as folder:
+        json.dump(ROUTED_CONFIG, open(os.path.join(folder, "config.json"), "w"))
+        cfg = read_config(ROUTED_CONFIG)
+        write_model_folder(folder, ROUTED_CONFIG, Model(cfg.plan(), "float32", cfg).tensor_specs(), 9, "float32")
+        w = {k: v.double() for k, v in load_all(folder).items()}
+        model = Model.from_folder(folder, "float32", "cuda:0")
+    eng = Engine(model, 512, max_seqs=2)
+    assert sum(len(g.entries) for g in eng.cache.groups) == 3         # three calls, three entries
+    prompts = [random_ids(n, 61, 40 + n) for n in (21, 50)]
+    want = [_routed_reference(w, p) for p in prompts]
+    slots = [eng.acquire() for _ in prompts]
+    heads = [len(p) - 4 for p in prompts]
+    out = eng.step(slots, [p[:h] for p, h in zip(prompts, heads)], [list(range(h)) for h in heads])
+    got = [[o] for o in torch.split(out, heads)]
+    for t in range(4):
+        o = eng.step(slots, [[p[h + t]] for p, h in zip(prompts, heads)])
+        for b in range(2):
+            got[b].append(o[b:b + 1])
+    for b in range(2):
+        assert rel_err(torch.cat(got[b]), want[b]) < 2e-5, b
+    eng.check_status()
