@@ -253,13 +253,14 @@ class Engine:
         (src/graph/params.rs:10-60: the reuse identity has no n_past)."""
         n_rows = len(slots)
         max_end = max(starts) + 1
-        # a bound on the lengths: 256, 512, 1024, then multiples of 1024 (a new graph every 1024
-        # positions; key chunks beyond a sequence's end cost a launch and nothing else)
+        # a bound on the lengths: 256, 512, 1024, then multiples of 512 (a new graph every 512
+        # positions; a key chunk beyond a sequence's end costs a CTA that leaves at once:
+        # 2 % of a step at batch 64 with multiples of 1024)
         cap = 256
         while cap < max_end and cap < 1024:
             cap *= 2
         if cap < max_end:
-            cap = ((max_end + 1023) // 1024) * 1024
+            cap = ((max_end + 511) // 512) * 512
         key = (n_rows, cap)
         entry = self._graphs.get(key)
         if entry is None and key not in self._seen_shapes:

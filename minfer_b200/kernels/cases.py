@@ -75,6 +75,16 @@ def gemm_decode_split(reps):
     _gemm(8, NE, NF, K.EPI_ACCUM, reps)
 
 
+def gemm_decode_m64(reps):
+    """The gate|up projection with fused SwiGLU for 64 tokens."""
+    _gemm(64, 2 * NF, NE, K.EPI_SWIGLU, reps)
+
+
+def gemm_decode_split_m64(reps):
+    """The down projection for 64 tokens (split along K, partial sums reduced)."""
+    _gemm(64, NE, NF, K.EPI_ACCUM, reps)
+
+
 def gemm_prefill(reps):
     """The gate|up projection with fused SwiGLU for 2,048 tokens: 556 GFLOP."""
     _gemm(2048, 2 * NF, NE, K.EPI_SWIGLU, reps)
@@ -192,7 +202,7 @@ def step_decode(reps, layers=4):
     print(f"decode step, {layers} layers, batch 8: {us:.1f} us")
 
 
-CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_prefill, gemm_prefill_down,
+CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_decode_m64, gemm_decode_split_m64, gemm_prefill, gemm_prefill_down,
                                  attention_decode, attention_decode_b8, attention_prefill,
                                  attention_prefill_tc, attention_prefill_tc_8k, attention_prefill_8k,
                                  step_prefill, step_decode)}
