@@ -220,8 +220,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 #define DEC_WARPS 8           // warps per CTA; each takes DEC_KEYS keys of the 256-key chunk
 #define DEC_KEYS 32
 
-template <int HD>
-__global__ void __launch_bounds__(DEC_WARPS * 32, 2) attention_decode_mma_kernel(AttnArgs a) {
+// MINB: CTAs per SM the registers are cut for.  Two (128 registers) are faster while all CTAs
+// fit on the GPU at once; with many rounds of CTAs a third one per SM (80 registers) keeps
+// more loads in flight (batch 64: 2.8 % of a step).
+template <int HD, int MINB>
+__global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_kernel(AttnArgs a) {
     pdl_prologue();
     constexpr int CPR = HD / 8;                       // 16-byte chunks per row
     extern __shared__ __align__(128) uint8_t dec_smem[];
@@ -409,21 +412,27 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, 2) attention_decode_mma_kernel
     }
 }
 
-template <int HD>
-static int launch_decode_mma(const AttnArgs& a, cudaStream_t stream) {
+template <int HD, int MINB>
+static int launch_decode_mma_as(const AttnArgs& a, cudaStream_t stream) {
     constexpr int smem = DEC_WARPS * 16 * (HD + 8) * 4 + DEC_WARPS * 16 * 3 * 4;
     static_assert(DEC_WARPS * DEC_KEYS * HD * 2 <= DEC_WARPS * 16 * (HD + 8) * 4, "values fit the staging area");
     static_assert(DEC_WARPS * DEC_KEYS == 256, "a CTA covers one 256-key chunk");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD>,
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, MINB>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(a.n_chunks, a.n_kv, a.rows);
-    mf_launch(attention_decode_mma_kernel<HD>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, a);
+    mf_launch(attention_decode_mma_kernel<HD, MINB>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, a);
     return MF_LAUNCH_CHECK();
+}
+
+template <int HD>
+static int launch_decode_mma(const AttnArgs& a, cudaStream_t stream) {
+    const long long ctas = (long long)a.n_chunks * a.n_kv * a.rows;
+    return ctas > 2 * 296 ? launch_decode_mma_as<HD, 3>(a, stream) : launch_decode_mma_as<HD, 2>(a, stream);
 }
 
 static int check_sizes(int n_heads, int n_kv, int hd) {

@@ -444,6 +444,34 @@ def test_attention_decode_tensor_core_kernel(hd, nh, nk, window, ring):
         assert torch.allclose(outs[False][6, :hd].float().cpu(), hist_v[6][17, 0].float(), atol=2e-2)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+def test_attention_decode_many_rows(hd):
+    """Many rows at once: the decode kernel's variant for grids of several rounds of CTAs
+    (three CTAs per SM) against the generic kernel over the same random cache."""
+    from minfer_b200.kernels import api as K
+    B, nh, nk, n_chunks, width = 200, 8, 4, 3, 12
+    g = torch.Generator().manual_seed(hd)
+    dt = torch.bfloat16
+    n_pages = B * width
+    kc = torch.randn(n_pages, nk, 64, hd, generator=g).to(dt).cuda()
+    vc = torch.randn(n_pages, nk, 64, hd, generator=g).to(dt).cuda()
+    table = torch.randperm(n_pages, generator=g).to(torch.int32).reshape(B, width).cuda()
+    lens = torch.randint(1, 64 * width + 1, (B,), generator=g)
+    lens[:4] = torch.tensor([1, 256, 257, 64 * width])
+    q = torch.randn(B, nh, hd, generator=g).to(dt).cuda()
+    row_seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    row_pos = (lens - 1).to(torch.int32).cuda()
+    outs = []
+    for force in (False, True):
+        out = torch.full((B, nh * hd), float("nan"), dtype=dt, device="cuda")
+        partial = torch.full((B * nh * n_chunks * (hd + 2),), float("nan"), device="cuda")
+        K.attention_paged(q, kc, vc, row_seq, row_pos, table, width, 0, out, partial, nh, nk, hd, 0,
+                          256, n_chunks, 1.0 / math.sqrt(hd), force_generic=force)
+        outs.append(out)
+    assert not torch.isnan(outs[0].float()).any()
+    close(outs[0], outs[1].double(), dt, scale=3.0)
+
+
 @pytest.mark.parametrize("hd,nh,nk,window", [(128, 7, 1, 0), (64, 14, 2, 0), (128, 4, 4, 33),
                                              (64, 6, 2, 200), (128, 2, 1, 64), (64, 3, 1, 1)])
 def test_attention_prefill_tensor_core_kernel(hd, nh, nk, window):
