@@ -400,7 +400,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_ker
 #pragma unroll
     for (int nt = 0; nt < HD / 8; ++nt) {
         *reinterpret_cast<float2*>(ow + (size_t)g * OS + nt * 8 + 2 * t) = make_float2(o[nt][0], o[nt][1]);
-        *reinterpret_cast<float2*>(ow + (size_t)(g + 8) * OS + nt * 8 + 2 * t) = make_float2(o[nt][2], o[nt][3]);
+        if (G > 8)      // rows 8-15 hold heads only in groups of more than eight
+            *reinterpret_cast<float2*>(ow + (size_t)(g + 8) * OS + nt * 8 + 2 * t) = make_float2(o[nt][2], o[nt][3]);
     }
     __syncthreads();
     for (int idx = tid; idx < G * HD; idx += DEC_WARPS * 32) {
