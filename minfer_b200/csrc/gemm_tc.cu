@@ -656,9 +656,10 @@ static int sm_count() {
 
 // The token tile of the CTA-pair kernel: the one whose tiles fill the fewest, shortest rounds
 // over the pairs (14 weight tiles x 8 token tiles of 256 are 112 tiles for 74 pairs: the second
-// round runs half empty; 10 token tiles of 208 are 140 tiles and two rounds of 208).  A tile
-// costs its tokens plus what of its epilogue is not hidden.  An element's sum does not depend
-// on the tile (k ascending, one accumulator), so the choice changes no bits.
+// round runs half empty; 10 token tiles of 208 are 140 tiles and two rounds of 208).  A tile's
+// time follows the operand bytes it pulls through L2, 256 weight rows plus its tokens per
+// k-block (measured: a 208-token tile takes 0.96 of a 256-token one).  An element's sum does
+// not depend on the tile (k ascending, one accumulator), so the choice changes no bits.
 static int pair_token_tile(int M, int N) {
     static const int candidates[] = {256, 224, 208, 192, 160};
     const int pairs = sm_count() / 2, tiles_n = (N + 255) / 256;
@@ -667,7 +668,7 @@ static int pair_token_tile(int M, int N) {
     for (int nt : candidates) {
         const long long tiles = (long long)((M + nt - 1) / nt) * tiles_n;
         const long long rounds = (tiles + pairs - 1) / pairs;
-        const long long cost = rounds * (nt + 16);
+        const long long cost = rounds * (nt + 256);
         if (best_cost < 0 || cost < best_cost) { best = nt; best_cost = cost; }
     }
     return best;
