@@ -49,8 +49,17 @@ TINY_E = {
     "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
     "use_sliding_window": False, "max_position_embeddings": 2048,
 }
+# a group of 20 query heads on one key/value head: more than the 16 rows of the decode
+# kernel's MMA tile, so decoding takes the generic kernel while prompts take the tcgen05 one
+TINY_F = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 151, "hidden_size": 1280, "num_hidden_layers": 1,
+    "num_attention_heads": 20, "num_key_value_heads": 1, "intermediate_size": 136,
+    "rope_theta": 500000.0, "rms_norm_eps": 2e-6, "tie_word_embeddings": True,
+    "use_sliding_window": False, "max_position_embeddings": 512,
+}
 TINY = {"A": (TINY_A, 0, 0.0), "B": (TINY_B, 1, 0.01), "C": (TINY_C, 2, 0.02),
-        "D": (TINY_D, 3, 0.01), "E": (TINY_E, 4, 0.0)}
+        "D": (TINY_D, 3, 0.01), "E": (TINY_E, 4, 0.0), "F": (TINY_F, 5, 0.01)}
 
 # Tolerances, as a fraction of the largest logit magnitude of the comparison.  float32
 # differs from the float64 plain implementation by summation order only; bfloat16 rounds

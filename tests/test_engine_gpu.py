@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 LENGTHS = [37, 5, 90, 64, 1, 65, 130]
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E", "F"])
 def tiny(request):
     folder = make_folder(request.param)
     cfg, w = P.load_folder(folder)
