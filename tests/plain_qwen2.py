@@ -3,10 +3,13 @@ sequences, no cache, one function per part, float64 by default.  It shares no co
 ``minfer_b200``: it reads ``config.json`` as a dictionary and the weights with the
 ``safetensors`` package.
 
-It rests on the reference's formulas, not on running the reference: yusiwen/minfer is Rust,
-there is no Rust toolchain here, and it reads GGUF files only, so its model code can be
+It rests on the reference's formulas, not on running the reference's model: yusiwen/minfer is
+Rust, there is no Rust toolchain here, and it reads GGUF files only, so its model code can be
 neither imported nor compiled in this environment.  Each function cites the lines of the
-reference (paths within that project) that it restates.
+reference (paths within that project) that it restates.  What of the reference does compile
+are its float32 CUDA kernels (src/cuda_kernels.cu, plain C): their outputs for RMSNorm, the
+NeoX rotation, SwiGLU and grouped-query attention on seeded inputs lie under tests/golden/
+with the script that made them, and tests/test_plain.py holds this file's functions to them.
 """
 from __future__ import annotations
 

@@ -98,3 +98,41 @@ def test_decoding_a_prefix_matches_the_whole_sequence_and_schedule_repeats_layer
     assert twice.shape == whole.shape and not torch.allclose(twice, whole)
     shared = P.forward(cfg, w, ids, schedule=[(0, 0, True), (1, 0, False)])
     assert not torch.allclose(shared, whole)
+
+
+def test_parts_agree_with_the_references_own_cuda_kernels():
+    """RMSNorm, NeoX rotation (at positions up to 4095 and both frequency bases), SwiGLU and
+    grouped-query attention over a cache: the plain implementation in float64 against what the
+    reference's float32 CUDA kernels (src/cuda_kernels.cu, compiled unchanged) gave on the
+    same seeded inputs; tests/golden/make_reference_kernel_vectors.py made the file."""
+    import importlib.util
+    import os
+
+    import numpy as np
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location(
+        "make_reference_kernel_vectors", os.path.join(here, "golden", "make_reference_kernel_vectors.py"))
+    maker = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(maker)
+    cases = maker.inputs()
+    gold = np.load(os.path.join(here, "golden", "reference_kernels.npz"))
+
+    def err(got, name):
+        want = torch.from_numpy(gold[name]).double()
+        assert got.shape == want.shape
+        return float((got.double() - want).abs().max() / want.abs().max())
+
+    c = cases["rms_norm"]
+    assert err(P.rms_norm(c["x"].double(), c["w"].double(), c["eps"]), "rms_norm") < 1e-6
+    # the reference forms the angle in float32 (pos * freq): 1e-4 rad off at position 4095
+    for name, tol in (("rope", 3e-4), ("rope_base_10000", 3e-4)):
+        c = cases[name]
+        assert err(P.rope_neox(c["x"].double(), c["positions"], c["theta"], c["scale"]), name) < tol
+    early = cases["rope"]["x"][:4].double()          # positions 0, 1, 2, 7: float32 angles are exact enough
+    got = P.rope_neox(early, cases["rope"]["positions"][:4], cases["rope"]["theta"])
+    assert float((got - torch.from_numpy(gold["rope"][:4]).double()).abs().max()) < 2e-6
+    c = cases["swiglu"]
+    g, u = c["gate"].double(), c["up"].double()
+    assert err(g / (1.0 + torch.exp(-g)) * u, "swiglu") < 1e-6
+    c = cases["attention"]
+    assert err(P.attention(c["q"].double(), c["k"].double(), c["v"].double(), c["scale"]), "attention") < 2e-6
