@@ -68,6 +68,23 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int i = threadIdx.x; i < width; i += blockDim.x) yr[i] = from_f32<TO>(xr[i] * scale * w[i]);
 }
 
+// four neighbouring outputs in one store
+template <typename T> struct Pack4;
+template <> struct Pack4<float> {
+    static __device__ __forceinline__ void store(float* p, float a, float b, float c, float d) {
+        *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+    }
+};
+template <> struct Pack4<__nv_bfloat16> {
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b, float c, float d) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 v;
+        v.x = *reinterpret_cast<unsigned*>(&lo);
+        v.y = *reinterpret_cast<unsigned*>(&hi);
+        *reinterpret_cast<uint2*>(p) = v;
+    }
+};
+
 // the same with float4 accesses and the row kept in registers (one pass over memory), for
 // widths that are multiples of 4 up to 16384
 template <typename TO>
@@ -100,10 +117,8 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
         if (i < nv) {
             const float4 g = reinterpret_cast<const float4*>(w)[i];
             const float4 v = row[j];
-            yr[4 * i + 0] = from_f32<TO>(v.x * scale * g.x);
-            yr[4 * i + 1] = from_f32<TO>(v.y * scale * g.y);
-            yr[4 * i + 2] = from_f32<TO>(v.z * scale * g.z);
-            yr[4 * i + 3] = from_f32<TO>(v.w * scale * g.w);
+            Pack4<TO>::store(yr + 4 * i, v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z,
+                             v.w * scale * g.w);
         }
     }
 }
@@ -112,8 +127,10 @@ extern "C" int mf_rmsnorm(const float* x, const float* w, const int* rows, void*
                           int n_rows, int width, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (width % 4 == 0 && width <= 16384 && (out_dtype == MF_DTYPE_F32 || out_dtype == MF_DTYPE_BF16)) {
+        // up to four float4 a thread: fewer warps to sum over, more rows on an SM at once
+        // (2,048 rows of 3,584: 6.1 us with 256 threads, 13.1 us with 1,024)
         int threads = 32;
-        while (threads < 1024 && threads * 4 < width) threads <<= 1;
+        while (threads < 1024 && threads * 16 < width) threads <<= 1;
         if (out_dtype == MF_DTYPE_F32)
             mf_launch(rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, w, rows,
                       (float*)y, width, eps);
@@ -215,10 +232,8 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ partial,
         if (i < nv) {
             const float4 g = reinterpret_cast<const float4*>(w)[i];
             const float4 v = row[j];
-            yr[4 * i + 0] = from_f32<TO>(v.x * scale * g.x);
-            yr[4 * i + 1] = from_f32<TO>(v.y * scale * g.y);
-            yr[4 * i + 2] = from_f32<TO>(v.z * scale * g.z);
-            yr[4 * i + 3] = from_f32<TO>(v.w * scale * g.w);
+            Pack4<TO>::store(yr + 4 * i, v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z,
+                             v.w * scale * g.w);
         }
     }
 }
@@ -394,22 +409,6 @@ __global__ void rope_kvstore_kernel(const float* __restrict__ qkv, int n_partial
 // The common case in wide accesses: pairs (i, i + hd/2), the whole head rotated, head sizes
 // that are multiples of 8.  A thread takes 4 neighbouring pairs of a q or k head (two float4
 // loads per split, two 4-element stores per destination) or 8 elements of a v head.
-template <typename T> struct Pack4;
-template <> struct Pack4<float> {
-    static __device__ __forceinline__ void store(float* p, float a, float b, float c, float d) {
-        *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
-    }
-};
-template <> struct Pack4<__nv_bfloat16> {
-    static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b, float c, float d) {
-        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
-        uint2 v;
-        v.x = *reinterpret_cast<unsigned*>(&lo);
-        v.y = *reinterpret_cast<unsigned*>(&hi);
-        *reinterpret_cast<uint2*>(p) = v;
-    }
-};
-
 template <typename T>
 __global__ void __launch_bounds__(128)
 rope_kvstore_vec_kernel(const float* __restrict__ qkv, int n_partials, int n_tokens,
