@@ -16,7 +16,7 @@
 // reference uses f64.
 //
 // One block of 1024 threads works on one row, whatever the batch, so a row's result never
-// depends on its neighbours.  The recent window and the draw counter live in a small
+// depends on its neighbours.  Every pass over the row is coalesced (see sample_kernel).  The recent window and the draw counter live in a small
 // fixed-size state per sequence: state[slot] = {n_seen, n_draws, ring[64]}.
 #include "common.cuh"
 
@@ -24,6 +24,7 @@
 #define SMP_RECENT 64
 #define SMP_STATE_INTS (2 + SMP_RECENT)
 #define SMP_SORT_MAX 1024
+#define SMP_LIST_MAX 2048
 
 __device__ __forceinline__ unsigned order_key(float v) {
     const unsigned u = __float_as_uint(v);
@@ -62,69 +63,76 @@ struct SampleArgs {
     int update_state;         // append the sampled token to the window, count the draw
 };
 
-// inclusive scan of one double per thread over the block; returns this thread's inclusive sum
-__device__ double block_scan_inclusive(double v, double* buf) {
-    const int t = threadIdx.x;
-    buf[t] = v;
-    __syncthreads();
-    for (int off = 1; off < SMP_THREADS; off <<= 1) {
-        const double add = t >= off ? buf[t - off] : 0.0;
-        __syncthreads();
-        buf[t] += add;
-        __syncthreads();
-    }
-    const double r = buf[t];
-    __syncthreads();
-    return r;
+// ---- block-wide reductions: shuffles inside a warp, 32 partial results through shared memory ----
+__device__ __forceinline__ double warp_sum_double(double v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
 }
-__device__ int block_scan_inclusive_int(int v, int* buf) {
-    const int t = threadIdx.x;
-    buf[t] = v;
-    __syncthreads();
-    for (int off = 1; off < SMP_THREADS; off <<= 1) {
-        const int add = t >= off ? buf[t - off] : 0;
-        __syncthreads();
-        buf[t] += add;
-        __syncthreads();
-    }
-    const int r = buf[t];
-    __syncthreads();
-    return r;
+__device__ __forceinline__ int warp_sum_int(int v) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
 }
+// every thread gets the block's sum; `buf` holds 32 doubles
 __device__ double block_sum_double(double v, double* buf) {
-    const int t = threadIdx.x;
-    buf[t] = v;
+    v = warp_sum_double(v);
+    if ((threadIdx.x & 31) == 0) buf[threadIdx.x >> 5] = v;
     __syncthreads();
-    for (int off = SMP_THREADS / 2; off > 0; off >>= 1) {
-        if (t < off) buf[t] += buf[t + off];
-        __syncthreads();
-    }
-    const double r = buf[0];
+    double r = buf[threadIdx.x & 31];
+    r = warp_sum_double(r);
     __syncthreads();
     return r;
 }
-
-__global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleArgs a) {
+__device__ int block_sum_int(int v, int* buf) {
+    v = warp_sum_int(v);
+    if ((threadIdx.x & 31) == 0) buf[threadIdx.x >> 5] = v;
+    __syncthreads();
+    int r = buf[threadIdx.x & 31];
+    r = warp_sum_int(r);
+    __syncthreads();
+    return r;
+}
+__device__ int block_min_int(int v, int* buf) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, off));
+    if ((threadIdx.x & 31) == 0) buf[threadIdx.x >> 5] = v;
+    __syncthreads();
+    int r = buf[threadIdx.x & 31];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) r = min(r, __shfl_xor_sync(0xffffffffu, r, off));
+    __syncthreads();
+    return r;
+}
+// The row is cut into 32 consecutive ranges, one per warp; a warp walks its range in rows of
+// 32 consecutive indices, lane l taking the l-th: loads are coalesced and (warp, row, lane)
+// is the index order, which the draw and the ties of top-p need.
+__global__ void __launch_bounds__(SMP_THREADS, 1) sample_kernel(SampleArgs a) {
     pdl_prologue();
-    __shared__ double dbuf[SMP_THREADS];
+    __shared__ double dbuf[32];
     __shared__ float fscratch[33];
-    __shared__ int ibuf[SMP_THREADS];
+    __shared__ int ibuf[32];
     __shared__ float sort_p[SMP_SORT_MAX];
     __shared__ int sort_i[SMP_SORT_MAX];
     __shared__ unsigned hist[256];
     __shared__ double hsum[256];
+    __shared__ double wsum[32];
+    __shared__ float list_v[SMP_LIST_MAX];       // top-k: the candidates of the highest digits
+    __shared__ int list_i[SMP_LIST_MAX];
+    __shared__ float surv_v[SMP_SORT_MAX];       // top-k: the survivors' logits, beside sort_p / sort_i
     __shared__ unsigned sh_prefix;
     __shared__ int sh_int;
     __shared__ double sh_dbl;
 
     const int row = blockIdx.x;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int V = a.vocab;
     float* x = a.logits + (size_t)row * a.ld;
     int* st = (a.slots != nullptr && a.state != nullptr)
                   ? a.state + (size_t)a.slots[row] * SMP_STATE_INTS : nullptr;
-    const int seg = (V + SMP_THREADS - 1) / SMP_THREADS;   // contiguous indices per thread
-    const int i_begin = min(V, tid * seg), i_end = min(V, i_begin + seg);
+    const int n_rows = (V + SMP_THREADS - 1) / SMP_THREADS;    // rows of 32 indices per warp
+    const int w_begin = warp * n_rows * 32;                    // may lie beyond V for late warps
+#define OWN_ROWS(j, i) for (int j = 0, i = w_begin + lane; j < n_rows; ++j, i += 32)
 
     // ---- penalties over the distinct tokens of the window -------------------------------
     const bool pen = st != nullptr && (fabsf(a.repeat - 1.0f) >= 1e-6f ||
@@ -160,32 +168,215 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleArgs a) {
         // ---- greedy: the first maximum wins ---------------------------------------------
         float best = -INFINITY;
         int best_i = V;                                    // V = "none yet"
-        for (int i = i_begin; i < i_end; ++i) {
-            const float v = x[i];
-            if (best_i == V || v > best) { best = v; best_i = i; }
+#pragma unroll 8
+        OWN_ROWS(j, i) {
+            if (i < V) {
+                const float v = x[i];
+                if (best_i == V || v > best) { best = v; best_i = i; }
+            }
         }
         const float mx = block_max(best_i == V ? -INFINITY : best, fscratch);
         // lowest index among those equal to the maximum (a NaN row falls back to index 0)
-        int cand = (best_i != V && best == mx) ? best_i : V;
-        ibuf[tid] = cand;
-        __syncthreads();
-        for (int off = SMP_THREADS / 2; off > 0; off >>= 1) {
-            if (tid < off) ibuf[tid] = min(ibuf[tid], ibuf[tid + off]);
-            __syncthreads();
-        }
-        chosen = ibuf[0] < V ? ibuf[0] : 0;
-        __syncthreads();
+        const int first = block_min_int((best_i != V && best == mx) ? best_i : V, ibuf);
+        chosen = first < V ? first : 0;
     } else {
-        // ---- top-k: mask everything below the k-th largest value ------------------------
+        // ---- top-k, the usual case: the k-th largest value lies among the few highest first
+        // digits (sign and exponent bits).  Three passes over the row (maximum; counts of the
+        // four highest digits, in registers; gather of those candidates into shared memory),
+        // then everything else (the exact threshold, top-p, the draw) on the short list.
+        int n_list = -1;                                   // >= 0: survivors are in surv_v / sort_i
+        float list_max = -INFINITY;
+        if (a.top_k > 0 && a.top_k < V) {
+            float mx_l = -INFINITY;
+#pragma unroll 8
+            OWN_ROWS(j, i)
+                if (i < V) mx_l = fmaxf(mx_l, x[i]);
+            list_max = block_max(mx_l, fscratch);
+            const int d_max = (int)(order_key(list_max) >> 24);
+            int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+#pragma unroll 8
+            OWN_ROWS(j, i) {
+                if (i < V) {
+                    const int d = (int)(order_key(x[i]) >> 24);
+                    c0 += d == d_max; c1 += d == d_max - 1; c2 += d == d_max - 2; c3 += d == d_max - 3;
+                }
+            }
+            const int cnt[4] = {block_sum_int(c0, ibuf), block_sum_int(c1, ibuf), block_sum_int(c2, ibuf),
+                                block_sum_int(c3, ibuf)};
+            int sel = -1, k_left = a.top_k, n_cand = 0;
+            for (int t = 0; t < 4; ++t) {
+                n_cand += cnt[t];
+                if (cnt[t] >= k_left) { sel = d_max - t; break; }
+                k_left -= cnt[t];
+            }
+            if (sel >= 0 && n_cand <= SMP_LIST_MAX) {
+                if (tid == 0) sh_int = 0;
+                __syncthreads();
+#pragma unroll 8
+                OWN_ROWS(j, i) {
+                    const float v = i < V ? x[i] : 0.0f;
+                    const bool in = i < V && (int)(order_key(v) >> 24) >= sel;
+                    const unsigned lanes = __ballot_sync(0xffffffffu, in);
+                    if (lanes != 0u) {
+                        int base = 0;
+                        if (lane == 0) base = atomicAdd(&sh_int, __popc(lanes));
+                        base = __shfl_sync(0xffffffffu, base, 0);
+                        if (in) {
+                            const int at = base + __popc(lanes & ((1u << lane) - 1u));
+                            list_v[at] = v;
+                            list_i[at] = i;
+                        }
+                    }
+                }
+                __syncthreads();
+                // the k_left-th largest among the candidates whose first digit is `sel`
+                unsigned prefix = (unsigned)sel << 24, mask = 0xff000000u;
+                for (int shift = 16; shift >= 0; shift -= 8) {
+                    if (tid < 256) hist[tid] = 0u;
+                    __syncthreads();
+                    for (int e = tid; e < n_cand; e += SMP_THREADS) {
+                        const unsigned key = order_key(list_v[e]);
+                        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+                    }
+                    __syncthreads();
+                    if (tid == 0) {
+                        int left = k_left;
+                        int bin = 255;
+                        for (; bin > 0; --bin) {
+                            if ((int)hist[bin] >= left) break;
+                            left -= (int)hist[bin];
+                        }
+                        sh_prefix = prefix | ((unsigned)bin << shift);
+                        sh_int = left;
+                    }
+                    __syncthreads();
+                    prefix = sh_prefix;
+                    k_left = sh_int;
+                    mask |= 255u << shift;
+                    __syncthreads();
+                }
+                const float threshold = key_value(prefix);
+                if (tid == 0) sh_int = 0;
+                __syncthreads();
+                for (int e = tid; e < n_cand; e += SMP_THREADS) {
+                    const float v = list_v[e];
+                    if (v >= threshold) {                  // ties at the edge stay
+                        const int at = atomicAdd(&sh_int, 1);
+                        if (at < SMP_SORT_MAX) { surv_v[at] = v; sort_i[at] = list_i[e]; }
+                    }
+                }
+                __syncthreads();
+                if (sh_int <= SMP_SORT_MAX) n_list = sh_int;
+                __syncthreads();
+            }
+        }
+        if (n_list >= 0) {
+            // ---- top-p and the draw over the survivors' list --------------------------------
+            int n = n_list;
+            int sz = 32;
+            while (sz < n) sz <<= 1;
+            if (a.top_p > 0.0f && a.top_p < 1.0f) {
+                double part = 0.0;
+                if (tid < n) part = exp((double)(surv_v[tid] - list_max));
+                const float sum_f = (float)block_sum_double(part, dbuf);
+                if (tid < sz) sort_p[tid] = tid < n ? expf(surv_v[tid] - list_max) / sum_f : -1.0f;
+                if (tid >= n && tid < sz) sort_i[tid] = 0x7fffffff;
+                __syncthreads();
+                // by (probability descending, index ascending); the logits move along
+                for (int size = 2; size <= sz; size <<= 1) {
+                    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                        if (tid < sz) {
+                            const int partner = tid ^ stride;
+                            if (partner > tid) {
+                                const bool descending_block = (tid & size) == 0;
+                                const float pa = sort_p[tid], pb = sort_p[partner];
+                                const int ia = sort_i[tid], ib = sort_i[partner];
+                                const bool a_first = pa > pb || (pa == pb && ia < ib);
+                                if (a_first != descending_block) {
+                                    const float va = surv_v[tid], vb = surv_v[partner];
+                                    sort_p[tid] = pb; sort_p[partner] = pa;
+                                    sort_i[tid] = ib; sort_i[partner] = ia;
+                                    surv_v[tid] = vb; surv_v[partner] = va;
+                                }
+                            }
+                        }
+                        __syncthreads();
+                    }
+                }
+                if (tid == 0) {
+                    float cum = 0.0f;
+                    int keep = n;
+                    for (int i = 0; i < n; ++i) {
+                        cum += sort_p[i];
+                        if (cum > a.top_p) { keep = i + 1; break; }
+                    }
+                    sh_int = keep;
+                }
+                __syncthreads();
+                n = sh_int;
+                __syncthreads();
+            }
+            // the draw walks the indices in ascending order: sort what is left by index
+            if (tid >= n && tid < sz) sort_i[tid] = 0x7fffffff;
+            __syncthreads();
+            for (int size = 2; size <= sz; size <<= 1) {
+                for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                    if (tid < sz) {
+                        const int partner = tid ^ stride;
+                        if (partner > tid) {
+                            const bool ascending_block = (tid & size) == 0;
+                            const int ia = sort_i[tid], ib = sort_i[partner];
+                            if ((ia < ib) != ascending_block) {
+                                const float va = surv_v[tid], vb = surv_v[partner];
+                                sort_i[tid] = ib; sort_i[partner] = ia;
+                                surv_v[tid] = vb; surv_v[partner] = va;
+                            }
+                        }
+                    }
+                    __syncthreads();
+                }
+            }
+            const float inv_temp = 1.0f / a.temp;
+            const float mx = list_max * inv_temp;          // the maximum always survives
+            const float e_t = tid < n ? expf(surv_v[tid] * inv_temp - mx) : 0.0f;
+            const double total = block_sum_double((double)e_t, dbuf);
+            const float inv_sum = (float)(1.0 / total);
+            const float pr = e_t * inv_sum;
+            // running sum over the survivors, in index order: inside a warp, then over the warps
+            double run = (double)pr;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const double up = __shfl_up_sync(0xffffffffu, run, off);
+                if (lane >= off) run += up;
+            }
+            if (lane == 31) wsum[warp] = run;
+            __syncthreads();
+            double before = 0.0;
+            for (int w = 0; w < warp; ++w) before += wsum[w];
+            const double cum = before + run;
+            const unsigned draw = st ? (unsigned)st[1] : 0u;
+            const unsigned stream = a.stream_ids ? (unsigned)a.stream_ids[row] : (unsigned)row;
+            const float r = (float)(philox_uniform_bits(a.seed, draw, stream) >> 8) *
+                            (1.0f / 16777216.0f);
+            const int first = block_min_int((tid < n && pr > 0.0f && (double)r <= cum) ? tid : SMP_THREADS, ibuf);
+            const int last = -block_min_int((tid < n && pr > 0.0f) ? -tid : 1, ibuf);
+            if (first < SMP_THREADS) chosen = sort_i[first];
+            else chosen = last >= 0 ? sort_i[last] : V - 1;
+        } else {
+        // ---- top-k in general: radix selection over the whole row ---------------------------
         if (a.top_k > 0 && a.top_k < V) {
             unsigned prefix = 0u, mask = 0u;
+
             int k_left = a.top_k;
             for (int shift = 24; shift >= 0; shift -= 8) {
                 if (tid < 256) hist[tid] = 0u;
                 __syncthreads();
-                for (int i = tid; i < V; i += SMP_THREADS) {
-                    const unsigned key = order_key(x[i]);
-                    if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+#pragma unroll 8
+                OWN_ROWS(j, i) {
+                    if (i < V) {
+                        const unsigned key = order_key(x[i]);
+                        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+                    }
                 }
                 __syncthreads();
                 if (tid == 0) {
@@ -205,8 +396,9 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleArgs a) {
                 __syncthreads();
             }
             const float threshold = key_value(prefix);
-            for (int i = tid; i < V; i += SMP_THREADS)
-                if (x[i] < threshold) x[i] = -INFINITY;
+#pragma unroll 8
+            OWN_ROWS(j, i)
+                if (i < V && x[i] < threshold) x[i] = -INFINITY;
             __syncthreads();
         }
 
@@ -214,35 +406,47 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleArgs a) {
         if (a.top_p > 0.0f && a.top_p < 1.0f) {
             int mine = 0;
             float mx_l = -INFINITY;
-            for (int i = i_begin; i < i_end; ++i) {
-                const float v = x[i];
-                if (v > -INFINITY) { ++mine; mx_l = fmaxf(mx_l, v); }
+#pragma unroll 8
+            OWN_ROWS(j, i) {
+                if (i < V) {
+                    const float v = x[i];
+                    if (v > -INFINITY) { ++mine; mx_l = fmaxf(mx_l, v); }
+                }
             }
-            const int incl = block_scan_inclusive_int(mine, ibuf);
-            if (tid == SMP_THREADS - 1) sh_int = incl;
-            __syncthreads();
-            const int n_surv = sh_int;
+            const int n_surv = block_sum_int(mine, ibuf);
             const float mx = block_max(mx_l, fscratch);
             if (n_surv > 0) {
                 double part = 0.0;
-                for (int i = i_begin; i < i_end; ++i) {
-                    const float v = x[i];
-                    if (v > -INFINITY) part += exp((double)(v - mx));
+#pragma unroll 8
+                OWN_ROWS(j, i) {
+                    if (i < V) {
+                        const float v = x[i];
+                        if (v > -INFINITY) part += exp((double)(v - mx));
+                    }
                 }
                 const float sum_f = (float)block_sum_double(part, dbuf);
                 if (n_surv <= SMP_SORT_MAX) {
-                    // gather in index order, sort by (probability descending, index ascending)
-                    if (tid < SMP_SORT_MAX) { sort_p[tid] = -1.0f; sort_i[tid] = 0x7fffffff; }
+                    // gather (in any order), sort by (probability descending, index ascending)
+                    int sz = 32;
+                    while (sz < n_surv) sz <<= 1;
+                    if (tid < sz) { sort_p[tid] = -1.0f; sort_i[tid] = 0x7fffffff; }
+                    if (tid == 0) sh_int = 0;
                     __syncthreads();
-                    int at = incl - mine;
-                    for (int i = i_begin; i < i_end; ++i) {
-                        const float v = x[i];
-                        if (v > -INFINITY) { sort_p[at] = expf(v - mx) / sum_f; sort_i[at] = i; ++at; }
+#pragma unroll 8
+                    OWN_ROWS(j, i) {
+                        if (i < V) {
+                            const float v = x[i];
+                            if (v > -INFINITY) {
+                                const int at = atomicAdd(&sh_int, 1);
+                                sort_p[at] = expf(v - mx) / sum_f;
+                                sort_i[at] = i;
+                            }
+                        }
                     }
                     __syncthreads();
-                    for (int size = 2; size <= SMP_SORT_MAX; size <<= 1) {
+                    for (int size = 2; size <= sz; size <<= 1) {
                         for (int stride = size >> 1; stride > 0; stride >>= 1) {
-                            if (tid < SMP_SORT_MAX) {
+                            if (tid < sz) {
                                 const int partner = tid ^ stride;
                                 if (partner > tid) {
                                     const bool descending_block = (tid & size) == 0;
@@ -280,8 +484,8 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleArgs a) {
                     for (int shift = 24; shift >= 0; shift -= 8) {
                         if (tid < 256) { hist[tid] = 0u; hsum[tid] = 0.0; }
                         __syncthreads();
-                        for (int i = tid; i < V; i += SMP_THREADS) {
-                            const float v = x[i];
+                        OWN_ROWS(j, i) {
+                            const float v = i < V ? x[i] : -INFINITY;
                             if (v > -INFINITY) {
                                 const float pr = expf(v - mx) / sum_f;
                                 const unsigned key = __float_as_uint(pr);
@@ -311,23 +515,30 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleArgs a) {
                     // entries equal to the threshold: keep them in index order while needed
                     const float thr = __uint_as_float(prefix);
                     int ties = 0;
-                    for (int i = i_begin; i < i_end; ++i) {
-                        const float v = x[i];
+                    OWN_ROWS(j, i) {
+                        const float v = i < V ? x[i] : -INFINITY;
                         if (v > -INFINITY && expf(v - mx) / sum_f == thr) ++ties;
                     }
-                    int rank = block_scan_inclusive_int(ties, ibuf) - ties;
+                    // ties in the warps before this one
+                    ties = warp_sum_int(ties);
+                    if (lane == 0) ibuf[warp] = ties;
+                    __syncthreads();
+                    int rank = 0;
+                    for (int w = 0; w < warp; ++w) rank += ibuf[w];
+                    __syncthreads();
                     int need = 0x7fffffff;                // ties to keep
                     if (thr > 0.0f) {
                         const double gap = (double)a.top_p - above;
                         need = gap < 0.0 ? 1 : (int)floor(gap / (double)thr) + 1;
                     }
-                    for (int i = i_begin; i < i_end; ++i) {
-                        const float v = x[i];
-                        if (v > -INFINITY) {
-                            const float pr = expf(v - mx) / sum_f;
-                            if (pr < thr) x[i] = -INFINITY;
-                            else if (pr == thr) { if (rank >= need) x[i] = -INFINITY; ++rank; }
-                        }
+                    OWN_ROWS(j, i) {
+                        const float v = i < V ? x[i] : -INFINITY;
+                        const float pr = v > -INFINITY ? expf(v - mx) / sum_f : -1.0f;
+                        const bool tie = pr == thr;
+                        const unsigned tie_lanes = __ballot_sync(0xffffffffu, tie);
+                        const int my_rank = rank + __popc(tie_lanes & ((1u << lane) - 1u));
+                        if (v > -INFINITY && (pr < thr || (tie && my_rank >= need))) x[i] = -INFINITY;
+                        rank += __popc(tie_lanes);
                     }
                     __syncthreads();
                 }
@@ -337,53 +548,105 @@ __global__ void __launch_bounds__(SMP_THREADS) sample_kernel(SampleArgs a) {
         // ---- the draw ------------------------------------------------------------------
         const float inv_temp = 1.0f / a.temp;
         float mx_l = -INFINITY;
-        for (int i = i_begin; i < i_end; ++i) mx_l = fmaxf(mx_l, x[i] * inv_temp);
+#pragma unroll 8
+        OWN_ROWS(j, i)
+            if (i < V) mx_l = fmaxf(mx_l, x[i] * inv_temp);
         const float mx = block_max(mx_l, fscratch);
         double part = 0.0;
-        for (int i = i_begin; i < i_end; ++i) {
-            const float v = x[i] * inv_temp;
-            if (v > -INFINITY) part += (double)expf(v - mx);
+#pragma unroll 8
+        OWN_ROWS(j, i) {
+            if (i < V) {
+                const float v = x[i] * inv_temp;
+                if (v > -INFINITY) part += (double)expf(v - mx);
+            }
         }
         const double total = block_sum_double(part, dbuf);
         const float inv_sum = (float)(1.0 / total);
+        // the probabilities as they are drawn from (float32, as the reference's), summed per warp
         double mine = 0.0;
-        for (int i = i_begin; i < i_end; ++i) {
-            const float v = x[i] * inv_temp;
-            if (v > -INFINITY) mine += (double)(expf(v - mx) * inv_sum);
+#pragma unroll 8
+        OWN_ROWS(j, i) {
+            if (i < V) {
+                const float v = x[i] * inv_temp;
+                if (v > -INFINITY) mine += (double)(expf(v - mx) * inv_sum);
+            }
         }
-        const double incl = block_scan_inclusive(mine, dbuf);
+        mine = warp_sum_double(mine);
+        if (lane == 0) wsum[warp] = mine;
+        __syncthreads();
         const unsigned draw = st ? (unsigned)st[1] : 0u;
         const unsigned stream = a.stream_ids ? (unsigned)a.stream_ids[row] : (unsigned)row;
         const float r = (float)(philox_uniform_bits(a.seed, draw, stream) >> 8) *
                         (1.0f / 16777216.0f);
-        // the first thread whose inclusive sum reaches r owns the answer
-        ibuf[tid] = ((double)r <= incl && mine > 0.0) ? tid : SMP_THREADS;
-        __syncthreads();
-        for (int off = SMP_THREADS / 2; off > 0; off >>= 1) {
-            if (tid < off) ibuf[tid] = min(ibuf[tid], ibuf[tid + off]);
-            __syncthreads();
+        // the first warp whose running sum reaches r owns the answer
+        double before = 0.0;
+        int owner = 32;
+        for (int w = 0; w < 32; ++w) {
+            const double incl = before + wsum[w];
+            if ((double)r <= incl && wsum[w] > 0.0) { owner = w; break; }
+            before = incl;
         }
-        const int owner = ibuf[0];
-        __syncthreads();
-        if (owner == SMP_THREADS) {
+        if (owner == 32) {
             if (tid == 0) sh_int = V - 1;                  // the reference's fallback
-        } else if (tid == owner) {
-            double cum = incl - mine;
-            int pick = -1, last_pos = -1;
-            for (int i = i_begin; i < i_end; ++i) {
+        } else if (warp == owner) {
+            auto prob = [&](int i) -> float {
+                if (i >= V) return 0.0f;
                 const float v = x[i] * inv_temp;
-                if (!(v > -INFINITY)) continue;
-                const float pr = expf(v - mx) * inv_sum;
-                if (pr <= 0.0f) continue;
-                cum += (double)pr;
-                last_pos = i;
-                if ((double)r <= cum) { pick = i; break; }
+                return v > -INFINITY ? expf(v - mx) * inv_sum : 0.0f;
+            };
+            // the range's rows of 32 indices: totals of 32 rows at a time (lane l sums row
+            // g * 32 + l: loads that do not wait for one another), then a scan over them
+            double cum = before;
+            int hit_row = -1, last_row = -1;
+            double cum_at_row = 0.0;
+            for (int g0 = 0; g0 < n_rows && hit_row < 0; g0 += 32) {
+                const int rr = g0 + lane;
+                double tot = 0.0;
+                if (rr < n_rows) {
+                    const int i0 = w_begin + rr * 32;
+#pragma unroll 8
+                    for (int e = 0; e < 32; ++e) tot += (double)prob(i0 + e);
+                }
+                double run = tot;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const double up = __shfl_up_sync(0xffffffffu, run, off);
+                    if (lane >= off) run += up;
+                }
+                const unsigned hits = __ballot_sync(0xffffffffu, tot > 0.0 && (double)r <= cum + run);
+                const unsigned live = __ballot_sync(0xffffffffu, tot > 0.0);
+                if (live != 0u) last_row = g0 + (31 - __clz(live));
+                if (hits != 0u) {
+                    const int l = __ffs(hits) - 1;
+                    hit_row = g0 + l;
+                    cum_at_row = cum + __shfl_sync(0xffffffffu, run - tot, l);
+                }
+                cum += __shfl_sync(0xffffffffu, run, 31);
             }
-            sh_int = pick >= 0 ? pick : last_pos;
+            // inside the row that crosses r (or, if rounding left none, the last row with mass)
+            const int the_row = hit_row >= 0 ? hit_row : last_row;
+            int pick = -1;
+            if (the_row >= 0) {
+                const int i = w_begin + the_row * 32 + lane;
+                const float pr = prob(i);
+                double run = (double)pr;
+#pragma unroll
+                for (int off = 1; off < 32; off <<= 1) {
+                    const double up = __shfl_up_sync(0xffffffffu, run, off);
+                    if (lane >= off) run += up;
+                }
+                const unsigned hits = __ballot_sync(0xffffffffu, hit_row >= 0 && pr > 0.0f && (double)r <= cum_at_row + run);
+                const unsigned live = __ballot_sync(0xffffffffu, pr > 0.0f);
+                if (hits != 0u) pick = i - lane + (__ffs(hits) - 1);
+                else if (live != 0u) pick = i - lane + (31 - __clz(live));
+            }
+            if (lane == 0) sh_int = pick >= 0 ? pick : V - 1;
         }
         __syncthreads();
         chosen = sh_int;
+        }   // the general path
     }
+#undef OWN_ROWS
 
     if (tid == 0) {
         a.out[row] = chosen;
