@@ -560,19 +560,17 @@ __global__ void __launch_bounds__(SMP_THREADS, 1) sample_kernel(SampleArgs a) {
                 if (v > -INFINITY) part += (double)expf(v - mx);
             }
         }
-        const double total = block_sum_double(part, dbuf);
+        // each warp's share of the sum decides which warp's range holds the answer (the share
+        // scaled by 1/sum stands for the sum of the range's float32 probabilities: they differ
+        // in the eighth digit, and a draw that falls into that gap takes the range's last token)
+        part = warp_sum_double(part);
+        if (lane == 0) wsum[warp] = part;
+        __syncthreads();
+        double total = 0.0;
+        for (int w = 0; w < 32; ++w) total += wsum[w];
         const float inv_sum = (float)(1.0 / total);
-        // the probabilities as they are drawn from (float32, as the reference's), summed per warp
-        double mine = 0.0;
-#pragma unroll 8
-        OWN_ROWS(j, i) {
-            if (i < V) {
-                const float v = x[i] * inv_temp;
-                if (v > -INFINITY) mine += (double)(expf(v - mx) * inv_sum);
-            }
-        }
-        mine = warp_sum_double(mine);
-        if (lane == 0) wsum[warp] = mine;
+        __syncthreads();
+        if (lane == 0) wsum[warp] = part * (double)inv_sum;
         __syncthreads();
         const unsigned draw = st ? (unsigned)st[1] : 0u;
         const unsigned stream = a.stream_ids ? (unsigned)a.stream_ids[row] : (unsigned)row;
