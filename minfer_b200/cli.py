@@ -21,7 +21,7 @@ USAGE = """minfer-b200 - a small B200-native LLM generation library in minfer's 
 
 USAGE:
   {prog} <model> [prompt] [OPTIONS]
-  {prog} info <model>
+  {prog} info <model>                      (also: {prog} --info <model>)
   {prog} random <config.json> <folder> [--seed N] [--store-dtype bfloat16|float32]
 
 MODEL - a folder with config.json and model.safetensors
@@ -29,7 +29,9 @@ PROMPT - token ids separated by commas or spaces, e.g. "151644,872,198"
 
 OPTIONS:
   --meta                  print the configuration and key tensors
+  --prompt-ids <IDS>      the prompt as an option instead of the second argument
   --prompt-file <FILE>    one prompt per line (token ids); all lines run as batches
+  --max-seqs <N>          sequences per batch (default: all prompts, at most 64)
   --temp <T>              sampling temperature (default 0.8; 0 = greedy)
   --greedy                greedy decoding (--temp 0)
   --top-k <K>             top-K sampling (default 40)
@@ -37,8 +39,8 @@ OPTIONS:
   --repeat-penalty <N>    penalize repeated tokens (default 1.1; 1.0 = off)
   --frequency-penalty <N> penalize by token count in the window (default 0.0)
   --presence-penalty <N>  penalize any token present in the window (default 0.0)
-  --stop <ID>             stop generation at this token id (repeatable; default: the
-                          model's eos_token_id)
+  --stop <ID>             stop generation at this token id (repeatable; also --stop-id;
+                          default: the model's eos_token_id)
   -n, --n-predict <N>     max tokens to generate (default 512)
   --seed <N>              RNG seed for sampling (default 42)
   --n-ctx <N>             context per sequence (default 4096); sizes the cache
@@ -97,6 +99,12 @@ def parse_args(argv: List[str]) -> dict:
             opts["meta"] = True
         elif a == "--prompt-file":
             opts["prompt_file"] = value(a)
+        elif a == "--prompt-ids":
+            opts["prompt"] = parse_ids(value(a))
+        elif a == "--info":
+            opts["command"] = "info"
+        elif a == "--max-seqs":
+            opts["max_seqs"] = number(a, int)
         elif a in ("--temp", "-t"):
             opts["temp"] = number(a, float)
         elif a == "--greedy":
@@ -111,7 +119,7 @@ def parse_args(argv: List[str]) -> dict:
             opts["frequency_penalty"] = number(a, float)
         elif a == "--presence-penalty":
             opts["presence_penalty"] = number(a, float)
-        elif a == "--stop":
+        elif a in ("--stop", "--stop-id"):
             opts["stop"].append(number(a, int))
         elif a in ("-n", "--n-predict"):
             opts["n_predict"] = number(a, int)
@@ -135,7 +143,11 @@ def parse_args(argv: List[str]) -> dict:
     pos = opts["positional"]
     if opts["command"] in ("help", "version"):
         return opts
-    if pos and pos[0] == "info":
+    if opts["command"] == "info":                        # --info <model>
+        if len(pos) != 1:
+            raise CliError("usage: --info <model>")
+        opts["model"] = pos[0]
+    elif pos and pos[0] == "info":
         if len(pos) != 2:
             raise CliError("usage: info <model>")
         opts["command"], opts["model"] = "info", pos[1]
@@ -150,6 +162,8 @@ def parse_args(argv: List[str]) -> dict:
             raise CliError(f"unexpected argument {pos[2]!r}")
         opts["model"] = pos[0]
         if len(pos) == 2:
+            if opts["prompt"] is not None:
+                raise CliError("a prompt was given twice (positional and --prompt-ids)")
             opts["prompt"] = parse_ids(pos[1])
     return opts
 
@@ -230,6 +244,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     model = Model.from_folder(opts["model"], opts["dtype"], "cuda:0")
     per_seq = ((min(opts["n_ctx"], model.plan.max_positions) + 63) // 64) * 64
     batch = min(len(prompts), 64)
+    if opts.get("max_seqs"):
+        batch = max(1, min(batch, opts["max_seqs"]))
     gen = Generator(model, max_tokens=per_seq * batch, max_batch=batch,
                     cuda_graphs=opts["cuda_graph"])
     sampling = SamplingParams(opts["temp"], opts["top_k"], opts["top_p"], opts["repeat_penalty"],

@@ -116,6 +116,46 @@ class Model:
             weights[spec.name] = t.contiguous()
         return model.bind(weights, device)
 
+    # ---- the short way in: the same calls under the names a user of model libraries expects --
+    @classmethod
+    def from_pretrained(cls, folder: str, dtype: Any = "bfloat16",
+                        device: torch.device | str = "cuda:0") -> "Model":
+        """``from_folder`` under its usual name: config.json + model.safetensors -> model."""
+        return cls.from_folder(folder, dtype, device)
+
+    @classmethod
+    def random(cls, config: Mapping[str, Any], seed: int = 0, dtype: Any = "bfloat16",
+               device: torch.device | str = "cuda:0") -> "Model":
+        """Seeded random weights for a configuration (``from_config`` with its defaults)."""
+        return cls.from_config(config, seed, dtype, device)
+
+    def new_session(self, max_seqs: int = 8, max_positions: int = 4096, cuda_graphs: bool = True):
+        """An ``Engine`` over this model: a cache for ``max_seqs`` sequences of up to
+        ``max_positions`` positions; ``acquire`` slots, ``step`` them, ``release`` them."""
+        from .engine.step import Engine
+        return Engine(self, max_tokens=max_seqs * max_positions, max_seqs=max_seqs,
+                      cuda_graphs=cuda_graphs)
+
+    def generate(self, prompts, max_new_tokens: int = 512, sampling=None, stop_token_ids=None,
+                 max_batch: int = 8, max_positions: int = 4096):
+        """Token ids in, ``GenerationResult``s out; builds a ``Generator`` for this call (keep
+        a ``Generator`` yourself to reuse its cache and captured graphs)."""
+        from .engine.generate import Generator
+        gen = Generator(self, max_tokens=max_batch * max_positions, max_batch=max_batch)
+        return gen.generate(prompts, max_new_tokens, sampling, stop_token_ids)
+
+    def export_state_dict(self) -> Dict[str, torch.Tensor]:
+        """The weights by their names in the checkpoint, as this model holds them (projections
+        that were packed at load come back as views into the packed storage)."""
+        p = self.plan
+        out = {p.embedding_name: self.embedding}
+        for block in self.blocks:
+            out.update(block.export(""))
+        out.update(self.final_norm.export(p.final_norm_prefix))
+        if p.head_name is not None:
+            out[p.head_name] = self.head.weight
+        return out
+
     # ---- sizes ----------------------------------------------------------------------------
     def parameter_bytes(self) -> int:
         seen, total = set(), 0

@@ -90,6 +90,21 @@ class Attention(Mixer):
         if self.position is not None:
             self.position.load(p, weights)
 
+    def export(self, prefix: str) -> Dict[str, torch.Tensor]:
+        p = f"{prefix}self_attn."
+        nq, nkv = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        out = {}
+        for name, lo, hi in (("q", 0, nq), ("k", nq, nq + nkv), ("v", nq + nkv, nq + 2 * nkv)):
+            out[f"{p}{name}_proj.weight"] = self.qkv.weight[lo:hi]
+            if self.qkv_bias:
+                out[f"{p}{name}_proj.bias"] = self.qkv.bias[lo:hi]
+        out[f"{p}o_proj.weight"] = self.out.weight
+        if self.out_bias:
+            out[f"{p}o_proj.bias"] = self.out.bias
+        if self.position is not None:
+            out.update(self.position.export(p))
+        return out
+
     # ---- what it keeps per sequence -----------------------------------------------------
     def cache_request(self) -> Optional[CacheRequest]:
         return CacheRequest(self.n_kv_heads, self.head_dim, self.window)

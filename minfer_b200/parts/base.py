@@ -132,6 +132,11 @@ class Part:
     def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
         """Takes its tensors (already on the device, in the precision they are held in)."""
 
+    def export(self, prefix: str) -> Dict[str, torch.Tensor]:
+        """The tensors of ``tensor_specs`` by name, as held (views into packed storage where
+        the part packed them at load)."""
+        return {}
+
 
 class Norm(Part):
     def forward(self, x32: torch.Tensor, out_dtype: torch.dtype,

@@ -34,6 +34,12 @@ class PreNormBlock(Block):
         for part in self._parts():
             part.load(self.prefix, weights)
 
+    def export(self, prefix: str = "") -> Dict[str, torch.Tensor]:
+        out: Dict[str, torch.Tensor] = {}
+        for part in self._parts():
+            out.update(part.export(self.prefix))
+        return out
+
     accepts_pending = True     # its norms add a pending projection output while reading h
 
     @staticmethod

@@ -58,6 +58,17 @@ class GatedMlp(FeedForward):
         self.gate_up = Linear(packed.contiguous())
         self.down = Linear(weights[f"{p}down_proj.weight"])
 
+    def export(self, prefix: str) -> Dict[str, torch.Tensor]:
+        p = f"{prefix}mlp."
+        w = self.gate_up.weight
+        if self.interleaved:
+            pairs = w.view(self.intermediate_size, 2, self.hidden_size)
+            gate, up = pairs[:, 0], pairs[:, 1]
+        else:
+            gate, up = w[:self.intermediate_size], w[self.intermediate_size:]
+        return {f"{p}gate_proj.weight": gate, f"{p}up_proj.weight": up,
+                f"{p}down_proj.weight": self.down.weight}
+
     def forward_add(self, x: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
         from ..kernels import gemm
         act = torch.empty((x.shape[0], self.intermediate_size), dtype=ctx.act_dtype,

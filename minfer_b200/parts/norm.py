@@ -28,6 +28,9 @@ class RmsNorm(Norm):
     def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
         self.weight = weights[f"{prefix}{self.name}.weight"]
 
+    def export(self, prefix: str) -> Dict[str, torch.Tensor]:
+        return {f"{prefix}{self.name}.weight": self.weight}
+
     def forward(self, x32: torch.Tensor, out_dtype: torch.dtype,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = x32.shape[0] if rows is None else rows.numel()

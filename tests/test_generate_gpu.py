@@ -116,3 +116,21 @@ def test_cli_generates(tiny, capsys):
     want = P.generate(tiny["cfg"], tiny["w"], [5, 17, 3], 6)
     assert " ".join(str(t) for t in want) in out
     assert "Prefill: 3 tokens" in out and "Generated: 6 tokens" in out
+
+
+def test_model_conveniences(tiny):
+    """``from_pretrained``, ``new_session`` and ``Model.generate`` are the loader, the engine
+    and the generator under other names: the same logits and tokens."""
+    from minfer_b200.model import Model
+    from minfer_b200.sampling.params import SamplingParams
+    model = Model.from_pretrained(tiny["folder"], "float32")
+    ids = [5, 17, 3, 9]
+    session = model.new_session(max_seqs=2, max_positions=128)
+    s = session.acquire()
+    logits = session.step([s], [ids], [list(range(len(ids)))])
+    session.release(s)
+    want = P.forward(tiny["cfg"], tiny["w"], ids)
+    assert float((logits.double().cpu() - want).abs().max() / want.abs().max()) < 2e-5
+    out = model.generate([ids], 5, SamplingParams.greedy(), stop_token_ids=[], max_batch=1,
+                         max_positions=128)
+    assert out[0].tokens == P.generate(tiny["cfg"], tiny["w"], ids, 5)

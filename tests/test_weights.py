@@ -132,3 +132,24 @@ def test_random_mode_is_a_function_of_seed_and_name_only(tmp_path):
     # in-place random weights equal the folder's
     m = Model.from_config(TINY_B, seed=11, dtype="bfloat16", device="cpu")
     assert torch.equal(m.embedding, ta["model.embed_tokens.weight"])
+
+
+def test_export_state_dict_returns_what_was_loaded():
+    """Packed projections come back under their checkpoint names with the loaded values, in
+    both engines (rows alternate gate/up in the bfloat16 one)."""
+    import tempfile
+
+    import torch
+    from helpers import TINY_B
+    from minfer_b200.model import Model, write_random_model
+    from minfer_b200.weights.safetensors_io import load_all
+    with tempfile.TemporaryDirectory() as folder:
+        write_random_model(folder, TINY_B, 3, "bfloat16")
+        stored = load_all(folder)
+        for dtype in ("bfloat16", "float32"):
+            model = Model.from_pretrained(folder, dtype, "cpu")
+            got = model.export_state_dict()
+            assert set(got) == set(stored)
+            for name, t in stored.items():
+                assert got[name].shape == t.shape
+                assert torch.equal(got[name].float(), t.float()), name
