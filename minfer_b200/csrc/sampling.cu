@@ -104,6 +104,57 @@ __device__ int block_min_int(int v, int* buf) {
     __syncthreads();
     return r;
 }
+// The k-th largest of `n` values in shared memory (1 <= k <= n), by radix selection over the
+// order-preserving bits; every thread of the block calls it and gets the value.
+__device__ float kth_largest(const float* vals, int n, int k, unsigned* hist, unsigned* sh_prefix,
+                             int* sh_left) {
+    unsigned prefix = 0u, mask = 0u;
+    int k_left = k;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        if (threadIdx.x < 256) hist[threadIdx.x] = 0u;
+        __syncthreads();
+        for (int e = threadIdx.x; e < n; e += SMP_THREADS) {
+            const unsigned key = order_key(vals[e]);
+            if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            // the highest bin at which the count from the top reaches k_left: lane l holds the
+            // bins 255 - 8 l down to 248 - 8 l
+            const int lane = threadIdx.x;
+            int mine[8], total = 0;
+#pragma unroll
+            for (int b = 0; b < 8; ++b) { mine[b] = (int)hist[255 - 8 * lane - b]; total += mine[b]; }
+            int incl = total;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, off);
+                if (lane >= off) incl += up;
+            }
+            const unsigned reach = __ballot_sync(0xffffffffu, incl >= k_left);
+            const int owner = reach != 0u ? __ffs(reach) - 1 : 31;
+            if (lane == owner) {
+                int left = k_left - (incl - total);
+                int b = 0;
+                for (; b < 7; ++b) {
+                    if (mine[b] >= left) break;
+                    left -= mine[b];
+                }
+                int bin = 255 - 8 * lane - b;
+                if (reach == 0u) { bin = 0; left = 1; }      // fewer than k values: the lowest bin
+                *sh_prefix = prefix | ((unsigned)bin << shift);
+                *sh_left = left;
+            }
+        }
+        __syncthreads();
+        prefix = *sh_prefix;
+        k_left = *sh_left;
+        mask |= 255u << shift;
+        __syncthreads();
+    }
+    return key_value(prefix);
+}
+
 // The row is cut into 32 consecutive ranges, one per warp; a warp walks its range in rows of
 // 32 consecutive indices, lane l taking the l-th: loads are coalesced and (warp, row, lane)
 // is the index order, which the draw and the ties of top-p need.
@@ -117,6 +168,7 @@ __global__ void __launch_bounds__(SMP_THREADS, 1) sample_kernel(SampleArgs a) {
     __shared__ unsigned hist[256];
     __shared__ double hsum[256];
     __shared__ double wsum[32];
+    __shared__ double rowtot[SMP_THREADS];       // the draw: sums of the owner range's rows
     __shared__ float list_v[SMP_LIST_MAX];       // top-k: the candidates of the highest digits
     __shared__ int list_i[SMP_LIST_MAX];
     __shared__ float surv_v[SMP_SORT_MAX];       // top-k: the survivors' logits, beside sort_p / sort_i
@@ -180,82 +232,48 @@ __global__ void __launch_bounds__(SMP_THREADS, 1) sample_kernel(SampleArgs a) {
         const int first = block_min_int((best_i != V && best == mx) ? best_i : V, ibuf);
         chosen = first < V ? first : 0;
     } else {
-        // ---- top-k, the usual case: the k-th largest value lies among the few highest first
-        // digits (sign and exponent bits).  Three passes over the row (maximum; counts of the
-        // four highest digits, in registers; gather of those candidates into shared memory),
-        // then everything else (the exact threshold, top-p, the draw) on the short list.
+        // ---- top-k, the usual case (k up to a few hundred).  Every thread has the maximum of
+        // its own elements; the k-th largest of those 1024 maxima is a lower bound of the k-th
+        // largest element (k elements reach it), so whatever passes it is a candidate: about k
+        // elements whatever the logits' distribution.  Two passes over the row (maxima; gather
+        // of the candidates into shared memory), then everything else (the exact threshold,
+        // top-p, the draw) on the short list.
         int n_list = -1;                                   // >= 0: survivors are in surv_v / sort_i
         float list_max = -INFINITY;
-        if (a.top_k > 0 && a.top_k < V) {
+        if (a.top_k > 0 && a.top_k < V && a.top_k <= SMP_THREADS) {
             float mx_l = -INFINITY;
 #pragma unroll 8
             OWN_ROWS(j, i)
                 if (i < V) mx_l = fmaxf(mx_l, x[i]);
             list_max = block_max(mx_l, fscratch);
-            const int d_max = (int)(order_key(list_max) >> 24);
-            int c0 = 0, c1 = 0, c2 = 0, c3 = 0;
-#pragma unroll 8
-            OWN_ROWS(j, i) {
-                if (i < V) {
-                    const int d = (int)(order_key(x[i]) >> 24);
-                    c0 += d == d_max; c1 += d == d_max - 1; c2 += d == d_max - 2; c3 += d == d_max - 3;
-                }
-            }
-            const int cnt[4] = {block_sum_int(c0, ibuf), block_sum_int(c1, ibuf), block_sum_int(c2, ibuf),
-                                block_sum_int(c3, ibuf)};
-            int sel = -1, k_left = a.top_k, n_cand = 0;
-            for (int t = 0; t < 4; ++t) {
-                n_cand += cnt[t];
-                if (cnt[t] >= k_left) { sel = d_max - t; break; }
-                k_left -= cnt[t];
-            }
-            if (sel >= 0 && n_cand <= SMP_LIST_MAX) {
-                if (tid == 0) sh_int = 0;
-                __syncthreads();
+            list_v[tid] = mx_l;
+            __syncthreads();
+            const float bound = kth_largest(list_v, SMP_THREADS, a.top_k, hist, &sh_prefix, &sh_int);
+            if (tid == 0) sh_int = 0;
+            __syncthreads();
+            if (bound > -INFINITY) {
 #pragma unroll 8
                 OWN_ROWS(j, i) {
-                    const float v = i < V ? x[i] : 0.0f;
-                    const bool in = i < V && (int)(order_key(v) >> 24) >= sel;
+                    const float v = i < V ? x[i] : -INFINITY;
+                    const bool in = i < V && v >= bound;
                     const unsigned lanes = __ballot_sync(0xffffffffu, in);
                     if (lanes != 0u) {
                         int base = 0;
                         if (lane == 0) base = atomicAdd(&sh_int, __popc(lanes));
                         base = __shfl_sync(0xffffffffu, base, 0);
-                        if (in) {
-                            const int at = base + __popc(lanes & ((1u << lane) - 1u));
+                        const int at = base + __popc(lanes & ((1u << lane) - 1u));
+                        if (in && at < SMP_LIST_MAX) {
                             list_v[at] = v;
                             list_i[at] = i;
                         }
                     }
                 }
-                __syncthreads();
-                // the k_left-th largest among the candidates whose first digit is `sel`
-                unsigned prefix = (unsigned)sel << 24, mask = 0xff000000u;
-                for (int shift = 16; shift >= 0; shift -= 8) {
-                    if (tid < 256) hist[tid] = 0u;
-                    __syncthreads();
-                    for (int e = tid; e < n_cand; e += SMP_THREADS) {
-                        const unsigned key = order_key(list_v[e]);
-                        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
-                    }
-                    __syncthreads();
-                    if (tid == 0) {
-                        int left = k_left;
-                        int bin = 255;
-                        for (; bin > 0; --bin) {
-                            if ((int)hist[bin] >= left) break;
-                            left -= (int)hist[bin];
-                        }
-                        sh_prefix = prefix | ((unsigned)bin << shift);
-                        sh_int = left;
-                    }
-                    __syncthreads();
-                    prefix = sh_prefix;
-                    k_left = sh_int;
-                    mask |= 255u << shift;
-                    __syncthreads();
-                }
-                const float threshold = key_value(prefix);
+            }
+            __syncthreads();
+            const int n_cand = sh_int;
+            __syncthreads();
+            if (n_cand >= a.top_k && n_cand <= SMP_LIST_MAX) {
+                const float threshold = kth_largest(list_v, n_cand, a.top_k, hist, &sh_prefix, &sh_int);
                 if (tid == 0) sh_int = 0;
                 __syncthreads();
                 for (int e = tid; e < n_cand; e += SMP_THREADS) {
@@ -584,61 +602,64 @@ __global__ void __launch_bounds__(SMP_THREADS, 1) sample_kernel(SampleArgs a) {
             if ((double)r <= incl && wsum[w] > 0.0) { owner = w; break; }
             before = incl;
         }
+        auto prob = [&](int i) -> float {
+            if (i >= V) return 0.0f;
+            const float v = x[i] * inv_temp;
+            return v > -INFINITY ? expf(v - mx) * inv_sum : 0.0f;
+        };
         if (owner == 32) {
             if (tid == 0) sh_int = V - 1;                  // the reference's fallback
-        } else if (warp == owner) {
-            auto prob = [&](int i) -> float {
-                if (i >= V) return 0.0f;
-                const float v = x[i] * inv_temp;
-                return v > -INFINITY ? expf(v - mx) * inv_sum : 0.0f;
-            };
-            // the range's rows of 32 indices: totals of 32 rows at a time (lane l sums row
-            // g * 32 + l: loads that do not wait for one another), then a scan over them
-            double cum = before;
-            int hit_row = -1, last_row = -1;
-            double cum_at_row = 0.0;
-            for (int g0 = 0; g0 < n_rows && hit_row < 0; g0 += 32) {
-                const int rr = g0 + lane;
-                double tot = 0.0;
-                if (rr < n_rows) {
-                    const int i0 = w_begin + rr * 32;
-#pragma unroll 8
-                    for (int e = 0; e < 32; ++e) tot += (double)prob(i0 + e);
-                }
-                double run = tot;
-#pragma unroll
-                for (int off = 1; off < 32; off <<= 1) {
-                    const double up = __shfl_up_sync(0xffffffffu, run, off);
-                    if (lane >= off) run += up;
-                }
-                const unsigned hits = __ballot_sync(0xffffffffu, tot > 0.0 && (double)r <= cum + run);
-                const unsigned live = __ballot_sync(0xffffffffu, tot > 0.0);
-                if (live != 0u) last_row = g0 + (31 - __clz(live));
-                if (hits != 0u) {
-                    const int l = __ffs(hits) - 1;
-                    hit_row = g0 + l;
-                    cum_at_row = cum + __shfl_sync(0xffffffffu, run - tot, l);
-                }
-                cum += __shfl_sync(0xffffffffu, run, 31);
+        } else {
+            // all warps: the sums of the owner range's rows of 32 indices
+            const int o_begin = owner * n_rows * 32;
+            for (int rr = warp; rr < n_rows; rr += 32) {
+                const double tot = warp_sum_double((double)prob(o_begin + rr * 32 + lane));
+                if (lane == 0) rowtot[rr] = tot;
             }
-            // inside the row that crosses r (or, if rounding left none, the last row with mass)
-            const int the_row = hit_row >= 0 ? hit_row : last_row;
-            int pick = -1;
-            if (the_row >= 0) {
-                const int i = w_begin + the_row * 32 + lane;
-                const float pr = prob(i);
-                double run = (double)pr;
+            __syncthreads();
+            if (warp == 0) {
+                // the first row at which the running sum reaches r (32 rows at a time)
+                double cum = before;
+                int hit_row = -1, last_row = -1;
+                double cum_at_row = 0.0;
+                for (int g0 = 0; g0 < n_rows && hit_row < 0; g0 += 32) {
+                    const int rr = g0 + lane;
+                    const double tot = rr < n_rows ? rowtot[rr] : 0.0;
+                    double run = tot;
 #pragma unroll
-                for (int off = 1; off < 32; off <<= 1) {
-                    const double up = __shfl_up_sync(0xffffffffu, run, off);
-                    if (lane >= off) run += up;
+                    for (int off = 1; off < 32; off <<= 1) {
+                        const double up = __shfl_up_sync(0xffffffffu, run, off);
+                        if (lane >= off) run += up;
+                    }
+                    const unsigned hits = __ballot_sync(0xffffffffu, tot > 0.0 && (double)r <= cum + run);
+                    const unsigned live = __ballot_sync(0xffffffffu, tot > 0.0);
+                    if (live != 0u) last_row = g0 + (31 - __clz(live));
+                    if (hits != 0u) {
+                        const int l = __ffs(hits) - 1;
+                        hit_row = g0 + l;
+                        cum_at_row = cum + __shfl_sync(0xffffffffu, run - tot, l);
+                    }
+                    cum += __shfl_sync(0xffffffffu, run, 31);
                 }
-                const unsigned hits = __ballot_sync(0xffffffffu, hit_row >= 0 && pr > 0.0f && (double)r <= cum_at_row + run);
-                const unsigned live = __ballot_sync(0xffffffffu, pr > 0.0f);
-                if (hits != 0u) pick = i - lane + (__ffs(hits) - 1);
-                else if (live != 0u) pick = i - lane + (31 - __clz(live));
+                // inside that row (or, if rounding left none, the last row with mass)
+                const int the_row = hit_row >= 0 ? hit_row : last_row;
+                int pick = -1;
+                if (the_row >= 0) {
+                    const int i = o_begin + the_row * 32 + lane;
+                    const float pr = prob(i);
+                    double run = (double)pr;
+#pragma unroll
+                    for (int off = 1; off < 32; off <<= 1) {
+                        const double up = __shfl_up_sync(0xffffffffu, run, off);
+                        if (lane >= off) run += up;
+                    }
+                    const unsigned hits = __ballot_sync(0xffffffffu, hit_row >= 0 && pr > 0.0f && (double)r <= cum_at_row + run);
+                    const unsigned live = __ballot_sync(0xffffffffu, pr > 0.0f);
+                    if (hits != 0u) pick = i - lane + (__ffs(hits) - 1);
+                    else if (live != 0u) pick = i - lane + (31 - __clz(live));
+                }
+                if (lane == 0) sh_int = pick >= 0 ? pick : V - 1;
             }
-            if (lane == 0) sh_int = pick >= 0 ? pick : V - 1;
         }
         __syncthreads();
         chosen = sh_int;
@@ -662,6 +683,7 @@ extern "C" int mf_sample(float* logits, long long ld, int rows, int vocab, const
                          unsigned long long seed, int update_state, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return MF_ERR_ARGUMENT;
+    if ((vocab + SMP_THREADS - 1) / SMP_THREADS > SMP_THREADS) return MF_ERR_UNSUPPORTED;   // over 1,048,576
     SampleArgs a;
     a.logits = logits; a.ld = ld; a.vocab = vocab; a.slots = slots; a.state = state;
     a.stream_ids = stream_ids; a.out = out; a.temp = temp; a.top_k = top_k; a.top_p = top_p;
