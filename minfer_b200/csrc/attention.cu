@@ -165,26 +165,44 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attention_generic_kernel(AttnA
     }
 }
 
-// merges the chunks of one (row, head) in chunk order
+// merges the chunks of one (row, head) in chunk order.  The chunks' maxima and sums are
+// fetched once (a load per thread), the factors exp(m_c - m) computed once per chunk; then
+// every thread sums its output dimension over the chunks with loads that do not wait for one
+// another.  Dynamic shared memory: 2 * n_chunks floats.
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ partial, T* __restrict__ out,
                                          int n_chunks, int hd) {
     pdl_prologue();
+    extern __shared__ float comb_s[];
+    float* f_s = comb_s;                              // m_c, then the factor of chunk c
+    float* l_s = comb_s + n_chunks;
+    __shared__ float red_s[33];
     const size_t rh = blockIdx.x;                     // row * n_heads + head
-    const float* p = partial + rh * n_chunks * (hd + 2);
-    float m = -INFINITY;
-    for (int c = 0; c < n_chunks; ++c) m = fmaxf(m, p[(size_t)c * (hd + 2)]);
-    float l = 0.0f;
-    for (int c = 0; c < n_chunks; ++c) {
-        const float mc = p[(size_t)c * (hd + 2)];
-        if (mc > -INFINITY) l += p[(size_t)c * (hd + 2) + 1] * expf(mc - m);
+    const size_t stride = (size_t)(hd + 2);
+    const float* p = partial + rh * n_chunks * stride;
+    float m_l = -INFINITY;
+    for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
+        const float mc = p[(size_t)c * stride];
+        f_s[c] = mc;
+        l_s[c] = p[(size_t)c * stride + 1];
+        m_l = fmaxf(m_l, mc);
     }
+    const float m = block_max(m_l, red_s);            // (also orders the writes above)
+    float l_l = 0.0f;
+    for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
+        const float mc = f_s[c];
+        const float f = mc > -INFINITY ? expf(mc - m) : 0.0f;
+        f_s[c] = f;
+        l_l += l_s[c] * f;
+    }
+    const float l = block_sum(l_l, red_s);
     const float inv = 1.0f / l;
     for (int d = threadIdx.x; d < hd; d += blockDim.x) {
         float o = 0.0f;
+#pragma unroll 8
         for (int c = 0; c < n_chunks; ++c) {
-            const float mc = p[(size_t)c * (hd + 2)];
-            if (mc > -INFINITY) o = fmaf(p[(size_t)c * (hd + 2) + 2 + d], expf(mc - m), o);
+            const float f = f_s[c];
+            if (f > 0.0f) o = fmaf(p[(size_t)c * stride + 2 + d], f, o);
         }
         out[rh * hd + d] = from_f32<T>(o * inv);
     }
@@ -223,7 +241,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // MINB: CTAs per SM the registers are cut for.  Two (128 registers) are faster while all CTAs
 // fit on the GPU at once; with many rounds of CTAs a third one per SM (80 registers) keeps
 // more loads in flight (batch 64: 2.8 % of a step).
-template <int HD, int MINB>
+// LOOP: the chunk may hold more than one block of 256 keys.
+template <int HD, int MINB, bool LOOP>
 __global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_kernel(AttnArgs a) {
     pdl_prologue();
     constexpr int CPR = HD / 8;                       // 16-byte chunks per row
@@ -244,10 +263,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_ker
     const int pos = a.row_pos[row];
     const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
     const int hi = pos + 1;
-    const int c_lo = chunk_id * 256;
+    // the CTA's chunk: a.chunk keys (a multiple of 256), walked in blocks of 256; every warp
+    // carries its running maximum, sum and output from block to block
+    const int chunk_lo = chunk_id * a.chunk;
     const size_t part_stride = (size_t)(HD + 2);
     float* part0 = a.partial + (((size_t)row * a.n_heads + (size_t)hk * G) * a.n_chunks + chunk_id) * part_stride;
-    if (max(lo, c_lo) >= min(hi, c_lo + 256)) {       // nothing of this chunk is visible
+    if (max(lo, chunk_lo) >= min(hi, chunk_lo + a.chunk)) {       // nothing of this chunk is visible
         if (tid < G) {
             float* p = part0 + (size_t)tid * a.n_chunks * part_stride;
             p[0] = -INFINITY;
@@ -256,15 +277,17 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_ker
         return;
     }
 
-    const int j0 = c_lo + warp * DEC_KEYS;            // first position of this warp's keys
-    const int w_lo = max(lo, j0), w_hi = min(hi, j0 + DEC_KEYS);
-    const bool active = w_lo < w_hi;
     float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
     float o[HD / 8][4];
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
 
+    for (int c_lo = chunk_lo; c_lo == chunk_lo || (LOOP && c_lo < chunk_lo + a.chunk && c_lo < hi); c_lo += 256) {
+    const int j0 = c_lo + warp * DEC_KEYS;            // first position of this warp's keys
+    const int w_lo = max(lo, j0), w_hi = min(hi, j0 + DEC_KEYS);
+    const bool active = w_lo < w_hi;
     if (active) {
+        __syncwarp();                                 // the block before is done with the warp's values
         const int p_eff = a.ring > 0 ? j0 % a.ring : j0;
         const int page = a.page_table[(size_t)b * a.table_stride + (p_eff >> 6)];
         const size_t tile = (((size_t)page * a.n_kv + hk) * MF_PAGE + (j0 & (MF_PAGE - 1))) * HD;
@@ -317,8 +340,9 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_ker
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) mma_bf16_16816(sacc[nt], qa[2 * s + 1], kv[nt][s].z, kv[nt][s].w);
         }
-        // scale (to base 2), mask by position, row maxima
+        // scale (to base 2), mask by position, row maxima (on top of the blocks before)
         const float sl2 = a.scale * 1.4426950408889634f;
+        const float m_old[2] = {m_r[0], m_r[1]};
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -334,6 +358,14 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_ker
             m_r[r] = fmaxf(m_r[r], __shfl_xor_sync(0xffffffffu, m_r[r], 1));
             m_r[r] = fmaxf(m_r[r], __shfl_xor_sync(0xffffffffu, m_r[r], 2));
         }
+        if (LOOP && c_lo != chunk_lo) {
+            // what the warp holds from earlier blocks comes down to the new maxima
+            const float c0 = m_old[0] > -INFINITY ? exp2f(m_old[0] - m_r[0]) : 0.0f;
+            const float c1 = m_old[1] > -INFINITY ? exp2f(m_old[1] - m_r[1]) : 0.0f;
+            l_r[0] *= c0; l_r[1] *= c1;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+        }
         uint32_t pa[NT / 2][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -346,12 +378,6 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_ker
             pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16(p[0], p[1]);
             pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(p[2], p[3]);
         }
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 1);
-            l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 2);
-        }
-
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncwarp();
         // O[16 heads][HD] = P[16][32] V[32][HD]
@@ -370,6 +396,13 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_ker
                 mma_bf16_16816(o[2 * np + 1], pa[ks], r2, r3);
             }
         }
+    }
+    }   // blocks of the chunk
+    // the four lanes of a row each hold a part of its sum
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 1);
+        l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 2);
     }
     // maxima (base-2 units) and sums of every warp, then the factors that bring them to the
     // chunk's maximum
@@ -413,27 +446,30 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_ker
     }
 }
 
-template <int HD, int MINB>
+template <int HD, int MINB, bool LOOP>
 static int launch_decode_mma_as(const AttnArgs& a, cudaStream_t stream) {
     constexpr int smem = DEC_WARPS * 16 * (HD + 8) * 4 + DEC_WARPS * 16 * 3 * 4;
     static_assert(DEC_WARPS * DEC_KEYS * HD * 2 <= DEC_WARPS * 16 * (HD + 8) * 4, "values fit the staging area");
-    static_assert(DEC_WARPS * DEC_KEYS == 256, "a CTA covers one 256-key chunk");
+    static_assert(DEC_WARPS * DEC_KEYS == 256, "a CTA walks its chunk in blocks of 256 keys");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, MINB>,
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, MINB, LOOP>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(a.n_chunks, a.n_kv, a.rows);
-    mf_launch(attention_decode_mma_kernel<HD, MINB>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, a);
+    mf_launch(attention_decode_mma_kernel<HD, MINB, LOOP>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, a);
     return MF_LAUNCH_CHECK();
 }
 
 template <int HD>
 static int launch_decode_mma(const AttnArgs& a, cudaStream_t stream) {
+    // chunks of several blocks carry more state in registers: two CTAs per SM
+    if (a.chunk > 256) return launch_decode_mma_as<HD, 2, true>(a, stream);
     const long long ctas = (long long)a.n_chunks * a.n_kv * a.rows;
-    return ctas > 2 * 296 ? launch_decode_mma_as<HD, 3>(a, stream) : launch_decode_mma_as<HD, 2>(a, stream);
+    return ctas > 2 * 296 ? launch_decode_mma_as<HD, 3, false>(a, stream)
+                          : launch_decode_mma_as<HD, 2, false>(a, stream);
 }
 
 static int check_sizes(int n_heads, int n_kv, int hd) {
@@ -475,6 +511,7 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
     if (rows <= 0) return 0;
     if (int e = check_sizes(n_heads, n_kv, hd)) return e;
     if (n_chunks < 1 || (n_chunks > 1 && (partial == nullptr || chunk <= 0))) return MF_ERR_ARGUMENT;
+    if (n_chunks > 6000) return MF_ERR_UNSUPPORTED;    // the merge keeps two floats per chunk in shared memory
     if (ring % MF_PAGE != 0) return MF_ERR_ARGUMENT;
     AttnArgs a{};
     a.q = q; a.k = k_cache; a.v = v_cache; a.row_seq = row_seq; a.row_pos = row_pos;
@@ -484,7 +521,7 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
     a.chunk = chunk; a.n_chunks = n_chunks; a.scale = scale;
     // tensor-core path: bfloat16, head size 64 or 128, groups of up to 16 heads, 256-key chunks
     const bool fast = dtype == MF_DTYPE_BF16 && (hd == 64 || hd == 128) && n_heads / n_kv <= 16 &&
-                      chunk == 256 && partial != nullptr && rows <= 65535 && n_kv <= 65535 &&
+                      chunk >= 256 && chunk % 256 == 0 && partial != nullptr && rows <= 65535 && n_kv <= 65535 &&
                       !force_generic;
     if (fast) {
         a.partial = partial;
@@ -492,8 +529,8 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
         if (e) return e;
         // measured: started early, the merge of the chunks costs 5 us more than it saves (its
         // blocks sit on the SMs while the last attention blocks still look for room)
-        mf_launch_ex(false, attention_combine_kernel<__nv_bfloat16>, dim3(rows * n_heads), dim3(hd), 0,
-                     stream, partial, (__nv_bfloat16*)out, n_chunks, hd);
+        mf_launch_ex(false, attention_combine_kernel<__nv_bfloat16>, dim3(rows * n_heads), dim3(hd),
+                     (size_t)n_chunks * 8, stream, partial, (__nv_bfloat16*)out, n_chunks, hd);
         return MF_LAUNCH_CHECK();
     }
     const long long items = (long long)rows * n_heads * n_chunks;
@@ -508,10 +545,10 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
     if (e || n_chunks == 1) return e;
     const int threads = hd >= 128 ? 128 : (hd >= 64 ? 64 : 32);
     if (dtype == MF_DTYPE_F32)
-        mf_launch(attention_combine_kernel<float>, dim3(rows * n_heads), dim3(threads), 0, stream, 
+        mf_launch(attention_combine_kernel<float>, dim3(rows * n_heads), dim3(threads), (size_t)n_chunks * 8, stream,
             partial, (float*)out, n_chunks, hd);
     else
-        mf_launch(attention_combine_kernel<__nv_bfloat16>, dim3(rows * n_heads), dim3(threads), 0, stream, 
+        mf_launch(attention_combine_kernel<__nv_bfloat16>, dim3(rows * n_heads), dim3(threads), (size_t)n_chunks * 8, stream,
             partial, (__nv_bfloat16*)out, n_chunks, hd);
     return MF_LAUNCH_CHECK();
 }

@@ -120,6 +120,11 @@ def attention_decode_b8(reps):
     attention_decode(reps, batch=8)
 
 
+def attention_decode_long(reps):
+    """Decode attention of 8 sequences at 8,192 cached positions: reads 537 MB of K and V."""
+    attention_decode(reps, batch=8, ctx=8192)
+
+
 def attention_prefill(reps, tokens=2048):
     """Causal attention of one 2,048-token prompt, 28 heads: 30 GFLOP."""
     q = torch.randn(tokens, NH, HD, device="cuda").bfloat16()
@@ -203,7 +208,7 @@ def step_decode(reps, layers=4):
 
 
 CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_decode_m64, gemm_decode_split_m64, gemm_prefill, gemm_prefill_down,
-                                 attention_decode, attention_decode_b8, attention_prefill,
+                                 attention_decode, attention_decode_b8, attention_decode_long, attention_prefill,
                                  attention_prefill_tc, attention_prefill_tc_8k, attention_prefill_8k,
                                  step_prefill, step_decode)}
 

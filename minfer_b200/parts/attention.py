@@ -24,10 +24,26 @@ from ..weights.spec import MATRIX, VECTOR, Init, TensorSpec
 from .base import CacheRequest, CallBinding, Mixer, StepContext, settle_pending
 from .linear import Linear
 
-DECODE_CHUNK = 256     # keys per chunk when attending over the cache
+DECODE_CHUNK = 256     # keys per block when attending over the cache
+DECODE_CTAS = 296      # CTAs the decode kernel wants in flight: two on each of 148 SMs
 FORCE_GENERIC_ATTENTION = os.environ.get("MINFER_B200_GENERIC_ATTENTION", "0") == "1"
 # "tcgen05" (tensor memory, the default) or "mma" (the mma.sync twin) for whole prompts in bfloat16
 PROMPT_ATTENTION = os.environ.get("MINFER_B200_PROMPT_ATTENTION", "tcgen05")
+
+
+def decode_chunks(items: int, max_end: int, tensor_cores: bool = True) -> tuple:
+    """How attention over the cache cuts the keys: (keys per chunk, chunks).  A chunk is a
+    CTA's work and a multiple of 256 keys.  The tensor-core kernel is fastest when the CTAs of
+    all ``items`` (rows x key/value heads) fill the GPU about once, two to an SM: with few
+    items or long contexts a CTA then walks several blocks of 256 keys (8 sequences at 8,192
+    positions: 36.7 us with 4 blocks a CTA against 46.0 with one; at 32,000: 108 against
+    157 us), and fewer chunks are left to merge."""
+    blocks = max(1, -(-max_end // DECODE_CHUNK))
+    if not tensor_cores or items * blocks <= DECODE_CTAS * 3 // 2:
+        return DECODE_CHUNK, blocks                    # one block a CTA: up to three CTAs on an SM
+    n_chunks = max(1, min(blocks, DECODE_CTAS // max(items, 1)))
+    per = -(-blocks // n_chunks)
+    return per * DECODE_CHUNK, -(-blocks // per)
 
 
 class Attention(Mixer):
@@ -171,16 +187,16 @@ class Attention(Mixer):
                 raise K.KernelError(
                     "a windowed cache is read one token at a time: several tokens of a sequence "
                     "in one step must start at position 0")
-            lo_bound = ctx.max_end
-            n_chunks = max(1, -(-lo_bound // DECODE_CHUNK))
+            chunk, n_chunks = decode_chunks(n * nk, ctx.max_end, tensor_cores=(
+                act == torch.bfloat16 and hd in (64, 128) and nh // nk <= 16
+                and not FORCE_GENERIC_ATTENTION))
             partial = None
             if n_chunks > 1 or act == torch.bfloat16:
                 partial = torch.empty((n * nh * n_chunks * (hd + 2),), dtype=torch.float32,
                                       device=dev)
             K.attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions, cache.page_table,
                               cache.table_stride, cache.ring, o, partial, nh, nk, hd, self.window,
-                              DECODE_CHUNK, n_chunks, self.scale,
-                              force_generic=FORCE_GENERIC_ATTENTION)
+                              chunk, n_chunks, self.scale, force_generic=FORCE_GENERIC_ATTENTION)
         pending = self.out.partial_sums(o)
         if pending is None:
             self.out.forward(o, torch.float32, out=residual, accumulate=True)

@@ -434,6 +434,13 @@ def test_attention_decode_tensor_core_kernel(hd, nh, nk, window, ring):
         K.attention_paged(q, kc, vc, row_seq, row_pos, table.cuda(), width, ring, out, partial,
                           nh, nk, hd, window, 256, n_chunks, scale, force_generic=force)
         outs[force] = out
+    # chunks of several 256-key blocks (a CTA walks them with a running softmax)
+    for chunk, chunks in ((512, 2), (1024, 1), (768, 2)):
+        out = torch.full((B, nh * hd), float("nan"), dtype=dt, device="cuda")
+        partial = torch.full((B * nh * chunks * (hd + 2),), float("nan"), device="cuda")
+        K.attention_paged(q, kc, vc, row_seq, row_pos, table.cuda(), width, ring, out, partial,
+                          nh, nk, hd, window, chunk, chunks, scale)
+        close(out, outs[False].double(), dt, scale=3.0)
         for b, n in enumerate(lens):
             qq = torch.zeros(n, nh, hd, dtype=torch.float64)
             qq[n - 1] = q[b].double().cpu()
