@@ -255,6 +255,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_ker
     float* o_s = (float*)dec_smem;
     float* ml_s = (float*)(dec_smem + DEC_WARPS * 16 * OS * 4);          // [DEC_WARPS][16][2]
     float* f_s = ml_s + DEC_WARPS * 16 * 2;                              // [DEC_WARPS][16] merge factors
+    float* l_s = f_s + DEC_WARPS * 16;                                   // [16] the chunk's sums
 
     const int chunk_id = blockIdx.x, hk = blockIdx.y, row = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -423,7 +424,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_ker
             f_s[w * 16 + tid] = f;
             l += ml_s[(w * 16 + tid) * 2 + 1] * f;
         }
-        if (tid < G) {
+        l_s[tid] = l;
+        if (tid < G && a.n_chunks > 1) {
             float* p = part0 + (size_t)tid * a.n_chunks * part_stride;
             p[0] = m * 0.6931471805599453f;           // back to natural-log units for the merge
             p[1] = l;
@@ -442,13 +444,17 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_ker
         float acc = 0.0f;
 #pragma unroll
         for (int w = 0; w < DEC_WARPS; ++w) acc = fmaf(o_s[((size_t)w * 16 + r) * OS + d], f_s[w * 16 + r], acc);
-        part0[(size_t)r * a.n_chunks * part_stride + 2 + d] = acc;
+        if (a.n_chunks > 1)
+            part0[(size_t)r * a.n_chunks * part_stride + 2 + d] = acc;
+        else        // the only chunk: the result itself, no merge kernel follows
+            ((__nv_bfloat16*)a.out)[((size_t)row * a.n_heads + (size_t)hk * G + r) * HD + d] =
+                __float2bfloat16(acc / l_s[r]);
     }
 }
 
 template <int HD, int MINB, bool LOOP>
 static int launch_decode_mma_as(const AttnArgs& a, cudaStream_t stream) {
-    constexpr int smem = DEC_WARPS * 16 * (HD + 8) * 4 + DEC_WARPS * 16 * 3 * 4;
+    constexpr int smem = DEC_WARPS * 16 * (HD + 8) * 4 + DEC_WARPS * 16 * 3 * 4 + 16 * 4;
     static_assert(DEC_WARPS * DEC_KEYS * HD * 2 <= DEC_WARPS * 16 * (HD + 8) * 4, "values fit the staging area");
     static_assert(DEC_WARPS * DEC_KEYS == 256, "a CTA walks its chunk in blocks of 256 keys");
     static bool configured = false;
@@ -526,7 +532,7 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
     if (fast) {
         a.partial = partial;
         int e = hd == 64 ? launch_decode_mma<64>(a, stream) : launch_decode_mma<128>(a, stream);
-        if (e) return e;
+        if (e || n_chunks == 1) return e;
         // measured: started early, the merge of the chunks costs 5 us more than it saves (its
         // blocks sit on the SMs while the last attention blocks still look for room)
         mf_launch_ex(false, attention_combine_kernel<__nv_bfloat16>, dim3(rows * n_heads), dim3(hd),

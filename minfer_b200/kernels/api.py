@@ -422,7 +422,7 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _i32(row_pos, "row_pos"), _i32(page_table, "page_table"), int(table_stride), int(ring),
         _ptr(out, "out"), _f32(partial, "partial"), rows, n_heads, n_kv, head_dim, int(window),
         int(chunk), int(n_chunks), float(scale), dtype_code(q.dtype), 1 if force_generic else 0,
-        _stream()), "attention_paged", 2 if (n_chunks > 1 or partial is not None) else 1)
+        _stream()), "attention_paged", 2 if n_chunks > 1 else 1)
 
 
 # ---------------------------------------------------------------------------------------
