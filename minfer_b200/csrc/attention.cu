@@ -180,6 +180,26 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial, T* _
     const size_t rh = blockIdx.x;                     // row * n_heads + head
     const size_t stride = (size_t)(hd + 2);
     const float* p = partial + rh * n_chunks * stride;
+    if (n_chunks <= 16) {
+        // few chunks: every thread reads the maxima and sums itself; no barrier at all
+        float m = -INFINITY;
+        for (int c = 0; c < n_chunks; ++c) m = fmaxf(m, p[(size_t)c * stride]);
+        float l = 0.0f;
+        for (int c = 0; c < n_chunks; ++c) {
+            const float mc = p[(size_t)c * stride];
+            if (mc > -INFINITY) l += p[(size_t)c * stride + 1] * expf(mc - m);
+        }
+        const float inv = 1.0f / l;
+        for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+            float o = 0.0f;
+            for (int c = 0; c < n_chunks; ++c) {
+                const float mc = p[(size_t)c * stride];
+                if (mc > -INFINITY) o = fmaf(p[(size_t)c * stride + 2 + d], expf(mc - m), o);
+            }
+            out[rh * hd + d] = from_f32<T>(o * inv);
+        }
+        return;
+    }
     float m_l = -INFINITY;
     for (int c = threadIdx.x; c < n_chunks; c += blockDim.x) {
         const float mc = p[(size_t)c * stride];

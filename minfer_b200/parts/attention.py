@@ -25,7 +25,7 @@ from .base import CacheRequest, CallBinding, Mixer, StepContext, settle_pending
 from .linear import Linear
 
 DECODE_CHUNK = 256     # keys per block when attending over the cache
-DECODE_CTAS = 296      # CTAs the decode kernel wants in flight: two on each of 148 SMs
+DECODE_CTAS = int(os.environ.get("MINFER_B200_DECODE_CTAS", "296"))   # CTAs the decode kernel wants in flight: two on each of 148 SMs
 FORCE_GENERIC_ATTENTION = os.environ.get("MINFER_B200_GENERIC_ATTENTION", "0") == "1"
 # "tcgen05" (tensor memory, the default) or "mma" (the mma.sync twin) for whole prompts in bfloat16
 PROMPT_ATTENTION = os.environ.get("MINFER_B200_PROMPT_ATTENTION", "tcgen05")
