@@ -129,7 +129,10 @@ class CacheGroup:
         self.n_pages = n_pages
         self.pool = PagePool(n_pages)
         self.pages: List[List[int]] = [[] for _ in range(n_slots)]
-        shape = (len(self.entries), n_pages, key.n_kv_heads, PAGE, key.head_dim)
+        # one page more than the pool hands out: the spare page, for rows that only fill a batch
+        # up to a size the engine has a captured graph for
+        self.spare_page = n_pages
+        shape = (len(self.entries), n_pages + 1, key.n_kv_heads, PAGE, key.head_dim)
         # zeros, once: a page's unwritten positions are masked by length but still multiplied
         # by a zero weight in the tensor-core kernels, so they must never hold NaN or Inf
         self.k = torch.zeros(shape, dtype=dtype, device=device)
@@ -161,14 +164,14 @@ class CacheGroup:
     def table_rows(self, slots: Sequence[int], width: int) -> List[List[int]]:
         rows = []
         for s in slots:
-            pg = self.pages[s]
+            pg = [self.spare_page] if s == len(self.pages) else self.pages[s]   # the spare slot
             if len(pg) > width:
                 raise CacheError("the page table is narrower than a sequence's pages")
             rows.append(pg + [-1] * (width - len(pg)))
         return rows
 
     def max_pages_of(self, slots: Sequence[int]) -> int:
-        return max((len(self.pages[s]) for s in slots), default=0)
+        return max((len(self.pages[s]) for s in slots if s < len(self.pages)), default=0)
 
 
 class StatePool:
@@ -207,7 +210,10 @@ class Cache:
         self.dtype = dtype
         self.device = device
         self.slots = SlotTable(max_seqs)
-        self.state = StatePool(max_seqs, device)
+        # one state row more than there are slots: the spare slot (index max_seqs), never handed
+        # out; rows that only pad a batch point at it and at each group's spare page
+        self.spare_slot = max_seqs
+        self.state = StatePool(max_seqs + 1, device)
         by_key: Dict[GroupKey, List[int]] = {}
         for entry in sorted(requests):
             by_key.setdefault(requests[entry], []).append(entry)
@@ -250,7 +256,8 @@ class Cache:
         self.slots.length[slot] = length
 
     def bytes(self) -> int:
-        return sum(2 * g.k.numel() * g.k.element_size() for g in self.groups)
+        """Bytes of key/value storage that sequences can hold (the spare pages not counted)."""
+        return sum(2 * g.k[:, :g.n_pages].numel() * g.k.element_size() for g in self.groups)
 
     def free_pages(self) -> List[int]:
         return [g.pool.n_free() for g in self.groups]

@@ -29,6 +29,15 @@ class StepError(RuntimeError):
     pass
 
 
+def padded_rows(n_rows: int) -> int:
+    """The batch size a decode graph is captured for: the next power of two (a padding row
+    costs little beside the weights, but not nothing: one sequence alone stays alone)."""
+    size = 1
+    while size < n_rows:
+        size *= 2
+    return size
+
+
 class Engine:
     """A model plus its cache.  ``max_tokens`` is the most tokens live sequences hold at any
     time, each sequence's count rounded up to a multiple of 64; it sizes the cache."""
@@ -251,7 +260,16 @@ class Engine:
         page tables' width and the number of key chunks); positions, slots, tokens and page
         tables are data in a buffer the graph reads, as positions are in the reference
         (src/graph/params.rs:10-60: the reuse identity has no n_past)."""
-        n_rows = len(slots)
+        n_live = len(slots)
+        # fill the batch up to a size that has (or gets) a graph: rows that point at the spare
+        # slot, bring token 0 at position 0 and whose logits nobody reads.  Sequences that end
+        # at different steps then keep one graph instead of capturing one for every size.
+        n_rows = padded_rows(n_live)
+        if n_rows > n_live:
+            pad = n_rows - n_live
+            slots = list(slots) + [self.cache.spare_slot] * pad
+            tokens = list(tokens) + [[0]] * pad
+            starts = list(starts) + [0] * pad
         max_end = max(starts) + 1
         # a bound on the lengths: 256, 512, 1024, then multiples of 512 (a new graph every 512
         # positions; a key chunk beyond a sequence's end costs a CTA that leaves at once:
@@ -286,10 +304,10 @@ class Engine:
         event.record()
         self.h2d_bytes += host.numel() * 4
         if device_tokens is not None:
-            entry["dev"][:n_rows].copy_(device_tokens)
+            entry["dev"][:n_live].copy_(device_tokens)
         entry["graph"].replay()
         K.launches += entry["kernels"]
-        return entry["logits"]
+        return entry["logits"][:n_live]
 
     def _capture(self, key, sizes, widths, flat, slots, cap):
         n_rows = key[0]

@@ -19,7 +19,10 @@ def test_groups_have_storage_of_their_own():
     assert len(c.groups) == 3
     g_lin, g_win, g_other = c.group_of[0], c.group_of[1], c.group_of[3]
     assert c.group_of[2] is g_win and g_lin is not g_win and g_other is not g_lin
-    assert g_lin.k.shape == (1, 16, 2, PAGE, 16) and g_win.k.shape[0] == 2
+    # 16 pages the pool hands out plus the spare page that only padding rows of a batch touch
+    assert g_lin.k.shape == (1, 16 + 1, 2, PAGE, 16) and g_win.k.shape[0] == 2
+    assert g_lin.spare_page == 16 and g_lin.pool.n_free() == 16
+    assert g_lin.table_rows([c.spare_slot], 3) == [[16, -1, -1]]
     assert g_win.ring == 128 and g_lin.ring == 0
     assert g_win.n_pages == min(16, 4 * 2)
 

@@ -151,3 +151,39 @@ def test_long_sequence_many_tiles_and_chunks(dtype):
         assert rel_err(out[0], want_long[2100 + t]) < TOL[dtype], t
         assert rel_err(out[1], want_short[7 + t]) < TOL[dtype], t
     eng.check_status()
+
+
+def test_batches_that_shrink_share_graphs_and_padding_changes_nothing():
+    """Decode graphs are captured for batch sizes that are powers of two; a batch of 5, then 3
+    (two sequences ended) is filled up with rows on the spare slot.  The live rows' logits are
+    those of the same sequences decoded alone, and only the padded sizes get graphs."""
+    folder = make_folder("D")
+    cfg, w = P.load_folder(folder)
+    eng = _engine(folder, "float32")
+    prompts = [random_ids(n, cfg["vocab_size"], 300 + n) for n in (9, 4, 17, 1, 30)]
+    nxt = [random_ids(12, cfg["vocab_size"], 400 + i) for i in range(5)]
+    alone = []
+    for p, t in zip(prompts, nxt):
+        s = eng.acquire()
+        eng.step([s], [p])
+        alone.append(torch.cat([eng.step([s], [[tok]]) for tok in t]))
+        eng.release(s)
+    graphs_before = set(eng._graphs)
+    slots = [eng.acquire() for _ in prompts]
+    eng.step(slots, prompts)
+    got = [[] for _ in prompts]
+    live = list(range(5))
+    for step in range(12):
+        if step == 6:
+            live = [0, 2, 4]                          # two sequences end here
+        out = eng.step([slots[b] for b in live], [[nxt[b][step]] for b in live])
+        for i, b in enumerate(live):
+            got[b].append(out[i:i + 1])
+    for b in range(5):
+        have = torch.cat(got[b])
+        assert torch.equal(have, alone[b][:have.shape[0]]), b      # float32: the same bits
+    sizes = {k[0] for k in set(eng._graphs) - graphs_before}
+    assert sizes <= {4, 8}, sizes
+    for s in slots:
+        eng.release(s)
+    eng.check_status()
