@@ -49,10 +49,23 @@ def peaks():
             with open(path) as f:
                 d = json.load(f)
             out = dict(FALLBACK_PEAKS)
-            for k in out:
-                if isinstance(d.get(k), (int, float)):
-                    out[k] = float(d[k])
-            return out, "measured"
+            found = 0
+
+            def look(node):                       # the keys may sit at the top or one level down
+                nonlocal found
+                if isinstance(node, dict):
+                    for k, v in node.items():
+                        if k in out and isinstance(v, (int, float)) and not isinstance(v, bool) and v > 0:
+                            out[k] = float(v)
+                            found += 1
+                        elif k in out and isinstance(v, dict) and isinstance(v.get("value"), (int, float)):
+                            out[k] = float(v["value"])
+                            found += 1
+                        else:
+                            look(v)
+            look(d)
+            if found:
+                return out, "measured"
         except (OSError, ValueError):
             pass
     return dict(FALLBACK_PEAKS), "fallback"
