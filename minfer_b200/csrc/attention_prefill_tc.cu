@@ -3,18 +3,27 @@
 // another.  Same formula as the other attention kernels (src/graph/cpu_backend.rs:437-494 in
 // the reference): scores * scale, mask by position, softmax in float32, weighted sum of values.
 //
-// A CTA owns 128 queries of one head and walks the keys in tiles of 128:
+// A CTA owns 256 queries of one head as two tiles of 128 and walks the keys in tiles of 128;
+// both query tiles use every key tile, so keys and values cross L2 -> shared memory once for
+// 256 queries (one query tile per CTA was bound by that traffic):
 //   S = Q K^T     tcgen05.mma, both operands in shared memory (TMA, 128-byte swizzle), S in
-//                 tensor memory; two S buffers, so the product for the next key tile runs
-//                 while the softmax of this one is still at work
-//   softmax       four warps, one thread per query row: the row of S comes out of tensor
-//                 memory, maximum / exp2 / sum in float32, and the probabilities go back into
-//                 the same columns as packed bfloat16
+//                 tensor memory, one S buffer for each query tile
+//   softmax       one warpgroup for each query tile, one thread per query row: the row of S
+//                 comes out of tensor memory into registers once, maximum / exp2 / sum in
+//                 float32, and the probabilities go back into the same columns as packed
+//                 bfloat16.  The two warpgroups take their registers from the first one
+//                 (setmaxnreg), which only issues copies and MMAs
 //   O += P V      tcgen05.mma with P read from tensor memory as the A operand and V from
-//                 shared memory as an MN-major B operand; O stays in tensor memory and is
-//                 rescaled there by the softmax threads only when a row's maximum has grown
-//   warp 0: TMA producer (Q once, K and V double-buffered); warp 1: MMA issuer; warps 2-5:
-//   softmax and the final O / sum.
+//                 shared memory as an MN-major B operand; O stays in tensor memory (one for
+//                 each query tile) and is rescaled there by the softmax threads only when a
+//                 row's maximum has grown
+//   The MMA thread alternates between the query tiles: O += P V of a key tile as soon as
+//   its probabilities are there, then at once S of the next key tile into the same columns;
+//   while one query tile is in its softmax the tensor cores work for the other.
+//   Tensor memory: S0 S1 O0 O1 = 512 columns.  Shared memory: Q 2 tiles, K and V rings of 2.
+//   warp 0: TMA producer; warp 1: MMA issuer; warps 4-7 and 8-11: softmax and the final
+//   O / sum of query tile 0 and 1.  The second tile may lie beyond the sequence (or see other
+//   key tiles than the first: causal edge, window): each tile has its own range of key tiles.
 // Rows of the packed tensors that lie beyond a sequence's end belong to the next sequence;
 // they are masked by position, never used.  Every mbarrier wait is bounded.
 #include <cuda.h>
