@@ -232,8 +232,11 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial, T* _
 // Decoding over the paged cache on tensor cores (bfloat16, head size 64 or 128, up to 16
 // query heads per key/value head).
 //
-// One CTA owns (key chunk of 256 positions, key/value head, query row); its four warps each
-// take one page of 64 keys.  The group's query heads are the 16 rows of an m16n8k16 MMA, so
+// One CTA owns (key chunk, key/value head, query row).  A chunk is a multiple of 256 positions
+// and is walked in blocks of 256; each of the eight warps takes 32 keys of a block and carries
+// its running maximum, sum and output from block to block.  The caller sizes the chunks (one
+// block when there are many rows, several when the context is long and the rows are few).
+// The group's query heads are the 16 rows of an m16n8k16 MMA, so
 // a key or value element is read once for the whole group (the reference's kernel re-reads
 // the cache for every query head: src/cuda_kernels.cu:673-790).  Keys go from global memory
 // straight into MMA fragments (16-byte loads; k is permuted the same way in both operands,
@@ -241,7 +244,8 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial, T* _
 // XOR swizzle and read transposed by ldmatrix.  Scores, maxima and sums are float32; the
 // probabilities are rounded to bfloat16 for the second product.  The warps' results are
 // merged in shared memory in warp order and written as one partial per chunk, which
-// attention_combine_kernel merges in chunk order.
+// attention_combine_kernel merges in chunk order; a row with a single chunk is written out
+// directly.
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void mma_bf16_16816(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
     asm volatile(
