@@ -85,7 +85,12 @@ class Engine:
             for req in model.blocks[call.layer].mixer.state_request():
                 tensors[req.name] = self.cache.state.add(f"call{i}.{req.name}", req.shape, req.dtype)
             self._call_state.append(tensors)
-        from ..kernels import gemm
+        from ..kernels import build, gemm
+        # what this model's steps will load, compiled side by side if it is not built yet
+        if self.dtype == torch.bfloat16:
+            build.prebuild(["ops", "gemm_tc", "attention", "attention_prefill_tc"])
+        else:
+            build.prebuild(["ops", "gemm_simt", "attention"])
         self.status = gemm.status_word(self.device)       # one word for every kernel's error bits
         self._graphs: Dict[tuple, dict] = {}
         self._seen_shapes: set = set()

@@ -143,6 +143,18 @@ def load_library(name: str) -> ctypes.CDLL:
         return lib
 
 
+def prebuild(names, verbose: bool = True) -> list[str]:
+    """Compiles those of the named libraries that are not built yet, side by side (nvcc runs
+    as a process of its own, a few seconds each); returns their paths."""
+    names = [n for n in dict.fromkeys(names)]
+    missing = [n for n in names if not os.path.exists(library_path(n))]
+    if len(missing) > 1:
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(max_workers=min(len(missing), max(1, os.cpu_count() or 1))) as pool:
+            list(pool.map(lambda n: compile_library(n, verbose), missing))
+    return [compile_library(n, verbose) for n in names]
+
+
 def build_all(verbose: bool = True) -> list[str]:
     """Compiles every library (cross-compiles without a GPU)."""
-    return [compile_library(name, verbose) for name in LIBRARIES]
+    return prebuild(list(LIBRARIES), verbose)
