@@ -14,6 +14,7 @@ from __future__ import annotations
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -121,9 +122,10 @@ def compile_library(name: str, verbose: bool = True) -> str:
         raise KernelBuildError(f"nvcc failed for {source}:\n{' '.join(cmd)}\n{log}")
     os.replace(tmp, out)
     # older builds of the same library (other source hashes) are of no use any more
-    prefix = f"libmf_{name}_"
+    # (the whole name is matched: "attention" must not take "attention_prefill_tc" for its own)
+    own = re.compile(rf"libmf_{re.escape(name)}_[0-9a-f]{{16}}\.so")
     for other in os.listdir(os.path.dirname(out)):
-        if other.startswith(prefix) and other.endswith(".so") and other != os.path.basename(out):
+        if own.fullmatch(other) and other != os.path.basename(out):
             try:
                 os.remove(os.path.join(os.path.dirname(out), other))
             except OSError:
