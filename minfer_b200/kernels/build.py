@@ -57,8 +57,20 @@ def _nvcc() -> str:
         "the CUDA kernels cannot be built and there is no other path")
 
 
+_build_dir_lock = threading.Lock()
+_build_dir_found: list = []
+
+
 def _build_dir() -> str:
-    """In-tree ``minfer_b200/_lib`` when writable, else a per-user folder under the temp dir."""
+    """In-tree ``minfer_b200/_lib`` when writable, else a per-user folder under the temp dir.
+    Decided once per process (threads that compile side by side must agree on it)."""
+    with _build_dir_lock:
+        if not _build_dir_found:
+            _build_dir_found.append(_find_build_dir())
+        return _build_dir_found[0]
+
+
+def _find_build_dir() -> str:
     env = os.environ.get("MINFER_B200_BUILD_DIR")
     candidates = [env] if env else []
     candidates.append(os.path.join(os.path.dirname(CSRC), "_lib"))
