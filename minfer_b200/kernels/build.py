@@ -104,6 +104,20 @@ def library_path(name: str) -> str:
     return os.path.join(_build_dir(), f"libmf_{name}_{_source_hash(source, flags)}.so")
 
 
+def remove_old_versions(name: str, keep: str) -> None:
+    """Older builds of library ``name`` (other source hashes) beside ``keep`` are of no use any
+    more.  The whole file name is matched: "attention" must not take "attention_prefill_tc"
+    for its own."""
+    own = re.compile(rf"libmf_{re.escape(name)}_[0-9a-f]{{16}}\.so")
+    folder = os.path.dirname(keep)
+    for other in os.listdir(folder):
+        if own.fullmatch(other) and other != os.path.basename(keep):
+            try:
+                os.remove(os.path.join(folder, other))
+            except OSError:
+                pass
+
+
 def compile_library(name: str, verbose: bool = True) -> str:
     """Builds the library if its file is not there yet; returns the path."""
     source, flags = LIBRARIES[name]
@@ -133,15 +147,7 @@ def compile_library(name: str, verbose: bool = True) -> str:
             pass
         raise KernelBuildError(f"nvcc failed for {source}:\n{' '.join(cmd)}\n{log}")
     os.replace(tmp, out)
-    # older builds of the same library (other source hashes) are of no use any more
-    # (the whole name is matched: "attention" must not take "attention_prefill_tc" for its own)
-    own = re.compile(rf"libmf_{re.escape(name)}_[0-9a-f]{{16}}\.so")
-    for other in os.listdir(os.path.dirname(out)):
-        if own.fullmatch(other) and other != os.path.basename(out):
-            try:
-                os.remove(os.path.join(os.path.dirname(out), other))
-            except OSError:
-                pass
+    remove_old_versions(name, out)
     if verbose:
         print(f"[minfer_b200] built {os.path.basename(out)} in {time.time() - t0:.1f} s",
               file=sys.stderr, flush=True)

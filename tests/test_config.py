@@ -104,3 +104,15 @@ def test_schedule_is_checked():
         with_schedule([LayerCall(0, 1, writes_cache=False), LayerCall(1, 1)]).validate()
     with pytest.raises(ConfigError, match="no call writes"):
         with_schedule([LayerCall(0, 0), LayerCall(1, 3, writes_cache=False)]).validate()
+
+
+def test_builder_removes_only_a_librarys_own_old_versions(tmp_path):
+    from minfer_b200.kernels.build import remove_old_versions
+    names = ["libmf_attention_0123456789abcdef.so", "libmf_attention_fedcba9876543210.so",
+             "libmf_attention_prefill_tc_0123456789abcdef.so", "libmf_attention_prefill_0123456789abcdef.so",
+             "libmf_attention_0123456789abcdef.so.123.tmp", "notes.txt"]
+    for n in names:
+        (tmp_path / n).write_bytes(b"")
+    remove_old_versions("attention", str(tmp_path / names[0]))
+    left = sorted(p.name for p in tmp_path.iterdir())
+    assert left == sorted(n for n in names if n != "libmf_attention_fedcba9876543210.so")
