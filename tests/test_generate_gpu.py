@@ -134,3 +134,31 @@ def test_model_conveniences(tiny):
     out = model.generate([ids], 5, SamplingParams.greedy(), stop_token_ids=[], max_batch=1,
                          max_positions=128)
     assert out[0].tokens == P.generate(tiny["cfg"], tiny["w"], ids, 5)
+
+
+def test_sampling_kernel_at_a_large_vocabulary():
+    """The same comparison at a vocabulary of 50,021 (no multiple of anything): the short-list
+    path of top-k (k = 40 and k = 1000), top-k beyond the list's reach (k = 3000: radix selection
+    over the row, then top-p over more than 1,024 survivors), plain temperature, and logits
+    whose scale puts thousands of values into one binary order of magnitude."""
+    from minfer_b200.kernels import api as K
+    V, rows = 50021, 3
+    g = torch.Generator().manual_seed(11)
+    logits = torch.randn(rows, V, generator=g)
+    logits[0] *= 0.3                                               # the top 40 share one exponent
+    logits[1] *= 4.0
+    logits[2, 123] = 9.0                                           # one token far ahead
+    cases = [dict(temp=0.8, top_k=40, top_p=0.95), dict(temp=1.0, top_k=1000, top_p=0.9),
+             dict(temp=1.2, top_k=3000, top_p=0.8), dict(temp=0.9, top_k=0, top_p=1.0),
+             dict(temp=0.0, top_k=0, top_p=1.0)]
+    for case in cases:
+        dev = logits.clone().cuda()
+        out = torch.empty(rows, dtype=torch.int32, device="cuda")
+        K.sample(dev, out, temperature=case["temp"], top_k=case["top_k"], top_p=case["top_p"],
+                 repeat_penalty=1.0, frequency_penalty=0.0, presence_penalty=0.0, seed=5)
+        got = out.cpu().tolist()
+        for r in range(rows):
+            u = P.philox_uniform(5, 0, r)
+            want = P.sample(logits[r].double(), case["temp"], case["top_k"], case["top_p"],
+                            1.0, 0.0, 0.0, [], u)
+            assert got[r] == want, (case, r)
