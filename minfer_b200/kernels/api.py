@@ -54,7 +54,13 @@ def _ptr(t: Optional[torch.Tensor], what: str = "tensor") -> Optional[int]:
     return t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle (called once per launch: the short way where torch has it)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
@@ -286,11 +292,26 @@ def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
             and w.data_ptr() % 16 == 0)
 
 
+_PLANS: dict = {}
+
+
 def gemm_tc_plan(m: int, n: int, k: int, epi: int = EPI_STORE) -> tuple[int, int]:
-    """(token tile, K splits) the kernel uses for these sizes."""
-    nt, sp = ctypes.c_int(0), ctypes.c_int(0)
-    _lib("gemm_tc").mf_gemm_tc_plan(m, n, k, epi, ctypes.addressof(nt), ctypes.addressof(sp))
-    return nt.value, sp.value
+    """(token tile, K splits) the kernel uses for these sizes (a function of the sizes only:
+    asked once per shape)."""
+    return _gemm_tc_shape(m, n, k, epi)[:2]
+
+
+def _gemm_tc_shape(m: int, n: int, k: int, epi: int) -> tuple[int, int, int]:
+    """(token tile, K splits, workspace floats) of a product of these sizes."""
+    key = (m, n, k, epi)
+    got = _PLANS.get(key)
+    if got is None:
+        lib = _lib("gemm_tc")
+        nt, sp = ctypes.c_int(0), ctypes.c_int(0)
+        lib.mf_gemm_tc_plan(m, n, k, epi, ctypes.addressof(nt), ctypes.addressof(sp))
+        got = (nt.value, sp.value, int(lib.mf_gemm_tc_workspace_floats(m, n, k, epi)))
+        _PLANS[key] = got
+    return got
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
@@ -309,7 +330,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
     if bias is not None and bias.numel() != n:
         raise KernelError("gemm: bias has the wrong length")
     lib = _lib("gemm_tc")
-    need = int(lib.mf_gemm_tc_workspace_floats(m, n, k, epi))
+    need = _gemm_tc_shape(m, n, k, epi)[2]
     ws = torch.empty(need, dtype=torch.float32, device=x.device) if need else None
     _check(lib.mf_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _f32(bias, "bias"),
                           out.data_ptr(), out.stride(0), dtype_code(out.dtype), m, n, k, epi,
@@ -326,10 +347,10 @@ def gemm_tc_partial_sums(x: torch.Tensor, w: torch.Tensor,
     n = w.shape[0]
     if not gemm_tc_supported(x, w) or w.shape[1] != k:
         return None
-    lib = _lib("gemm_tc")
-    need = int(lib.mf_gemm_tc_workspace_floats(m, n, k, EPI_STORE))
+    need = _gemm_tc_shape(m, n, k, EPI_STORE)[2]
     if need == 0:
         return None
+    lib = _lib("gemm_tc")
     ws = torch.empty(need, dtype=torch.float32, device=x.device)
     splits = ctypes.c_int(0)
     _check(lib.mf_gemm_tc(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), None,

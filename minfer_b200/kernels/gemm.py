@@ -20,8 +20,11 @@ def status_word(device: torch.device) -> torch.Tensor:
     return _status[key]
 
 
+_USE_TENSOR_CORES = os.environ.get("MINFER_B200_NO_TCGEN05", "0") != "1"     # read once
+
+
 def use_tensor_cores() -> bool:
-    return os.environ.get("MINFER_B200_NO_TCGEN05", "0") != "1"
+    return _USE_TENSOR_CORES
 
 
 def gemm_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
