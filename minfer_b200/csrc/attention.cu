@@ -16,7 +16,14 @@
 // pair instead of a full per-lane accumulator, and with key chunks whose boundaries are
 // multiples of `chunk` in absolute position, so that a sequence's result does not depend
 // on what else is in the batch.  Chunks are merged by mf_attention_combine.
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
+
+#define MF_ERR_NO_TENSORMAP 2003
+#define MF_ERR_TENSORMAP 2004
 
 #define ATT_WARPS 4
 #define ATT_MAX_HD 256
@@ -58,6 +65,7 @@ struct AttnArgs {
     int window;               // 0 = all earlier keys
     int chunk, n_chunks;
     float scale;
+    unsigned* status;         // device status word (the kernel with bounded waits only)
 };
 
 template <typename T, bool PAGED>
@@ -493,6 +501,394 @@ static int launch_decode_mma_as(const AttnArgs& a, cudaStream_t stream) {
     return MF_LAUNCH_CHECK();
 }
 
+// ------------------------------------------------------------------------------------------
+// The same decoding attention for chunks of several pages: the keys and values of a chunk come
+// through a ring in shared memory that a producer warp keeps filled by TMA, a page (64
+// positions of one key/value head: one stage) at a time, so that the next pages are in flight
+// while the four consumer warps work on this one.  (In the kernel above a warp asks for its
+// next keys only when it is done with these: with long chunks the loads in flight do not cover
+// the memory latency.)
+//
+//   warp 4       producer: looks up the chunk's pages (32 table entries a time, one per lane),
+//                waits for a stage to be free and issues the copies of its K and V tiles
+//                (tensor maps over the layer's cache [pages * kv_heads * 64][HD], boxes of
+//                64 x 64 elements with the 128-byte swizzle)
+//   warps 0-3    consumers: warp w owns keys 16w..16w+15 of every page.  Scores on mma.sync
+//                with the keys read by ldmatrix, running maximum and sum in float32,
+//                probabilities rounded to bfloat16, values read transposed by ldmatrix.  A warp
+//                frees a stage with one arrival; it never waits for the other warps.
+// At the chunk's end the four warps' results are merged in warp order in shared memory (over
+// the ring, which is idle by then) exactly like the eight warps above.  Waits are bounded.
+// ------------------------------------------------------------------------------------------
+#define RING_CONSUMERS 4
+#define RING_THREADS ((RING_CONSUMERS + 1) * 32)
+#define RING_MAX_SPIN (1u << 24)
+#define RING_MAX_WAIT_NS 2000000000ull
+
+__device__ __forceinline__ uint32_t ring_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool ring_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// false: the wait ran out (or another thread's did); the flag tells everyone to stop
+__device__ __forceinline__ bool ring_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    unsigned long long t0 = 0;
+    for (uint32_t it = 0; it < RING_MAX_SPIN; ++it) {
+        if (ring_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if ((it & 1023u) == 1023u) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > RING_MAX_WAIT_NS) break;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void ring_tma(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+template <int HD, int STAGES, int MINB>
+__global__ void __launch_bounds__(RING_THREADS, MINB)
+attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k,
+                             const __grid_constant__ CUtensorMap map_v, AttnArgs a) {
+    pdl_prologue();
+    constexpr int HALF_BYTES = MF_PAGE * 128;          // one box: 64 keys x 64 elements
+    constexpr int KV_BYTES = (HD / 64) * HALF_BYTES;   // the keys (or the values) of a page
+    constexpr int STAGE_BYTES = 2 * KV_BYTES;
+    constexpr int OS = HD + 8;
+    extern __shared__ uint8_t ring_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)ring_raw + 1023) & ~(uintptr_t)1023);
+    float* o_s = (float*)smem;                                           // over the ring, at the end
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);           // full[S], empty[S]
+    float* ml_s = (float*)(bars + 2 * STAGES);                           // [consumers][16][2]
+    float* f_s = ml_s + RING_CONSUMERS * 16 * 2;                         // [consumers][16]
+    float* l_s = f_s + RING_CONSUMERS * 16;                              // [16]
+    volatile int* abort_flag = (volatile int*)(l_s + 16);
+
+    const int chunk_id = blockIdx.x, hk = blockIdx.y, row = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int G = a.n_heads / a.n_kv;
+    const int b = a.row_seq[row];
+    const int pos = a.row_pos[row];
+    const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    const int hi = pos + 1;
+    const int chunk_lo = chunk_id * a.chunk;
+    const int k_lo = max(lo, chunk_lo), k_hi = min(hi, chunk_lo + a.chunk);
+    const size_t part_stride = (size_t)(HD + 2);
+    float* part0 = a.partial + (((size_t)row * a.n_heads + (size_t)hk * G) * a.n_chunks + chunk_id) * part_stride;
+    if (k_lo >= k_hi) {                               // nothing of this chunk is visible
+        if (tid < G) {
+            float* p = part0 + (size_t)tid * a.n_chunks * part_stride;
+            p[0] = -INFINITY;
+            p[1] = 0.0f;
+        }
+        return;
+    }
+    const int first = k_lo & ~(MF_PAGE - 1);          // position of the first page to visit
+    const int n_tiles = (k_hi - first + MF_PAGE - 1) / MF_PAGE;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(ring_smem(&bars[s])), "r"(1));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;"
+                         ::"r"(ring_smem(&bars[STAGES + s])), "r"(RING_CONSUMERS));
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == RING_CONSUMERS) {
+        // ---- producer ---------------------------------------------------------------------
+        bool ok = true;
+        for (int base = 0; base < n_tiles; base += 32) {
+            int page = 0;
+            if (base + lane < n_tiles) {
+                const int p = first + (base + lane) * MF_PAGE;
+                const int p_eff = a.ring > 0 ? p % a.ring : p;
+                page = a.page_table[(size_t)b * a.table_stride + (p_eff >> 6)];
+            }
+            const int cnt = min(32, n_tiles - base);
+            for (int i = 0; i < cnt; ++i) {
+                const int pg = __shfl_sync(0xffffffffu, page, i);
+                if (lane == 0 && ok) {
+                    const int n = base + i, s = n % STAGES;
+                    const uint32_t ph = (uint32_t)(n / STAGES) & 1u;
+                    ok = ring_wait(ring_smem(&bars[STAGES + s]), ph ^ 1u, abort_flag);
+                    if (ok) {
+                        const uint32_t full = ring_smem(&bars[s]);
+                        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
+                                     ::"r"(full), "r"((uint32_t)STAGE_BYTES) : "memory");
+                        const uint32_t dst = ring_smem(smem + (size_t)s * STAGE_BYTES);
+                        const int y = (pg * a.n_kv + hk) * MF_PAGE;
+#pragma unroll
+                        for (int h = 0; h < HD / 64; ++h) {
+                            ring_tma(dst + h * HALF_BYTES, &map_k, h * 64, y, full);
+                            ring_tma(dst + KV_BYTES + h * HALF_BYTES, &map_v, h * 64, y, full);
+                        }
+                    }
+                }
+            }
+        }
+        if (lane == 0 && !ok && a.status) atomicOr(a.status, MF_STATUS_WAIT_TIMEOUT);
+        return;
+    }
+
+    // ---- consumers ----------------------------------------------------------------------------
+    // query fragments: rows g and g+8 of the group (zero beyond the group's heads)
+    uint32_t qa[HD / 16][4];
+    {
+        const __nv_bfloat16* qrow = (const __nv_bfloat16*)a.q + ((size_t)row * a.n_heads + (size_t)hk * G) * HD;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            const __nv_bfloat16* q0 = qrow + (size_t)g * HD + 16 * kk + 2 * t;
+            const __nv_bfloat16* q1 = qrow + (size_t)(g + 8) * HD + 16 * kk + 2 * t;
+            qa[kk][0] = g < G ? *reinterpret_cast<const uint32_t*>(q0) : 0u;
+            qa[kk][1] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(q1) : 0u;
+            qa[kk][2] = g < G ? *reinterpret_cast<const uint32_t*>(q0 + 8) : 0u;
+            qa[kk][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(q1 + 8) : 0u;
+        }
+    }
+    float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.0f, 0.0f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
+    const float sl2 = a.scale * 1.4426950408889634f;
+    const uint32_t ring_base = ring_smem(smem);
+    bool ok = true;
+
+    for (int n = 0; n < n_tiles; ++n) {
+        const int s = n % STAGES;
+        const uint32_t ph = (uint32_t)(n / STAGES) & 1u;
+        ok = __all_sync(0xffffffffu, ring_wait(ring_smem(&bars[s]), ph, abort_flag));
+        if (!ok) break;
+        const int j0 = first + n * MF_PAGE + warp * 16;            // first position of this warp's keys
+        const int w_lo = max(k_lo, j0), w_hi = min(k_hi, j0 + 16);
+        if (w_lo < w_hi) {
+            const uint32_t kaddr = ring_base + (uint32_t)(s * STAGE_BYTES);
+            const uint32_t vaddr = kaddr + KV_BYTES;
+            // scores S[16 heads][16 keys]
+            // (two accumulators per key tile, for even and odd steps along the head: half as
+            // long a chain of dependent MMAs; added below)
+            float sacc[2][4], sodd[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.0f;
+                sodd[nt][0] = sodd[nt][1] = sodd[nt][2] = sodd[nt][3] = 0.0f;
+            }
+#pragma unroll
+            for (int ks2 = 0; ks2 < HD / 32; ++ks2) {
+                const int c = 4 * ks2 + (lane >> 3);              // 16-byte piece of a key's row
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    const int r = warp * 16 + nt * 8 + (lane & 7);
+                    const uint32_t addr = kaddr + (uint32_t)((c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+                    uint32_t r0, r1, r2, r3;
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+                    mma_bf16_16816(sacc[nt], qa[2 * ks2], r0, r1);
+                    mma_bf16_16816(sodd[nt], qa[2 * ks2 + 1], r2, r3);
+                }
+            }
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sacc[nt][e] += sodd[nt][e];
+            }
+            // scale (to base 2), mask by position, row maxima on top of the pages before
+            const float m_old[2] = {m_r[0], m_r[1]};
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = j0 + nt * 8 + 2 * t + (e & 1);
+                    const float sv = (key >= w_lo && key < w_hi) ? sacc[nt][e] * sl2 : -INFINITY;
+                    sacc[nt][e] = sv;
+                    m_r[e >> 1] = fmaxf(m_r[e >> 1], sv);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                m_r[r] = fmaxf(m_r[r], __shfl_xor_sync(0xffffffffu, m_r[r], 1));
+                m_r[r] = fmaxf(m_r[r], __shfl_xor_sync(0xffffffffu, m_r[r], 2));
+            }
+            if (__any_sync(0xffffffffu, m_r[0] != m_old[0] || m_r[1] != m_old[1])) {
+                // what the warp holds from earlier pages comes down to the new maxima
+                const float c0 = m_old[0] > -INFINITY ? exp2f(m_old[0] - m_r[0]) : 0.0f;
+                const float c1 = m_old[1] > -INFINITY ? exp2f(m_old[1] - m_r[1]) : 0.0f;
+                l_r[0] *= c0; l_r[1] *= c1;
+#pragma unroll
+                for (int i = 0; i < HD / 8; ++i) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
+            }
+            uint32_t pa[4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                float p[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    p[e] = exp2f(sacc[nt][e] - m_r[e >> 1]);
+                    l_r[e >> 1] += p[e];
+                }
+                pa[nt * 2 + 0] = pack_bf16(p[0], p[1]);
+                pa[nt * 2 + 1] = pack_bf16(p[2], p[3]);
+            }
+            // O[16 heads][HD] += P[16][16] V[16][HD]
+            const int key = warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+            for (int np = 0; np < HD / 16; ++np) {
+                const int dchunk = 2 * np + (lane >> 4);
+                const uint32_t addr = vaddr + (uint32_t)((dchunk >> 3) * HALF_BYTES + key * 128 + (((dchunk & 7) ^ (key & 7)) << 4));
+                uint32_t r0, r1, r2, r3;
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+                mma_bf16_16816(o[2 * np], pa, r0, r1);
+                mma_bf16_16816(o[2 * np + 1], pa, r2, r3);
+            }
+        }
+        __syncwarp();
+        if (lane == 0)
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(ring_smem(&bars[STAGES + s])) : "memory");
+    }
+    if (!ok && lane == 0 && a.status) atomicOr(a.status, MF_STATUS_WAIT_TIMEOUT);
+
+    // the four lanes of a row each hold a part of its sum
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 1);
+        l_r[r] += __shfl_xor_sync(0xffffffffu, l_r[r], 2);
+    }
+    if (t == 0) {
+        ml_s[(warp * 16 + g) * 2 + 0] = m_r[0]; ml_s[(warp * 16 + g) * 2 + 1] = l_r[0];
+        ml_s[(warp * 16 + g + 8) * 2 + 0] = m_r[1]; ml_s[(warp * 16 + g + 8) * 2 + 1] = l_r[1];
+    }
+    // consumers only (the producer has left): every warp is done with the ring
+    asm volatile("bar.sync 1, %0;" ::"n"(RING_CONSUMERS * 32) : "memory");
+    if (tid < 16) {
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < RING_CONSUMERS; ++w) m = fmaxf(m, ml_s[(w * 16 + tid) * 2]);
+        float l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < RING_CONSUMERS; ++w) {
+            const float mw = ml_s[(w * 16 + tid) * 2];
+            const float f = mw > -INFINITY ? exp2f(mw - m) : 0.0f;
+            f_s[w * 16 + tid] = f;
+            l += ml_s[(w * 16 + tid) * 2 + 1] * f;
+        }
+        l_s[tid] = l;
+        if (tid < G && a.n_chunks > 1) {
+            float* p = part0 + (size_t)tid * a.n_chunks * part_stride;
+            p[0] = m * 0.6931471805599453f;           // back to natural-log units for the merge
+            p[1] = l;
+        }
+    }
+    float* ow = o_s + (size_t)warp * 16 * OS;
+#pragma unroll
+    for (int nt = 0; nt < HD / 8; ++nt) {
+        *reinterpret_cast<float2*>(ow + (size_t)g * OS + nt * 8 + 2 * t) = make_float2(o[nt][0], o[nt][1]);
+        if (G > 8)
+            *reinterpret_cast<float2*>(ow + (size_t)(g + 8) * OS + nt * 8 + 2 * t) = make_float2(o[nt][2], o[nt][3]);
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(RING_CONSUMERS * 32) : "memory");
+    for (int idx = tid; idx < G * HD; idx += RING_CONSUMERS * 32) {
+        const int r = idx / HD, d = idx - r * HD;
+        float acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < RING_CONSUMERS; ++w) acc = fmaf(o_s[((size_t)w * 16 + r) * OS + d], f_s[w * 16 + r], acc);
+        if (a.n_chunks > 1)
+            part0[(size_t)r * a.n_chunks * part_stride + 2 + d] = acc;
+        else
+            ((__nv_bfloat16*)a.out)[((size_t)row * a.n_heads + (size_t)hk * G + r) * HD + d] =
+                __float2bfloat16(acc / l_s[r]);
+    }
+}
+
+// ---- tensor maps over a layer's cache ----------------------------------------------------------
+typedef CUresult (*RingEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                 const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static RingEncodeFn ring_encode_fn() {
+    static RingEncodeFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (RingEncodeFn)p;
+    });
+    return fn;
+}
+
+struct CacheMapKey {
+    const void* ptr; long long rows; int hd;
+    bool operator==(const CacheMapKey& o) const { return ptr == o.ptr && rows == o.rows && hd == o.hd; }
+};
+struct CacheMapKeyHash {
+    size_t operator()(const CacheMapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ (size_t)k.rows * 1315423911u ^ (size_t)k.hd * 97u;
+    }
+};
+
+// bfloat16 cache of a layer seen as [rows][hd]; a cache does not move, so its map is made once
+static int cache_map(CUtensorMap* out, const void* ptr, long long rows, int hd) {
+    static std::unordered_map<CacheMapKey, CUtensorMap, CacheMapKeyHash> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    const CacheMapKey key{ptr, rows, hd};
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+        RingEncodeFn fn = ring_encode_fn();
+        if (!fn) return MF_ERR_NO_TENSORMAP;
+        if (((uintptr_t)ptr & 15) != 0 || rows <= 0 || rows > 0x7fffffffLL) return MF_ERR_UNSUPPORTED;
+        CUtensorMap m;
+        cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+        cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+        cuuint32_t box[2] = {64, MF_PAGE};
+        cuuint32_t estr[2] = {1, 1};
+        CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return MF_ERR_TENSORMAP;
+        it = cache.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+
+template <int HD, int STAGES, int MINB>
+static int launch_decode_ring(const AttnArgs& a, long long cache_rows, cudaStream_t stream) {
+    constexpr int smem = 1024 + STAGES * 2 * (HD / 64) * MF_PAGE * 128 + 2 * STAGES * 8 +
+                         RING_CONSUMERS * 16 * 3 * 4 + 16 * 4 + 16;
+    static_assert(RING_CONSUMERS * 16 * (HD + 8) * 4 <= STAGES * 2 * (HD / 64) * MF_PAGE * 128,
+                  "the warps' results fit over the ring");
+    CUtensorMap mk, mv;
+    if (int e = cache_map(&mk, a.k, cache_rows, HD)) return e;
+    if (int e = cache_map(&mv, a.v, cache_rows, HD)) return e;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_ring_kernel<HD, STAGES, MINB>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(a.n_chunks, a.n_kv, a.rows);
+    mf_launch(attention_decode_ring_kernel<HD, STAGES, MINB>, dim3(grid), dim3(RING_THREADS), smem, stream,
+              mk, mv, a);
+    return MF_LAUNCH_CHECK();
+}
+
 template <int HD>
 static int launch_decode_mma(const AttnArgs& a, cudaStream_t stream) {
     // chunks of several blocks carry more state in registers: two CTAs per SM
@@ -532,12 +928,14 @@ extern "C" int mf_attention_packed(const void* q, const void* k, const void* v, 
 }
 
 // Attention over the paged cache.  `partial` must hold rows*n_heads*n_chunks*(hd+2) floats
-// when n_chunks > 1; chunk c covers absolute positions [c*chunk, (c+1)*chunk).
+// when n_chunks > 1; chunk c covers absolute positions [c*chunk, (c+1)*chunk).  `cache_pages`
+// (pages the cache tensors hold; 0 = unknown) and `status` (may be null) open the TMA-ring kernel.
 extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void* v_cache,
                                   const int* row_seq, const int* row_pos, const int* page_table,
                                   int table_stride, int ring, void* out, float* partial, int rows,
                                   int n_heads, int n_kv, int hd, int window, int chunk, int n_chunks,
-                                  float scale, int dtype, int force_generic, cudaStream_t stream) {
+                                  float scale, int dtype, int force_generic, long long cache_pages,
+                                  unsigned* status, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (int e = check_sizes(n_heads, n_kv, hd)) return e;
     if (n_chunks < 1 || (n_chunks > 1 && (partial == nullptr || chunk <= 0))) return MF_ERR_ARGUMENT;
@@ -555,7 +953,21 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
                       !force_generic;
     if (fast) {
         a.partial = partial;
-        int e = hd == 64 ? launch_decode_mma<64>(a, stream) : launch_decode_mma<128>(a, stream);
+        a.status = status;
+        // the TMA ring needs the cache's extent for its tensor maps and a status word for its
+        // bounded waits; without them, or with MINFER_B200_DECODE_RING=0, the kernel whose warps
+        // load their own keys runs (measured, 64 sequences at 2,048 positions: 44.5 against
+        // 60.7 us; 8 at 8,192: 30.4 against 37.4; equal on chunks of a single block)
+        static int ring_mode = -1;
+        if (ring_mode < 0) { const char* ev = getenv("MINFER_B200_DECODE_RING"); ring_mode = ev ? atoi(ev) : 1; }
+        int e;
+        if (ring_mode && cache_pages > 0 && status != nullptr) {
+            const long long cache_rows = cache_pages * n_kv * MF_PAGE;
+            e = hd == 64 ? launch_decode_ring<64, 6, 2>(a, cache_rows, stream)
+                         : launch_decode_ring<128, 3, 2>(a, cache_rows, stream);
+        } else {
+            e = hd == 64 ? launch_decode_mma<64>(a, stream) : launch_decode_mma<128>(a, stream);
+        }
         if (e || n_chunks == 1) return e;
         // measured: started early, the merge of the chunks costs 5 us more than it saves (its
         // blocks sit on the SMs while the last attention blocks still look for room)
@@ -624,5 +1036,5 @@ extern "C" int mf_attention_paged_noalloc(const void* q, const void* k_cache, co
     }
     return mf_attention_paged(q, k_cache, v_cache, row_seq, row_pos, page_table, table_stride, ring,
                               out, noalloc_scratch_of_device[device], rows, n_heads, n_kv, hd, window,
-                              chunk, n_chunks, scale, dtype, 0, stream);
+                              chunk, n_chunks, scale, dtype, 0, 0, nullptr, stream);
 }

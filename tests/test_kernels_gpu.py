@@ -434,12 +434,16 @@ def test_attention_decode_tensor_core_kernel(hd, nh, nk, window, ring):
         K.attention_paged(q, kc, vc, row_seq, row_pos, table.cuda(), width, ring, out, partial,
                           nh, nk, hd, window, 256, n_chunks, scale, force_generic=force)
         outs[force] = out
-    # chunks of several 256-key blocks (a CTA walks them with a running softmax)
-    for chunk, chunks in ((512, 2), (1024, 1), (768, 2)):
+    # chunks of several 256-key blocks: a CTA walks them with a running softmax, its warps
+    # loading their own keys (no status word) or fed by the TMA ring (with one)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for chunk, chunks, st in ((512, 2, None), (1024, 1, None), (768, 2, None),
+                              (512, 2, status), (1024, 1, status), (768, 2, status)):
         out = torch.full((B, nh * hd), float("nan"), dtype=dt, device="cuda")
         partial = torch.full((B * nh * chunks * (hd + 2),), float("nan"), device="cuda")
         K.attention_paged(q, kc, vc, row_seq, row_pos, table.cuda(), width, ring, out, partial,
-                          nh, nk, hd, window, chunk, chunks, scale)
+                          nh, nk, hd, window, chunk, chunks, scale, status=st)
+        assert int(status.item()) == 0
         close(out, outs[False].double(), dt, scale=3.0)
         for b, n in enumerate(lens):
             qq = torch.zeros(n, nh, hd, dtype=torch.float64)
@@ -449,6 +453,60 @@ def test_attention_decode_tensor_core_kernel(hd, nh, nk, window, ring):
     close(outs[False], outs[True].double(), dt, scale=3.0)
     if window == 0:
         assert torch.allclose(outs[False][6, :hd].float().cpu(), hist_v[6][17, 0].float(), atol=2e-2)
+
+
+@pytest.mark.parametrize("hd,nh,nk,window", [(128, 14, 2, 0), (64, 16, 1, 0), (128, 6, 2, 3000)])
+def test_attention_decode_ring_long_chunks(hd, nh, nk, window):
+    """The TMA-ring decode kernel on chunks of thousands of keys (the ring wraps many times and
+    the producer fetches page ids more than once), pages scattered over the cache, sequences
+    ending at a page edge, inside a page and in the first page of a chunk; a far key in an
+    early page must be found.  Against float64 attention."""
+    from minfer_b200.kernels import api as K
+    lens = [5000, 2049, 4096, 70, 2561]
+    B, width = len(lens), 80
+    n_pages = sum((n + 63) // 64 for n in lens) + 7
+    g = torch.Generator().manual_seed(hd + nh + window)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    scale = 1.0 / math.sqrt(hd)
+    dt = torch.bfloat16
+    kc = torch.randn(n_pages, nk, 64, hd, generator=g).to(dt).cuda()
+    vc = torch.randn(n_pages, nk, 64, hd, generator=g).to(dt).cuda()
+    table = torch.full((B, width), -1, dtype=torch.int32)
+    hist_k, hist_v = [], []
+    q32 = torch.randn(B, nh, hd, generator=g)
+    for b, n in enumerate(lens):
+        kk = torch.randn(n, nk, hd, generator=g)
+        vv = torch.randn(n, nk, hd, generator=g)
+        if n == 5000 and window == 0:           # position 2077 dominates head 1 of the first sequence
+            kk[2077, 0] = 0.0; kk[2077, 0, 5] = 30.0
+            q32[b, 1] = 0.0; q32[b, 1, 5] = 30.0
+        kk, vv = kk.to(dt), vv.to(dt)
+        hist_k.append(kk); hist_v.append(vv)
+        pages = [perm.pop() for _ in range((n + 63) // 64)]
+        table[b, :len(pages)] = torch.tensor(pages, dtype=torch.int32)
+        for i, pg in enumerate(pages):
+            m = min(64, n - 64 * i)
+            kc[pg, :, :m] = kk[64 * i:64 * i + m].transpose(0, 1).cuda()
+            vc[pg, :, :m] = vv[64 * i:64 * i + m].transpose(0, 1).cuda()
+    q = q32.to(dt).cuda()
+    row_seq = torch.arange(B, dtype=torch.int32, device="cuda")
+    row_pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    want = []
+    for b, n in enumerate(lens):
+        qq = torch.zeros(n, nh, hd, dtype=torch.float64)
+        qq[n - 1] = q[b].double().cpu()
+        want.append(attention_reference(qq, hist_k[b].double(), hist_v[b].double(), scale, window)[n - 1])
+    for chunk, chunks in ((5120, 1), (4096, 2), (2560, 2), (512, 10)):
+        out = torch.full((B, nh * hd), float("nan"), dtype=dt, device="cuda")
+        partial = torch.full((B * nh * chunks * (hd + 2),), float("nan"), device="cuda")
+        K.attention_paged(q, kc, vc, row_seq, row_pos, table.cuda(), width, 0, out, partial,
+                          nh, nk, hd, window, chunk, chunks, scale, status=status)
+        assert int(status.item()) == 0
+        for b in range(B):
+            close(out[b].reshape(nh, hd), want[b], dt, scale=3.0)
+        if window == 0:
+            assert torch.allclose(out[0, hd:2 * hd].float().cpu(), hist_v[0][2077, 0].float(), atol=2e-2)
 
 
 @pytest.mark.parametrize("hd", [64, 128])
