@@ -66,6 +66,8 @@ struct AttnArgs {
     int chunk, n_chunks;
     float scale;
     unsigned* status;         // device status word (the kernel with bounded waits only)
+    int old_keys_final;       // 1: of the keys a row sees, only the one at its own position is
+                              // written by a kernel of this step (one new token per sequence)
 };
 
 template <typename T, bool PAGED>
@@ -559,7 +561,11 @@ template <int HD, int STAGES, int MINB>
 __global__ void __launch_bounds__(RING_THREADS, MINB)
 attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k,
                              const __grid_constant__ CUtensorMap map_v, AttnArgs a) {
-    pdl_prologue();
+    // Positions and page tables are copied in before the step's first kernel starts, and (with
+    // old_keys_final) the pages below a row's own position were written by earlier steps: the
+    // producer asks for those before it waits for the kernel before this one, which wrote the
+    // newest key and the queries.  Everything else comes after the wait.
+    pdl_launch_dependents();
     constexpr int HALF_BYTES = MF_PAGE * 128;          // one box: 64 keys x 64 elements
     constexpr int KV_BYTES = (HD / 64) * HALF_BYTES;   // the keys (or the values) of a page
     constexpr int STAGE_BYTES = 2 * KV_BYTES;
@@ -585,6 +591,7 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k,
     const size_t part_stride = (size_t)(HD + 2);
     float* part0 = a.partial + (((size_t)row * a.n_heads + (size_t)hk * G) * a.n_chunks + chunk_id) * part_stride;
     if (k_lo >= k_hi) {                               // nothing of this chunk is visible
+        pdl_wait();
         if (tid < G) {
             float* p = part0 + (size_t)tid * a.n_chunks * part_stride;
             p[0] = -INFINITY;
@@ -609,7 +616,8 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k,
 
     if (warp == RING_CONSUMERS) {
         // ---- producer ---------------------------------------------------------------------
-        bool ok = true;
+        bool ok = true, waited = false;
+        const bool early = a.old_keys_final != 0 && a.ring == 0;
         for (int base = 0; base < n_tiles; base += 32) {
             int page = 0;
             if (base + lane < n_tiles) {
@@ -623,6 +631,11 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k,
                 if (lane == 0 && ok) {
                     const int n = base + i, s = n % STAGES;
                     const uint32_t ph = (uint32_t)(n / STAGES) & 1u;
+                    // a page that ends below the row's position holds no key of this step
+                    if (!waited && !(early && first + (n + 1) * MF_PAGE <= pos)) {
+                        pdl_wait();
+                        waited = true;
+                    }
                     ok = ring_wait(ring_smem(&bars[STAGES + s]), ph ^ 1u, abort_flag);
                     if (ok) {
                         const uint32_t full = ring_smem(&bars[s]);
@@ -639,9 +652,11 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k,
                 }
             }
         }
+        if (lane == 0 && !waited) pdl_wait();
         if (lane == 0 && !ok && a.status) atomicOr(a.status, MF_STATUS_WAIT_TIMEOUT);
         return;
     }
+    pdl_wait();
 
     // ---- consumers ----------------------------------------------------------------------------
     // query fragments: rows g and g+8 of the group (zero beyond the group's heads)
@@ -930,12 +945,15 @@ extern "C" int mf_attention_packed(const void* q, const void* k, const void* v, 
 // Attention over the paged cache.  `partial` must hold rows*n_heads*n_chunks*(hd+2) floats
 // when n_chunks > 1; chunk c covers absolute positions [c*chunk, (c+1)*chunk).  `cache_pages`
 // (pages the cache tensors hold; 0 = unknown) and `status` (may be null) open the TMA-ring kernel.
+// `old_keys_final`: every row is its sequence's only new token in this step, so the keys below
+// its position were in the cache before the step began (the ring kernel then asks for them while
+// the kernel before it still runs).
 extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void* v_cache,
                                   const int* row_seq, const int* row_pos, const int* page_table,
                                   int table_stride, int ring, void* out, float* partial, int rows,
                                   int n_heads, int n_kv, int hd, int window, int chunk, int n_chunks,
                                   float scale, int dtype, int force_generic, long long cache_pages,
-                                  unsigned* status, cudaStream_t stream) {
+                                  unsigned* status, int old_keys_final, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (int e = check_sizes(n_heads, n_kv, hd)) return e;
     if (n_chunks < 1 || (n_chunks > 1 && (partial == nullptr || chunk <= 0))) return MF_ERR_ARGUMENT;
@@ -954,6 +972,7 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
     if (fast) {
         a.partial = partial;
         a.status = status;
+        a.old_keys_final = old_keys_final;
         // the TMA ring needs the cache's extent for its tensor maps and a status word for its
         // bounded waits; without them, or with MINFER_B200_DECODE_RING=0, the kernel whose warps
         // load their own keys runs (measured, 64 sequences at 2,048 positions: 44.5 against
@@ -1036,5 +1055,5 @@ extern "C" int mf_attention_paged_noalloc(const void* q, const void* k_cache, co
     }
     return mf_attention_paged(q, k_cache, v_cache, row_seq, row_pos, page_table, table_stride, ring,
                               out, noalloc_scratch_of_device[device], rows, n_heads, n_kv, hd, window,
-                              chunk, n_chunks, scale, dtype, 0, 0, nullptr, stream);
+                              chunk, n_chunks, scale, dtype, 0, 0, nullptr, 0, stream);
 }

@@ -117,7 +117,7 @@ def _sig_attention(lib: ctypes.CDLL) -> None:
     lib.mf_attention_packed.argtypes = [c_void_p] * 7 + [c_int] * 5 + [c_float, c_int, c_void_p]
     lib.mf_attention_paged.argtypes = ([c_void_p] * 6 + [c_int, c_int, c_void_p, c_void_p] +
                                        [c_int] * 7 + [c_float, c_int, c_int, c_longlong, c_void_p,
-                                                      c_void_p])
+                                                      c_int, c_void_p])
 
 
 def _sig_sampling(lib: ctypes.CDLL) -> None:
@@ -427,12 +427,15 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     table_stride: int, ring: int, out: torch.Tensor,
                     partial: Optional[torch.Tensor], n_heads: int, n_kv: int, head_dim: int,
                     window: int, chunk: int, n_chunks: int, scale: float,
-                    force_generic: bool = False, status: Optional[torch.Tensor] = None) -> None:
+                    force_generic: bool = False, status: Optional[torch.Tensor] = None,
+                    old_keys_final: bool = False) -> None:
     """Attention of ``rows`` queries over the paged cache.  ``partial`` (float32,
     rows*n_heads*n_chunks*(head_dim+2)) is scratch for the key chunks; with it, bfloat16 and
     head size 64 or 128 run on the tensor-core kernels, everything else on the generic one.
-    With ``status`` (the device status word) chunks of more than 256 keys stream through the
-    TMA ring, whose bounded waits report there."""
+    With ``status`` (the device status word) the tensor-core kernel is the one that streams the
+    keys through a TMA ring, whose bounded waits report there.  ``old_keys_final``: each row is the only new
+    token of its sequence in this step (the keys below its position were cached before the step
+    began), which lets that kernel fetch them while the kernel before it still runs."""
     rows = q.shape[0]
     if q.dtype != k_cache.dtype or q.dtype != v_cache.dtype or q.dtype != out.dtype:
         raise KernelError("attention: q, the cache and out must share one dtype")
@@ -446,7 +449,7 @@ def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _i32(row_pos, "row_pos"), _i32(page_table, "page_table"), int(table_stride), int(ring),
         _ptr(out, "out"), _f32(partial, "partial"), rows, n_heads, n_kv, head_dim, int(window),
         int(chunk), int(n_chunks), float(scale), dtype_code(q.dtype), 1 if force_generic else 0,
-        int(k_cache.shape[0]), _i32(status, "status"),
+        int(k_cache.shape[0]), _i32(status, "status"), 1 if old_keys_final else 0,
         _stream()), "attention_paged", 2 if n_chunks > 1 else 1)
 
 

@@ -112,7 +112,7 @@ def attention_decode(reps, batch=64, ctx=2048):
     st = torch.zeros(1, dtype=torch.int32, device="cuda")
     us = _time(lambda: K.attention_paged(q, kc, vc, rows, pos, table, pages_per, 0, out, partial,
                                          NH, NK, HD, 0, chunk, n_chunks, 1 / math.sqrt(HD),
-                                         status=st), reps)
+                                         status=st, old_keys_final=True), reps)
     nbytes = batch * (ctx + 1) * NK * HD * 2 * 2
     print(f"attention decode batch={batch} ctx={ctx}, {n_chunks} chunks of {chunk} keys: {us:.1f} us "
           f"(kernel + merge), {nbytes / us / 1e3:.1f} GB/s of cache")

@@ -197,7 +197,7 @@ class Attention(Mixer):
             K.attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions, cache.page_table,
                               cache.table_stride, cache.ring, o, partial, nh, nk, hd, self.window,
                               chunk, n_chunks, self.scale, force_generic=FORCE_GENERIC_ATTENTION,
-                              status=ctx.status)
+                              status=ctx.status, old_keys_final=ctx.single_token)
         pending = self.out.partial_sums(o)
         if pending is None:
             self.out.forward(o, torch.float32, out=residual, accumulate=True)

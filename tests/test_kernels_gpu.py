@@ -442,7 +442,8 @@ def test_attention_decode_tensor_core_kernel(hd, nh, nk, window, ring):
         out = torch.full((B, nh * hd), float("nan"), dtype=dt, device="cuda")
         partial = torch.full((B * nh * chunks * (hd + 2),), float("nan"), device="cuda")
         K.attention_paged(q, kc, vc, row_seq, row_pos, table.cuda(), width, ring, out, partial,
-                          nh, nk, hd, window, chunk, chunks, scale, status=st)
+                          nh, nk, hd, window, chunk, chunks, scale, status=st,
+                          old_keys_final=st is not None and chunk != 768)
         assert int(status.item()) == 0
         close(out, outs[False].double(), dt, scale=3.0)
         for b, n in enumerate(lens):
@@ -497,11 +498,13 @@ def test_attention_decode_ring_long_chunks(hd, nh, nk, window):
         qq = torch.zeros(n, nh, hd, dtype=torch.float64)
         qq[n - 1] = q[b].double().cpu()
         want.append(attention_reference(qq, hist_k[b].double(), hist_v[b].double(), scale, window)[n - 1])
-    for chunk, chunks in ((5120, 1), (4096, 2), (2560, 2), (512, 10)):
+    for chunk, chunks, final in ((5120, 1, True), (4096, 2, False), (2560, 2, True), (512, 10, True),
+                                 (256, 20, True), (256, 20, False)):
         out = torch.full((B, nh * hd), float("nan"), dtype=dt, device="cuda")
         partial = torch.full((B * nh * chunks * (hd + 2),), float("nan"), device="cuda")
         K.attention_paged(q, kc, vc, row_seq, row_pos, table.cuda(), width, 0, out, partial,
-                          nh, nk, hd, window, chunk, chunks, scale, status=status)
+                          nh, nk, hd, window, chunk, chunks, scale, status=status,
+                          old_keys_final=final)
         assert int(status.item()) == 0
         for b in range(B):
             close(out[b].reshape(nh, hd), want[b], dt, scale=3.0)
