@@ -176,15 +176,16 @@ def attention_prefill_8k(reps):
           f"{flops / us / 1e6:.1f} TFLOP/s (causal)")
 
 
-def _engine(layers):
+def _engine(layers, max_tokens=8 * 4096, max_seqs=8, **sizes):
     from ..engine.step import Engine
     from ..model import Model
     cfg = {"architectures": ["Qwen2ForCausalLM"], "vocab_size": VOCAB, "hidden_size": NE,
            "num_hidden_layers": layers, "num_attention_heads": NH, "num_key_value_heads": NK,
            "intermediate_size": NF, "rope_theta": 1e6, "rms_norm_eps": 1e-6,
            "tie_word_embeddings": False, "max_position_embeddings": 32768}
+    cfg.update(sizes)
     model = Model.from_config(cfg, seed=0, dtype="bfloat16", device="cuda:0", make_on="device")
-    return Engine(model, max_tokens=8 * 4096, max_seqs=8), cfg
+    return Engine(model, max_tokens=max_tokens, max_seqs=max_seqs), cfg
 
 
 def step_prefill(reps, layers=4):
@@ -210,10 +211,25 @@ def step_decode(reps, layers=4):
     print(f"decode step, {layers} layers, batch 8: {us:.1f} us")
 
 
+def step_decode_small(reps, layers=24):
+    """Decode steps of 64 sequences at 16 to 1,024 positions, Qwen2.5-0.5B shape (hidden 896,
+    14 heads / 2 KV heads of 64, intermediate 4864, tied head), all 24 layers."""
+    eng, cfg = _engine(layers, max_tokens=64 * 1280, max_seqs=64, vocab_size=151936,
+                       hidden_size=896, num_attention_heads=14, num_key_value_heads=2,
+                       intermediate_size=4864, tie_word_embeddings=True)
+    g = torch.Generator().manual_seed(3)
+    lens = torch.randint(16, 1025, (64,), generator=g).tolist()
+    slots = [eng.acquire() for _ in range(64)]
+    eng.step(slots, [torch.randint(0, 151936, (n,), generator=g).tolist() for n in lens])
+    tokens = torch.randint(0, 151936, (64,), dtype=torch.int32, device="cuda")
+    us = _time(lambda: eng.decode_on_device(slots, tokens), reps, graph=False)
+    print(f"decode step, small shape, {layers} layers, batch 64 ragged: {us:.1f} us")
+
+
 CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_decode_m64, gemm_decode_split_m64, gemm_prefill, gemm_prefill_down,
                                  attention_decode, attention_decode_b8, attention_decode_long, attention_prefill,
                                  attention_prefill_tc, attention_prefill_tc_8k, attention_prefill_8k,
-                                 step_prefill, step_decode)}
+                                 step_prefill, step_decode, step_decode_small)}
 
 
 def main(argv=None) -> int:
