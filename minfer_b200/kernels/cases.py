@@ -201,14 +201,20 @@ def step_prefill(reps, layers=4):
     print(f"prefill step, {layers} layers, 2048 tokens: {us / 1e3:.2f} ms")
 
 
-def step_decode(reps, layers=4):
+def step_decode(reps, layers=4, batch=8):
     """Decode steps of 8 sequences at 2,048 positions through 4 layers plus the head."""
-    eng, cfg = _engine(layers)
-    slots = [eng.acquire() for _ in range(8)]
-    eng.step(slots, [torch.randint(0, VOCAB, (2048,)).tolist() for _ in range(8)])
-    tokens = torch.randint(0, VOCAB, (8,), dtype=torch.int32, device="cuda")
+    eng, cfg = _engine(layers, max_tokens=batch * 2304, max_seqs=batch)
+    slots = [eng.acquire() for _ in range(batch)]
+    for i in range(0, batch, 8):            # prompts of 8 sequences at a time
+        eng.step(slots[i:i + 8], [torch.randint(0, VOCAB, (2048,)).tolist() for _ in range(8)])
+    tokens = torch.randint(0, VOCAB, (batch,), dtype=torch.int32, device="cuda")
     us = _time(lambda: eng.decode_on_device(slots, tokens), reps, graph=False)
-    print(f"decode step, {layers} layers, batch 8: {us:.1f} us")
+    print(f"decode step, {layers} layers, batch {batch}: {us:.1f} us")
+
+
+def step_decode_b64(reps):
+    """Decode steps of 64 sequences at 2,048 positions through 4 layers plus the head."""
+    step_decode(reps, batch=64)
 
 
 def step_decode_small(reps, layers=24):
@@ -229,7 +235,7 @@ def step_decode_small(reps, layers=24):
 CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_decode_m64, gemm_decode_split_m64, gemm_prefill, gemm_prefill_down,
                                  attention_decode, attention_decode_b8, attention_decode_long, attention_prefill,
                                  attention_prefill_tc, attention_prefill_tc_8k, attention_prefill_8k,
-                                 step_prefill, step_decode, step_decode_small)}
+                                 step_prefill, step_decode, step_decode_b64, step_decode_small)}
 
 
 def main(argv=None) -> int:
