@@ -227,6 +227,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int n_iter = kb1 - kb0;
 
     if (tid == 0) {
+        // the token operand's descriptor is first used after the wait below: fetch it now
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&bars[s]), 1);
             mbar_init(smem_u32(&bars[STAGES + s]), 1);

@@ -91,11 +91,20 @@ template <typename TO>
 __global__ void __launch_bounds__(1024)
 rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
                    const int* __restrict__ rows, TO* __restrict__ y, int width, float eps) {
-    pdl_prologue();
+    // the norm's weights (and the row to take, an input of the step) are fetched while the
+    // kernel before this one still runs
+    pdl_launch_dependents();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int nv = width >> 2;
     const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * width);
+    float4 g[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) g[j] = reinterpret_cast<const float4*>(w)[i];
+    }
+    pdl_wait();
     float4 row[4];
     float ss = 0.0f;
 #pragma unroll
@@ -115,10 +124,9 @@ rmsnorm_vec_kernel(const float* __restrict__ x, const float* __restrict__ w,
     for (int j = 0; j < 4; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i < nv) {
-            const float4 g = reinterpret_cast<const float4*>(w)[i];
             const float4 v = row[j];
-            Pack4<TO>::store(yr + 4 * i, v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z,
-                             v.w * scale * g.w);
+            Pack4<TO>::store(yr + 4 * i, v.x * scale * g[j].x, v.y * scale * g[j].y,
+                             v.z * scale * g[j].z, v.w * scale * g[j].w);
         }
     }
 }
@@ -192,13 +200,21 @@ __global__ void __launch_bounds__(1024)
 add_rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ partial, int n_partials,
                        const float* __restrict__ bias, const float* __restrict__ w,
                        TO* __restrict__ y, int n_rows, int width, float eps) {
-    pdl_prologue();
+    // the norm's weights are fetched while the kernel before this one still runs
+    pdl_launch_dependents();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const int nv = width >> 2;                         // float4 per row
     float4* hr = reinterpret_cast<float4*>(h + (size_t)r * width);
     const size_t plane4 = ((size_t)n_rows * width) >> 2;
     const float4* pr = reinterpret_cast<const float4*>(partial) + ((size_t)r * width >> 2);
+    float4 g[ARN_MAXV];
+#pragma unroll
+    for (int j = 0; j < ARN_MAXV; ++j) {
+        const int i = threadIdx.x + j * blockDim.x;
+        if (i < nv) g[j] = reinterpret_cast<const float4*>(w)[i];
+    }
+    pdl_wait();
     float4 row[ARN_MAXV];
     float ss = 0.0f;
 #pragma unroll
@@ -230,10 +246,9 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ partial,
     for (int j = 0; j < ARN_MAXV; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i < nv) {
-            const float4 g = reinterpret_cast<const float4*>(w)[i];
             const float4 v = row[j];
-            Pack4<TO>::store(yr + 4 * i, v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z,
-                             v.w * scale * g.w);
+            Pack4<TO>::store(yr + 4 * i, v.x * scale * g[j].x, v.y * scale * g[j].y,
+                             v.z * scale * g[j].z, v.w * scale * g[j].w);
         }
     }
 }
@@ -419,7 +434,10 @@ rope_kvstore_vec_kernel(const float* __restrict__ qkv, int n_partials, int n_tok
                         T* __restrict__ v_cache, const int* __restrict__ page_table,
                         int table_stride, int ring, int n_heads, int n_kv, int hd,
                         unsigned* __restrict__ status) {
-    pdl_prologue();
+    // Positions, rows, page tables, inverse frequencies and the bias are the step's inputs
+    // (copied to the device before its first kernel) or weights: they are read, and the
+    // angles' sines and cosines formed, while the projection before this kernel still runs.
+    pdl_launch_dependents();
     __shared__ float2 cs_table[128];
     const int t = blockIdx.x;
     const int pos = positions[t];
@@ -463,6 +481,7 @@ rope_kvstore_vec_kernel(const float* __restrict__ qkv, int n_partials, int n_tok
         }
     }
     __syncthreads();
+    pdl_wait();                    // from here on: the projection's sums
     const int upr = half >> 2;                         // units per rotated head
     const int n_rot = (n_heads + n_kv) * upr;
     const int upv = hd >> 3;                           // units per value head
