@@ -195,7 +195,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const float* __restric
 // the same for widths that are multiples of 4 up to 4 * 4 * 1024: float4 accesses, the row
 // kept in registers, all loads of a thread independent of each other
 #define ARN_MAXV 4
-template <typename TO>
+template <typename TO, int MAXV>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ partial, int n_partials,
                        const float* __restrict__ bias, const float* __restrict__ w,
@@ -208,21 +208,23 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ partial,
     float4* hr = reinterpret_cast<float4*>(h + (size_t)r * width);
     const size_t plane4 = ((size_t)n_rows * width) >> 2;
     const float4* pr = reinterpret_cast<const float4*>(partial) + ((size_t)r * width >> 2);
-    float4 g[ARN_MAXV];
+    float4 g[MAXV];
 #pragma unroll
-    for (int j = 0; j < ARN_MAXV; ++j) {
+    for (int j = 0; j < MAXV; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i < nv) g[j] = reinterpret_cast<const float4*>(w)[i];
     }
     pdl_wait();
-    float4 row[ARN_MAXV];
+    float4 row[MAXV];
     float ss = 0.0f;
 #pragma unroll
-    for (int j = 0; j < ARN_MAXV; ++j) {
+    for (int j = 0; j < MAXV; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i < nv) {
+            float4 v;
+            if (MAXV == 1) v = hr[i];                 // in flight together with the splits
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
+#pragma unroll (MAXV == 1 ? 8 : 4)
             for (int s = 0; s < n_partials; ++s) {
                 const float4 p = pr[s * plane4 + i];
                 acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
@@ -231,7 +233,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ partial,
                 const float4 b = reinterpret_cast<const float4*>(bias)[i];
                 acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
             }
-            float4 v = hr[i];
+            if (MAXV != 1) v = hr[i];
             v.x += acc.x; v.y += acc.y; v.z += acc.z; v.w += acc.w;
             hr[i] = v;
             row[j] = v;
@@ -243,7 +245,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ partial,
     const float scale = 1.0f / sqrtf(ss / (float)width + eps);
     TO* yr = y + (size_t)r * width;
 #pragma unroll
-    for (int j = 0; j < ARN_MAXV; ++j) {
+    for (int j = 0; j < MAXV; ++j) {
         const int i = threadIdx.x + j * blockDim.x;
         if (i < nv) {
             const float4 v = row[j];
@@ -264,10 +266,13 @@ extern "C" int mf_add_rmsnorm(float* h, const float* partial, int n_partials, co
         int threads = 32;
         while (threads < 1024 && threads * 4 < width) threads <<= 1;
         if (out_dtype == MF_DTYPE_F32)
-            mf_launch(add_rmsnorm_vec_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, 
+            mf_launch(add_rmsnorm_vec_kernel<float, ARN_MAXV>, dim3(n_rows), dim3(threads), 0, stream,
                 h, partial, n_partials, bias, w, (float*)y, n_rows, width, eps);
+        else if (width <= 4 * 1024)        // one float4 a thread: more splits in flight at once
+            mf_launch(add_rmsnorm_vec_kernel<__nv_bfloat16, 1>, dim3(n_rows), dim3(threads), 0, stream,
+                h, partial, n_partials, bias, w, (__nv_bfloat16*)y, n_rows, width, eps);
         else
-            mf_launch(add_rmsnorm_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, 
+            mf_launch(add_rmsnorm_vec_kernel<__nv_bfloat16, ARN_MAXV>, dim3(n_rows), dim3(threads), 0, stream,
                 h, partial, n_partials, bias, w, (__nv_bfloat16*)y, n_rows, width, eps);
         return MF_LAUNCH_CHECK();
     }
@@ -451,17 +456,32 @@ rope_kvstore_vec_kernel(const float* __restrict__ qkv, int n_partials, int n_tok
     const size_t in_width = (size_t)(n_heads + 2 * n_kv) * hd;
     const float* in = qkv + (size_t)t * in_width;
     const size_t plane = (size_t)n_tokens * in_width;
-    auto load4 = [&](int col) -> float4 {
-        float4 v = *reinterpret_cast<const float4*>(in + col);
-        for (int sp = 1; sp < n_partials; ++sp) {
-            const float4 p = *reinterpret_cast<const float4*>(in + sp * plane + col);
-            v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+    // the sums of two columns at once: all loads of up to 8 splits are issued before the first
+    // addition (splits are added in split order, as everywhere)
+    auto load_pair = [&](int col_a, int col_c, float4& a, float4& c) {
+        a = *reinterpret_cast<const float4*>(in + col_a);
+        c = *reinterpret_cast<const float4*>(in + col_c);
+        for (int s0 = 1; s0 < n_partials; s0 += 8) {
+            float4 pa[8], pc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (s0 + j < n_partials) {
+                    pa[j] = *reinterpret_cast<const float4*>(in + (s0 + j) * plane + col_a);
+                    pc[j] = *reinterpret_cast<const float4*>(in + (s0 + j) * plane + col_c);
+                }
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (s0 + j < n_partials) {
+                    a.x += pa[j].x; a.y += pa[j].y; a.z += pa[j].z; a.w += pa[j].w;
+                    c.x += pc[j].x; c.y += pc[j].y; c.z += pc[j].z; c.w += pc[j].w;
+                }
         }
         if (bias != nullptr) {
-            const float4 bb = *reinterpret_cast<const float4*>(bias + col);
-            v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w;
+            const float4 ba = *reinterpret_cast<const float4*>(bias + col_a);
+            const float4 bc = *reinterpret_cast<const float4*>(bias + col_c);
+            a.x += ba.x; a.y += ba.y; a.z += ba.z; a.w += ba.w;
+            c.x += bc.x; c.y += bc.y; c.z += bc.z; c.w += bc.w;
         }
-        return v;
     };
     long long cache_row = -1;
     if (k_cache != nullptr) {
@@ -490,7 +510,8 @@ rope_kvstore_vec_kernel(const float* __restrict__ qkv, int n_partials, int n_tok
         if (u < n_rot) {
             const int head = u / upr;
             const int i0 = (u - head * upr) << 2;
-            const float4 a = load4(head * hd + i0), c = load4(head * hd + half + i0);
+            float4 a, c;
+            load_pair(head * hd + i0, head * hd + half + i0, a, c);
             const float av[4] = {a.x, a.y, a.z, a.w}, cv[4] = {c.x, c.y, c.z, c.w};
             float lo[4], hi[4];
 #pragma unroll
@@ -521,7 +542,8 @@ rope_kvstore_vec_kernel(const float* __restrict__ qkv, int n_partials, int n_tok
             const int hk = idx / upv;
             const int e0 = (idx - hk * upv) << 3;
             const int col = (n_heads + n_kv + hk) * hd + e0;
-            const float4 a = load4(col), c = load4(col + 4);
+            float4 a, c;
+            load_pair(col, col + 4, a, c);
             if (v_out != nullptr) {
                 T* o = v_out + ((size_t)t * n_kv + hk) * hd + e0;
                 Pack4<T>::store(o, a.x, a.y, a.z, a.w);
