@@ -191,20 +191,39 @@ __global__ void attention_combine_kernel(const float* __restrict__ partial, T* _
     const size_t stride = (size_t)(hd + 2);
     const float* p = partial + rh * n_chunks * stride;
     if (n_chunks <= 16) {
-        // few chunks: every thread reads the maxima and sums itself; no barrier at all
+        // few chunks: every thread reads the maxima and sums itself (no barrier at all) and
+        // asks for its first output dimension's values in the same breath: one round trip
+        float mc[16], lc[16], oc[16];
+        const int d0 = threadIdx.x;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            if (c < n_chunks) {
+                mc[c] = p[(size_t)c * stride];
+                lc[c] = p[(size_t)c * stride + 1];
+                oc[c] = d0 < hd ? p[(size_t)c * stride + 2 + d0] : 0.0f;
+            }
+        }
         float m = -INFINITY;
-        for (int c = 0; c < n_chunks; ++c) m = fmaxf(m, p[(size_t)c * stride]);
+#pragma unroll
+        for (int c = 0; c < 16; ++c)
+            if (c < n_chunks) m = fmaxf(m, mc[c]);
         float l = 0.0f;
-        for (int c = 0; c < n_chunks; ++c) {
-            const float mc = p[(size_t)c * stride];
-            if (mc > -INFINITY) l += p[(size_t)c * stride + 1] * expf(mc - m);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            if (c < n_chunks) {
+                mc[c] = mc[c] > -INFINITY ? expf(mc[c] - m) : 0.0f;     // the chunk's factor
+                if (mc[c] > 0.0f) l += lc[c] * mc[c];
+            }
         }
         const float inv = 1.0f / l;
-        for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+        for (int d = d0; d < hd; d += blockDim.x) {
             float o = 0.0f;
-            for (int c = 0; c < n_chunks; ++c) {
-                const float mc = p[(size_t)c * stride];
-                if (mc > -INFINITY) o = fmaf(p[(size_t)c * stride + 2 + d], expf(mc - m), o);
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                if (c < n_chunks) {
+                    const float v = d == d0 ? oc[c] : p[(size_t)c * stride + 2 + d];
+                    if (mc[c] > 0.0f) o = fmaf(v, mc[c], o);
+                }
             }
             out[rh * hd + d] = from_f32<T>(o * inv);
         }

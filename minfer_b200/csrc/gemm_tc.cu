@@ -259,6 +259,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             mbar_expect_tx(full, STAGE_BYTES);
             tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_w, (kb0 + i) * TILE_K, n0, full);
         }
+        // a CTA with only a few tiles beyond its ring asks for them in L2, so that the refill
+        // after the first MMAs is not a trip to HBM on the step's critical path
+        if (n_iter <= STAGES + 2)
+            for (int i = pre; i < n_iter; ++i)
+                asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                             ::"l"(&map_w), "r"((kb0 + i) * TILE_K), "r"(n0) : "memory");
         pdl_wait();
         for (int i = 0; i < pre; ++i)
             tma_load_2d(smem_u32(smem + i * STAGE_BYTES) + A_BYTES, &map_x, (kb0 + i) * TILE_K, m0,
