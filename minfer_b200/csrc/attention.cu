@@ -645,6 +645,19 @@ attention_decode_ring_kernel(const __grid_constant__ CUtensorMap map_k,
                 page = a.page_table[(size_t)b * a.table_stride + (p_eff >> 6)];
             }
             const int cnt = min(32, n_tiles - base);
+            // the next few old pages beyond the ring: asked for in L2 now, so that their turn in
+            // the ring is not a trip to HBM
+            if (base == 0 && early && lane >= STAGES && lane < 2 * STAGES && lane < n_tiles &&
+                first + (lane + 1) * MF_PAGE <= pos) {
+                const int y = (page * a.n_kv + hk) * MF_PAGE;
+#pragma unroll
+                for (int h = 0; h < HD / 64; ++h) {
+                    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                                 ::"l"(&map_k), "r"(h * 64), "r"(y) : "memory");
+                    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                                 ::"l"(&map_v), "r"(h * 64), "r"(y) : "memory");
+                }
+            }
             for (int i = 0; i < cnt; ++i) {
                 const int pg = __shfl_sync(0xffffffffu, page, i);
                 if (lane == 0 && ok) {

@@ -224,7 +224,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ partial,
             float4 v;
             if (MAXV == 1) v = hr[i];                 // in flight together with the splits
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll (MAXV == 1 ? 8 : 4)
+#pragma unroll (MAXV == 1 ? 10 : 4)
             for (int s = 0; s < n_partials; ++s) {
                 const float4 p = pr[s * plane4 + i];
                 acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
