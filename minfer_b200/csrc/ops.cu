@@ -429,7 +429,10 @@ __global__ void rope_kvstore_kernel(const float* __restrict__ qkv, int n_partial
 // The common case in wide accesses: pairs (i, i + hd/2), the whole head rotated, head sizes
 // that are multiples of 8.  A thread takes 4 neighbouring pairs of a q or k head (two float4
 // loads per split, two 4-element stores per destination) or 8 elements of a v head.
-template <typename T>
+// SPLIT: the input holds K splits of the projection (decoding: few tokens, every load of a
+// thread in flight at once); without it the kernel keeps few registers, so that many CTAs of
+// a long prompt share an SM and hide each other's loads.
+template <typename T, bool SPLIT>
 __global__ void __launch_bounds__(128)
 rope_kvstore_vec_kernel(const float* __restrict__ qkv, int n_partials, int n_tokens,
                         const float* __restrict__ bias, const int* __restrict__ positions,
@@ -461,7 +464,7 @@ rope_kvstore_vec_kernel(const float* __restrict__ qkv, int n_partials, int n_tok
     auto load_pair = [&](int col_a, int col_c, float4& a, float4& c) {
         a = *reinterpret_cast<const float4*>(in + col_a);
         c = *reinterpret_cast<const float4*>(in + col_c);
-        for (int s0 = 1; s0 < n_partials; s0 += 8) {
+        for (int s0 = 1; SPLIT && s0 < n_partials; s0 += 8) {
             float4 pa[8], pc[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j)
@@ -585,17 +588,17 @@ extern "C" int mf_rope_kvstore(const float* qkv, int n_partials, const float* bi
         if (vy > vy_max) vy = vy_max;
         if (vy < 1) vy = 1;
         const dim3 vgrid(n_tokens, vy);
-        if (dtype == MF_DTYPE_F32)
-            mf_launch(rope_kvstore_vec_kernel<float>, vgrid, dim3(threads), 0, stream, qkv, n_partials,
-                      n_tokens, bias, positions, token_row, seq_end, inv_freq, (float*)q_out,
-                      (float*)k_out, (float*)v_out, (float*)k_cache, (float*)v_cache, page_table,
-                      table_stride, ring, n_heads, n_kv, hd, status);
-        else
-            mf_launch(rope_kvstore_vec_kernel<__nv_bfloat16>, vgrid, dim3(threads), 0, stream, qkv,
-                      n_partials, n_tokens, bias, positions, token_row, seq_end, inv_freq,
-                      (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out,
-                      (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, page_table, table_stride,
-                      ring, n_heads, n_kv, hd, status);
+#define MF_ROPE_VEC(T, SPLIT)                                                                    \
+    mf_launch(rope_kvstore_vec_kernel<T, SPLIT>, vgrid, dim3(threads), 0, stream, qkv, n_partials, \
+              n_tokens, bias, positions, token_row, seq_end, inv_freq, (T*)q_out, (T*)k_out,       \
+              (T*)v_out, (T*)k_cache, (T*)v_cache, page_table, table_stride, ring, n_heads, n_kv,  \
+              hd, status)
+        if (dtype == MF_DTYPE_F32) {
+            if (n_partials > 1) MF_ROPE_VEC(float, true); else MF_ROPE_VEC(float, false);
+        } else {
+            if (n_partials > 1) MF_ROPE_VEC(__nv_bfloat16, true); else MF_ROPE_VEC(__nv_bfloat16, false);
+        }
+#undef MF_ROPE_VEC
         return MF_LAUNCH_CHECK();
     }
     if (dtype == MF_DTYPE_F32)
