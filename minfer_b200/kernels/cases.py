@@ -212,6 +212,38 @@ def step_decode(reps, layers=4, batch=8):
     print(f"decode step, {layers} layers, batch {batch}: {us:.1f} us")
 
 
+def step_decode_timeline(reps, layers=4, batch=8):
+    """The kernels of one replayed decode step (8 sequences at 2,048 positions, 4 layers) with
+    their start and end times inside the graph, from CUPTI activity records."""
+    from torch.profiler import ProfilerActivity, profile
+    eng, cfg = _engine(layers, max_tokens=batch * 2304, max_seqs=batch)
+    slots = [eng.acquire() for _ in range(batch)]
+    for i in range(0, batch, 8):
+        eng.step(slots[i:i + 8], [torch.randint(0, VOCAB, (2048,)).tolist() for _ in range(8)])
+    tokens = torch.randint(0, VOCAB, (batch,), dtype=torch.int32, device="cuda")
+    for _ in range(5):
+        eng.decode_on_device(slots, tokens)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        for _ in range(max(1, reps)):
+            eng.decode_on_device(slots, tokens)
+        torch.cuda.synchronize()
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    evs.sort(key=lambda e: e.time_range.start)
+    first = [i for i, e in enumerate(evs) if "embed_kernel" in e.name][-1]
+    step = evs[first:]
+    t0 = step[0].time_range.start
+    # a kernel starts early (its CTAs wait for the kernel before it): what it costs the step is
+    # the time from the end of the kernel before it to its own end
+    print(f"{'kernel':46s} {'start':>8s} {'end':>8s} {'after the one before':>21s}")
+    prev_end = t0
+    for e in step:
+        start, end = e.time_range.start - t0, e.time_range.end - t0
+        print(f"{e.name[:46]:46s} {start:8.1f} {end:8.1f} {end - max(prev_end - t0, 0.0):21.1f}")
+        prev_end = max(prev_end, e.time_range.end)
+    print(f"step: {step[-1].time_range.end - t0:.1f} us")
+
+
 def step_decode_b64(reps):
     """Decode steps of 64 sequences at 2,048 positions through 4 layers plus the head."""
     step_decode(reps, batch=64)
@@ -235,7 +267,8 @@ def step_decode_small(reps, layers=24):
 CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_decode_m64, gemm_decode_split_m64, gemm_prefill, gemm_prefill_down,
                                  attention_decode, attention_decode_b8, attention_decode_long, attention_prefill,
                                  attention_prefill_tc, attention_prefill_tc_8k, attention_prefill_8k,
-                                 step_prefill, step_decode, step_decode_b64, step_decode_small)}
+                                 step_prefill, step_decode, step_decode_timeline, step_decode_b64,
+                                 step_decode_small)}
 
 
 def main(argv=None) -> int:
