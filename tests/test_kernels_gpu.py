@@ -338,11 +338,13 @@ def test_unsupported_sizes_are_refused_not_miscomputed():
                                    (33, 640, 200), (64, 512, 1024), (100, 384, 512),
                                    (300, 640, 3584), (8, 3584, 3584), (700, 1000, 264),
                                    (2048, 3584, 128), (2048, 4608, 64), (16576, 256, 64),
-                                   (14208, 256, 72)])
+                                   (14208, 256, 72), (64, 896, 896), (8, 1152, 896),
+                                   (40, 896, 4864)])
 def test_gemm_tensor_core_against_float64(m, n, k):
     """The tcgen05 kernels at every token tile (16..128 for one CTA; 160, 192, 208, 224 and 256
     for the CTA pair: the last four sizes each pick another one), with and without K splits,
-    ragged edges in all three dimensions, every epilogue."""
+    ragged edges in all three dimensions, every epilogue.  The last three are small weights,
+    which are cut along K until a CTA has two k-blocks (7 splits; 16 with a short last one)."""
     from minfer_b200.kernels import api as K
     g = torch.Generator().manual_seed(m + n + k)
     x = (torch.randn(m, k, generator=g) * 0.5).bfloat16().cuda()
