@@ -244,6 +244,11 @@ def step_decode_timeline(reps, layers=4, batch=8):
     print(f"step: {step[-1].time_range.end - t0:.1f} us")
 
 
+def step_decode_timeline_b64(reps):
+    """The same timeline for 64 sequences at 2,048 positions."""
+    step_decode_timeline(reps, batch=64)
+
+
 def step_decode_b64(reps):
     """Decode steps of 64 sequences at 2,048 positions through 4 layers plus the head."""
     step_decode(reps, batch=64)
@@ -267,7 +272,7 @@ def step_decode_small(reps, layers=24):
 CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_decode_m64, gemm_decode_split_m64, gemm_prefill, gemm_prefill_down,
                                  attention_decode, attention_decode_b8, attention_decode_long, attention_prefill,
                                  attention_prefill_tc, attention_prefill_tc_8k, attention_prefill_8k,
-                                 step_prefill, step_decode, step_decode_timeline, step_decode_b64,
+                                 step_prefill, step_decode, step_decode_timeline, step_decode_timeline_b64, step_decode_b64,
                                  step_decode_small)}
 
 
