@@ -166,6 +166,8 @@ def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: tor
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
             rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = rmsnorm(x[rows[r]] or x[r]) * weight.  ``weight`` and ``rows`` are read while
+    the kernel before this one may still run: weights, or inputs of the step."""
     n, width = out.shape
     if x.shape[1] != width or weight.numel() != width:
         raise KernelError("rmsnorm: shapes do not fit")
@@ -200,7 +202,13 @@ def rope_kvstore(qkv: torch.Tensor, positions: torch.Tensor, token_row: torch.Te
                  status: torch.Tensor, n_partials: int = 0,
                  bias: Optional[torch.Tensor] = None) -> None:
     """``n_partials`` > 0: ``qkv`` is [n_partials, tokens, width], the K splits a deferred
-    projection left; they are added here in split order, with ``bias``."""
+    projection left; they are added here in split order, with ``bias``.
+
+    The kernel reads ``positions``, ``token_row``, ``seq_end``, ``page_table``, ``inv_freq`` and
+    ``bias`` while the kernel before it may still run (it only waits for that kernel before it
+    touches ``qkv``).  They must therefore be final before the step's first kernel starts, as
+    the engine's step inputs are (one copy to the device in front of the step), or be written
+    by an ordinary launch, which this kernel waits for in full."""
     if n_partials > 0:
         if qkv.dim() != 3 or qkv.shape[0] != n_partials:
             raise KernelError("rope_kvstore: partial sums must be [splits, tokens, width]")
