@@ -118,6 +118,25 @@ def test_cli_generates(tiny, capsys):
     assert "Prefill: 3 tokens" in out and "Generated: 6 tokens" in out
 
 
+def test_cli_as_a_process(tiny):
+    """``bin/minfer-b200`` as a user starts it: its own process, killed if it hangs.  The
+    reference prints usage and fails on an unknown flag (src/main.rs:280-286); so does this."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
+    exe = os.path.join(root, "bin", "minfer-b200")
+    run = subprocess.run([sys.executable, exe, tiny["folder"], "5,17,3", "--greedy",
+                          "--repeat-penalty", "1.0", "-n", "4", "--dtype", "bfloat16"],
+                         capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0, run.stderr[-2000:]
+    assert "Prefill: 3 tokens" in run.stdout and "Generated:" in run.stdout
+    bad = subprocess.run([sys.executable, exe, tiny["folder"], "--no-such-flag"],
+                         capture_output=True, text=True, timeout=120)
+    assert bad.returncode != 0
+    assert "usage" in (bad.stderr + bad.stdout).lower()
+
+
 def test_model_conveniences(tiny):
     """``from_pretrained``, ``new_session`` and ``Model.generate`` are the loader, the engine
     and the generator under other names: the same logits and tokens."""
