@@ -23,6 +23,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 PAGE = 64
@@ -132,6 +133,10 @@ class CacheGroup:
         # one page more than the pool hands out: the spare page, for rows that only fill a batch
         # up to a size the engine has a captured graph for
         self.spare_page = n_pages
+        # the page lists once more as one integer table (a row per slot, -1 where a sequence
+        # has no page, the spare slot's row last): a step's page tables are one slice of it
+        self._table = np.full((n_slots + 1, 8), -1, dtype=np.int32)
+        self._table[n_slots, 0] = self.spare_page
         shape = (len(self.entries), n_pages + 1, key.n_kv_heads, PAGE, key.head_dim)
         # zeros, once: a page's unwritten positions are masked by length but still multiplied
         # by a zero weight in the tensor-core kernels, so they must never hold NaN or Inf
@@ -151,11 +156,17 @@ class CacheGroup:
         need = self.pages_needed(length)
         while len(have) < need:
             have.append(self.pool.take(slot))
+            if len(have) > self._table.shape[1]:
+                wider = np.full((self._table.shape[0], 2 * self._table.shape[1]), -1, dtype=np.int32)
+                wider[:, :self._table.shape[1]] = self._table
+                self._table = wider
+            self._table[slot, len(have) - 1] = have[-1]
 
     def release(self, slot: int) -> None:
         for p in self.pages[slot]:
             self.pool.give_back(p, slot)
         self.pages[slot] = []
+        self._table[slot, :] = -1
 
     def entry_tensors(self, entry: int) -> Tuple[torch.Tensor, torch.Tensor]:
         i = self._index[entry]
@@ -169,6 +180,17 @@ class CacheGroup:
                 raise CacheError("the page table is narrower than a sequence's pages")
             rows.append(pg + [-1] * (width - len(pg)))
         return rows
+
+    def table_flat(self, slots: Sequence[int], width: int) -> List[int]:
+        """``table_rows`` row after row in one list, from the integer table."""
+        if self.max_pages_of(slots) > width:
+            raise CacheError("the page table is narrower than a sequence's pages")
+        have = self._table.shape[1]
+        if width <= have:
+            return self._table[list(slots), :width].ravel().tolist()
+        out = np.full((len(slots), width), -1, dtype=np.int32)
+        out[:, :have] = self._table[list(slots)]
+        return out.ravel().tolist()
 
     def max_pages_of(self, slots: Sequence[int]) -> int:
         return max((len(self.pages[s]) for s in slots if s < len(self.pages)), default=0)

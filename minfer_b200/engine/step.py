@@ -210,6 +210,14 @@ class Engine:
         cu_seqlens, lengths after the step, slots, wanted rows, then one page table per cache
         group (``widths[g]`` entries a row, -1 where a sequence has no page)."""
         n_rows = len(slots)
+        if all(c == 1 for c in counts) and all(len(w) == 1 and w[0] == 0 for w in want):
+            # one token a row, each row's logits wanted (decoding): no loop over the rows' tokens
+            rows = list(range(n_rows))
+            fields = [[int(t[0]) for t in tokens], list(starts), rows, list(range(n_rows + 1)),
+                      [p + 1 for p in starts], list(slots), rows]
+            for g, width in zip(self.cache.groups, widths):
+                fields.append(g.table_flat(slots, width))
+            return fields
         flat_tokens, positions, token_row, cu, want_rows = [], [], [], [0], []
         for b in range(n_rows):
             base = cu[-1]
@@ -221,8 +229,7 @@ class Engine:
         seq_end = [starts[b] + counts[b] for b in range(n_rows)]
         fields = [flat_tokens, positions, token_row, cu, seq_end, list(slots), want_rows]
         for g, width in zip(self.cache.groups, widths):
-            rows = g.table_rows(slots, width)
-            fields.append([p for row in rows for p in row])
+            fields.append(g.table_flat(slots, width))
         return fields
 
     def _views(self, dev: torch.Tensor, sizes) -> List[torch.Tensor]:
@@ -304,7 +311,7 @@ class Engine:
         entry["next"] += 1
         host, event = ring[slot_i]
         event.synchronize()                         # the copy that last used this buffer is done
-        host.copy_(torch.tensor(flat, dtype=torch.int32))
+        host.numpy()[:] = flat
         entry["dev"].copy_(host, non_blocking=True)
         event.record()
         self.h2d_bytes += host.numel() * 4
