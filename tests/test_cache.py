@@ -91,6 +91,10 @@ def test_a_page_is_never_held_twice_nor_lost_under_churn():
                 assert all(g.pool.owner(p) == s for p in g.pages[s])
                 if s not in live:
                     assert g.pages[s] == []
+            # the integer table a step's page tables are cut from mirrors the page lists
+            rows = list(live) + [c.spare_slot]
+            width = max(1, g.max_pages_of(rows)) + rng.randint(0, 2)
+            assert g.table_flat(rows, width) == [p for r in g.table_rows(rows, width) for p in r]
     for s in list(live):
         c.release(s)
     assert c.free_pages() == [g.n_pages for g in c.groups]
