@@ -10,7 +10,12 @@ server slot (src/server/slot.rs:15-32), and has one kind of layer only.  Here:
   them all back when its slot is released, so later batches use them again.
 * Cache entries with the same needs form a *group* with storage, pages and page tables of
   its own.  A group is either linear (every position is kept) or a ring of
-  ``ceil(window / 64) * 64`` positions (a windowed mixer never reads further back).
+  ``ceil((window + step_tokens - 1) / 64) * 64`` positions: a windowed mixer never reads
+  further back than ``window`` positions, and a step writes its new positions before it
+  attends, so a sequence may add up to ``ring - window + 1`` positions in one step without
+  overwriting a position that the step's first new token still sees
+  (``CacheGroup.max_new_positions``).  Whole prompts attend over the step's own keys and are
+  not bound by this.
 * Validity is a sequence's length, never a memset: a reused page still holds the last
   owner's values and nothing reads them.
 * ``StatePool`` holds fixed-size state per slot (zeroed when the slot is handed out) for
@@ -39,6 +44,14 @@ class OutOfPages(CacheError):
 
 def pages_for(n_positions: int) -> int:
     return (n_positions + PAGE - 1) // PAGE
+
+
+def ring_positions(window: int, step_tokens: int = 1) -> int:
+    """Positions a ring keeps for a window of ``window`` when a sequence may add
+    ``step_tokens`` positions in a step that reads the ring (0 for no window)."""
+    if window <= 0:
+        return 0
+    return pages_for(window + max(1, int(step_tokens)) - 1) * PAGE
 
 
 class SlotTable:
@@ -123,10 +136,10 @@ class CacheGroup:
     """Storage, pages and page tables of the cache entries that share one ``GroupKey``."""
 
     def __init__(self, key: GroupKey, entries: Sequence[int], n_pages: int, n_slots: int,
-                 dtype: torch.dtype, device: torch.device | str):
+                 dtype: torch.dtype, device: torch.device | str, step_tokens: int = 1):
         self.key = key
         self.entries = list(entries)
-        self.ring = pages_for(key.window) * PAGE if key.window > 0 else 0
+        self.ring = ring_positions(key.window, step_tokens)
         self.n_pages = n_pages
         self.pool = PagePool(n_pages)
         self.pages: List[List[int]] = [[] for _ in range(n_slots)]
@@ -143,6 +156,15 @@ class CacheGroup:
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         self.v = torch.zeros(shape, dtype=dtype, device=device)
         self._index = {e: i for i, e in enumerate(self.entries)}
+
+    def max_new_positions(self) -> Optional[int]:
+        """Most positions a sequence may add in one step whose tokens attend over this group's
+        storage (None: no bound).  Position ``p`` lies at ``p % ring``; the first new token at
+        ``s`` sees back to ``s - window + 1``, which the write of ``s + n - 1`` must not reach:
+        ``n <= ring - window + 1``."""
+        if not self.ring:
+            return None
+        return self.ring - self.key.window + 1
 
     def pages_needed(self, length: int) -> int:
         need = pages_for(length)
@@ -224,7 +246,7 @@ class Cache:
     ``GroupKey`` of the mixer that writes it."""
 
     def __init__(self, requests: Dict[int, GroupKey], max_tokens: int, max_seqs: int,
-                 dtype: torch.dtype, device: torch.device | str):
+                 dtype: torch.dtype, device: torch.device | str, step_tokens: int = 1):
         if max_tokens <= 0 or max_tokens % PAGE != 0:
             raise CacheError(f"max_tokens must be a positive multiple of {PAGE}, got {max_tokens}")
         self.max_tokens = max_tokens
@@ -245,8 +267,8 @@ class Cache:
         for key, entries in by_key.items():
             n_pages = total_pages
             if key.window > 0:
-                n_pages = min(total_pages, max_seqs * pages_for(key.window))
-            g = CacheGroup(key, entries, n_pages, max_seqs, dtype, device)
+                n_pages = min(total_pages, max_seqs * (ring_positions(key.window, step_tokens) // PAGE))
+            g = CacheGroup(key, entries, n_pages, max_seqs, dtype, device, step_tokens)
             self.groups.append(g)
             for e in entries:
                 self.group_of[e] = g
@@ -276,6 +298,12 @@ class Cache:
     def set_length(self, slot: int, length: int) -> None:
         self.slots.check(slot)
         self.slots.length[slot] = length
+
+    def max_new_positions(self) -> Optional[int]:
+        """Most tokens a sequence may bring in one step that attends over the cache (None: no
+        bound): the smallest bound of the groups."""
+        bounds = [b for b in (g.max_new_positions() for g in self.groups) if b is not None]
+        return min(bounds) if bounds else None
 
     def bytes(self) -> int:
         """Bytes of key/value storage that sequences can hold (the spare pages not counted)."""

@@ -1,5 +1,6 @@
-"""The step function: a batch of sequences that start together, with unequal lengths; their
-whole prompts in one step, then one token each.
+"""The step function: a batch of sequences, each going on from where its slot stands by one
+or more tokens: whole prompts in one step, one token each, a prompt in portions, or a new
+prompt beside sequences that decode.
 
 The reference's step is ``forward_cached(tokens, positions, n_out, n_ctx, cache)`` for one
 sequence (src/models/qwen2/graph.rs:276-408): it checks ``max(pos) < n_ctx`` (:288-293),
@@ -12,6 +13,12 @@ serves every step.
 ``Engine.step`` runs only the tokens it is given, as one batch, from the cache that earlier
 steps left, and returns float32 logits at the wanted places.  Rows are independent: no
 kernel's result for one row depends on what else is in the batch.
+
+Three shapes of a step, told apart on the host: every row starts at position 0 (whole
+prompts: attention over the step's own keys), every row brings one token (decoding: replayed
+as a CUDA graph), anything else (attention of the step's tokens over the cache, which holds
+their keys by then).  A cache group that keeps a ring of positions can take only so many new
+positions of a sequence in a step of the third shape; longer rows are run in portions.
 """
 from __future__ import annotations
 
@@ -40,10 +47,13 @@ def padded_rows(n_rows: int) -> int:
 
 class Engine:
     """A model plus its cache.  ``max_tokens`` is the most tokens live sequences hold at any
-    time, each sequence's count rounded up to a multiple of 64; it sizes the cache."""
+    time, each sequence's count rounded up to a multiple of 64; it sizes the cache.
+    ``ring_step_tokens``: how many tokens a sequence that goes on may bring in one pass over
+    layers with a window (their rings are that much longer than the window; longer rows are
+    run in portions of at least that many tokens)."""
 
     def __init__(self, model: Model, max_tokens: int, max_seqs: Optional[int] = None,
-                 cuda_graphs: bool = True):
+                 cuda_graphs: bool = True, ring_step_tokens: int = 256):
         if model.device is None or model.device.type != "cuda":
             raise StepError("the model's weights must be on a CUDA device (there is no CPU path)")
         self.model = model
@@ -77,7 +87,8 @@ class Engine:
                         f"a call reads cache entry {call.cache} with {want}, but it is written "
                         f"with {requests.get(call.cache)}")
         self._readers = readers
-        self.cache = Cache(requests, max_tokens, self.max_seqs, self.dtype, self.device)
+        self.cache = Cache(requests, max_tokens, self.max_seqs, self.dtype, self.device,
+                           step_tokens=ring_step_tokens)
         # per-sequence state of fixed size, per call
         self._call_state: List[Dict[str, torch.Tensor]] = []
         for i, call in enumerate(plan.schedule):
@@ -135,12 +146,6 @@ class Engine:
         if min(counts) < 1:
             raise StepError("every sequence of a step brings at least one token")
         starts = [self.cache.length(s) for s in slots]
-        from_start = all(s == 0 for s in starts)
-        single = all(c == 1 for c in counts)
-        if not from_start and not single:
-            raise StepError(
-                "the sequences of a step either all start at their first token or all go on "
-                "by one token")
         for b in range(n_rows):
             if starts[b] + counts[b] > plan.max_positions:
                 raise StepError(
@@ -158,7 +163,20 @@ class Engine:
                     raise StepError(f"wanted place {w} is outside the {counts[b]} tokens given")
         for b in range(n_rows):
             self.cache.reserve(slots[b], starts[b] + counts[b])
+        from_start = all(s == 0 for s in starts)
+        limit = self.cache.max_new_positions()
+        if not from_start and limit is not None and max(counts) > limit:
+            logits = self._step_in_portions(slots, tokens, want, counts, limit)
+        else:
+            logits = self._step_once(slots, tokens, want, counts, starts)
+        self.steps_run += 1
+        return logits
 
+    def _step_once(self, slots, tokens, want, counts, starts) -> torch.Tensor:
+        """One pass of the model over the rows' tokens (pages are reserved already)."""
+        n_rows = len(slots)
+        from_start = all(s == 0 for s in starts)
+        single = all(c == 1 for c in counts)
         logits = None
         if (self.cuda_graphs and single and not from_start
                 and all(list(w) == [0] for w in want)):
@@ -170,8 +188,36 @@ class Engine:
             logits = self._run(ctx, want_rows)
         for b in range(n_rows):
             self.cache.set_length(slots[b], starts[b] + counts[b])
-        self.steps_run += 1
         return logits
+
+    def _step_in_portions(self, slots, tokens, want, counts, limit: int) -> torch.Tensor:
+        """A step some of whose rows bring more tokens than a ring of the cache can take at
+        once: pass ``i`` runs tokens ``[i * limit, (i + 1) * limit)`` of every row that has
+        them.  The wanted logits come back in the order of the rows and of ``want``."""
+        n_rows = len(slots)
+        # where each wanted place goes in the result
+        first = [0] * n_rows
+        for b in range(1, n_rows):
+            first[b] = first[b - 1] + len(want[b - 1])
+        n_want = first[-1] + len(want[-1])
+        out = torch.empty((n_want, self.model.plan.vocab_size), dtype=torch.float32,
+                          device=self.device)
+        for lo in range(0, max(counts), limit):
+            rows = [b for b in range(n_rows) if counts[b] > lo]
+            sub_tokens = [tokens[b][lo:lo + limit] for b in rows]
+            sub_want, dest = [], []
+            for b in rows:
+                hi = min(lo + limit, counts[b])
+                picked = [(i, int(w)) for i, w in enumerate(want[b]) if lo <= int(w) < hi]
+                sub_want.append([w - lo for _, w in picked])
+                dest.extend(first[b] + i for i, _ in picked)
+            sub_slots = [slots[b] for b in rows]
+            sub_counts = [len(t) for t in sub_tokens]
+            sub_starts = [self.cache.length(s) for s in sub_slots]
+            got = self._step_once(sub_slots, sub_tokens, sub_want, sub_counts, sub_starts)
+            if dest:
+                out[torch.tensor(dest, dtype=torch.long, device=self.device)] = got
+        return out
 
     def decode_on_device(self, slots: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
         """One token per sequence, the token ids already on the device (int32 [rows], for

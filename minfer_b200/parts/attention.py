@@ -9,7 +9,9 @@ projection is the only path: one product, then one kernel that rotates and write
 cache, then attention, then Wo with the residual add in its epilogue.
 
 Whole prompts (every row of the step starts at position 0) attend over the step's own keys
-and values; any other step attends over the cache.  All sizes are parameters.
+and values; any other step (one token a row, a prompt's later portion, a mix of both)
+attends over the cache, which by then holds the step's keys too: every token is a query at
+its own absolute position.  All sizes are parameters.
 """
 from __future__ import annotations
 
@@ -182,11 +184,13 @@ class Attention(Mixer):
                 K.attention_packed(q, k_step, v_step, ctx.token_row, ctx.positions,
                                    ctx.cu_seqlens, o, nh, nk, hd, self.window, self.scale)
         else:
-            # keys and values come from the cache: a later token of a sequence
-            if cache.ring and not ctx.single_token:
+            # keys and values come from the cache, the step's own among them: each token is a
+            # query at its position
+            if cache.ring and ctx.max_row_tokens > cache.ring - self.window + 1:
                 raise K.KernelError(
-                    "a windowed cache is read one token at a time: several tokens of a sequence "
-                    "in one step must start at position 0")
+                    f"a sequence brings {ctx.max_row_tokens} tokens, but a ring of {cache.ring} "
+                    f"positions with a window of {self.window} takes "
+                    f"{cache.ring - self.window + 1} a step (the engine runs longer rows in portions)")
             chunk, n_chunks = decode_chunks(n * nk, ctx.max_end, tensor_cores=(
                 act == torch.bfloat16 and hd in (64, 128) and nh // nk <= 16
                 and not FORCE_GENERIC_ATTENTION))

@@ -86,3 +86,26 @@ def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
     got = got.detach().to(torch.float64).cpu()
     want = want.detach().to(torch.float64).cpu()
     return float((got - want).abs().max() / max(1e-30, float(want.abs().max())))
+
+
+# bfloat16, row by row: the root mean square error of a row of logits as a fraction of the
+# largest logit of the comparison.  The largest single error of a bfloat16 run has a long tail
+# (one logit in 14,000 of configuration E is 3.2 % off on the whole-prompt path itself), while a
+# fault of the cache or of the batch (a key missing, a stale page, a neighbour's row) moves a
+# whole row by tens of per cent; measured over all six configurations the worst row stays
+# below 0.9 %.
+ROW_RMS_TOL = 1.25e-2
+
+
+def row_rms_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    got = got.detach().to(torch.float64).cpu()
+    want = want.detach().to(torch.float64).cpu()
+    rms = (got - want).pow(2).mean(dim=-1).sqrt().max()
+    return float(rms / max(1e-30, float(want.abs().max())))
+
+
+def logits_err(got: torch.Tensor, want: torch.Tensor, dtype: str) -> tuple:
+    """(error, bound): float32 by the largest single error, bfloat16 by the worst row."""
+    if dtype == "float32":
+        return rel_err(got, want), TOL["float32"]
+    return row_rms_err(got, want), ROW_RMS_TOL

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 import plain_qwen2 as P
-from helpers import TINY, TOL, make_folder, random_ids, rel_err
+from helpers import TINY, TOL, logits_err, make_folder, random_ids, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -185,5 +185,102 @@ def test_batches_that_shrink_share_graphs_and_padding_changes_nothing():
     sizes = {k[0] for k in set(eng._graphs) - graphs_before}
     assert sizes <= {4, 8}, sizes
     for s in slots:
+        eng.release(s)
+    eng.check_status()
+
+
+# ---- any cut: prompts in portions, several tokens onto a sequence, starting beside decoding ----
+CUT_LENGTHS = [130, 300, 66]
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E", "F"])
+def tiny_cuts(request):
+    folder = make_folder(request.param)
+    cfg, w = P.load_folder(folder)
+    prompts = [random_ids(n, cfg["vocab_size"], 720 + i) for i, n in enumerate(CUT_LENGTHS)]
+    plain = [P.forward(cfg, w, ids) for ids in prompts]
+    return {"name": request.param, "folder": folder, "cfg": cfg, "prompts": prompts, "plain": plain}
+
+
+def _close(got, want, dtype):
+    err, bound = logits_err(got, want, dtype)
+    return err < bound
+
+
+def _in_portions(eng, ids, sizes):
+    """Feeds ``ids`` into a fresh slot in portions of the given sizes (the last size repeats),
+    asking for every place; returns the logits [len(ids), vocab]."""
+    s = eng.acquire()
+    rows, at, i = [], 0, 0
+    while at < len(ids):
+        n = sizes[min(i, len(sizes) - 1)]
+        part = ids[at:at + n]
+        rows.append(eng.step([s], [part], [list(range(len(part)))]))
+        at += len(part)
+        i += 1
+    eng.release(s)
+    return torch.cat(rows)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sizes", [[7], [64], [65], [200], [1, 2, 63, 64, 65], [2]])
+def test_prompt_in_portions(tiny_cuts, dtype, sizes):
+    """A prompt cut into portions of 7, 64, 65, 200, two tokens, or at 1, 3, 66, 130, 195: the
+    logits at every place are those of the whole sequence."""
+    eng = _engine(tiny_cuts["folder"], dtype)
+    for ids, want in zip(tiny_cuts["prompts"], tiny_cuts["plain"]):
+        if sizes == [2] and len(ids) > 140:
+            continue
+        got = _in_portions(eng, ids, sizes)
+        assert got.shape == want.shape
+        assert _close(got, want, dtype), (tiny_cuts["name"], len(ids), sizes)
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_rings_run_long_portions_in_passes(tiny_cuts, dtype):
+    """Rings no longer than the window's pages: a portion longer than a ring takes is run in
+    several passes by the engine, with the same logits; the last 32 tokens in portions of 4."""
+    from minfer_b200.engine.step import Engine
+    from minfer_b200.model import Model
+    eng = Engine(Model.from_folder(tiny_cuts["folder"], dtype, "cuda:0"), max_tokens=2048,
+                 ring_step_tokens=1)
+    limit = eng.cache.max_new_positions()
+    windowed = bool(tiny_cuts["cfg"].get("use_sliding_window"))
+    assert (limit is not None) == windowed
+    for ids, want in zip(tiny_cuts["prompts"], tiny_cuts["plain"]):
+        got = _in_portions(eng, ids, [50, 200])
+        assert _close(got, want, dtype), (tiny_cuts["name"], len(ids))
+        got = _in_portions(eng, ids, [len(ids) - 32, 4])
+        assert _close(got, want, dtype), (tiny_cuts["name"], len(ids))
+    assert all(n == eng.cache.groups[i].n_pages for i, n in enumerate(eng.cache.free_pages()))
+    eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_rows_that_start_beside_rows_that_go_on(tiny_cuts, dtype):
+    """One step holds a whole new prompt, two sequences that go on by one token and one that
+    goes on by five; the next one a second portion beside decoding rows; wanted places in
+    another order than the tokens'."""
+    eng = _engine(tiny_cuts["folder"], dtype)
+    p, plain = tiny_cuts["prompts"], tiny_cuts["plain"]
+    a, b, c, d = (eng.acquire() for _ in range(4))
+    ids_d = p[0][:47]                                   # a fourth request: the start of the first
+    out = eng.step([a, b, c], [p[0][:100], p[1][:250], p[2][:30]])
+    assert _close(out, torch.stack([plain[0][99], plain[1][249], plain[2][29]]), dtype)
+    out = eng.step([a, d, b, c], [[p[0][100]], ids_d[:40], [p[1][250]], p[2][30:35]],
+                   [[0], [39, 0, 17], [0], [4, 0]])
+    want = torch.stack([plain[0][100], plain[0][39], plain[0][0], plain[0][17], plain[1][250],
+                        plain[2][34], plain[2][30]])
+    assert _close(out, want, dtype), tiny_cuts["name"]
+    out = eng.step([d, a, c], [ids_d[40:47], [p[0][101]], [p[2][35]]], [[6, 5], [0], [0]])
+    want = torch.stack([plain[0][46], plain[0][45], plain[0][101], plain[2][35]])
+    assert _close(out, want, dtype), tiny_cuts["name"]
+    # and decoding goes on from there (through the graph path, if any)
+    for t in range(3):
+        out = eng.step([a, b, c, d], [[p[0][102 + t]], [p[1][251 + t]], [p[2][36 + t]], [p[0][47 + t]]])
+        want = torch.stack([plain[0][102 + t], plain[1][251 + t], plain[2][36 + t], plain[0][47 + t]])
+        assert _close(out, want, dtype), (tiny_cuts["name"], t)
+    for s in (a, b, c, d):
         eng.release(s)
     eng.check_status()

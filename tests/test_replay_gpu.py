@@ -1,6 +1,7 @@
 """bin/trace_run as a user runs it: a process fed JSON lines, writing <step>.f32 files.
-Whole requests, the last tokens one by one (long decoding included), and batches of unequal
-lengths one after another, in float32 and bfloat16, against the plain implementation."""
+Whole requests, the last tokens one by one (long decoding included), batches of unequal
+lengths one after another, and a request in portions beside others that decode or start, in
+float32 and bfloat16, against the plain implementation."""
 import json
 import os
 import subprocess
@@ -94,9 +95,28 @@ def test_replay_three_ways(tiny, dtype):
         rest = [r + "b" for r in batch if len(prompts[r]) == 1]
         steps.append({"step": n, "entries": [], "end": rest})
         n += 1
+    # 4. a request fed in portions (7 tokens, then 64, then the rest) while another decodes beside it,
+    #    joined by a third that starts later
+    ids0, ids4, ids1 = prompts["r0"], prompts["r4"], prompts["r1"]
+    steps.append({"step": n, "entries": [{"id": "c4", "tokens": ids4[:200], "want": [199]},
+                                         {"id": "c0", "tokens": ids0[:7], "want": [6, 0]}], "end": []})
+    expect.append((n, [("r4", [199]), ("r0", [6, 0])]))
+    n += 1
+    steps.append({"step": n, "entries": [{"id": "c4", "tokens": [ids4[200]], "want": [0]},
+                                         {"id": "c0", "tokens": ids0[7:71], "want": [63, 1]}], "end": []})
+    expect.append((n, [("r4", [200]), ("r0", [70, 8])]))
+    n += 1
+    steps.append({"step": n, "entries": [{"id": "c1", "tokens": ids1, "want": [len(ids1) - 1]},
+                                         {"id": "c4", "tokens": ids4[201:203], "want": [0, 1]},
+                                         {"id": "c0", "tokens": ids0[71:], "want": list(range(len(ids0) - 71))}],
+                  "end": ["c0", "c1", "c4"]})
+    expect.append((n, [("r1", [len(ids1) - 1]), ("r4", [201, 202]), ("r0", list(range(71, len(ids0))))]))
+    n += 1
+    steps.append({"step": n, "entries": [], "end": []})
+    n += 1
     # the cache is sized for what is live at once: the largest batch, each rounded up to 64
     live_max = max(sum(-(-len(prompts[r]) // 64) * 64 for r in b)
-                   for b in (["r0", "r1", "r2", "r3"], ["r4", "r3", "r1"]))
+                   for b in (["r0", "r1", "r2", "r3"], ["r4", "r3", "r1"], ["r4", "r0", "r1"]))
     out = run_trace(folder, dtype, steps, live_max)
     for step, wants in expect:
         got = read_logits(out, step, V)
