@@ -26,6 +26,16 @@
 //   key tiles than the first: causal edge, window): each tile has its own range of key tiles.
 // Rows of the packed tensors that lie beyond a sequence's end belong to the next sequence;
 // they are masked by position, never used.  Every mbarrier wait is bounded.
+//
+// PAGED: the step's tokens go on from what the cache holds (a prompt's later portion, several
+// tokens onto a sequence, rows that start beside rows that go on).  The queries are the
+// step's packed rows as before, at absolute positions start + i with start = the sequence's
+// length before the step; keys and values are read from the paged cache, which holds the
+// step's own by then (the kernel before this one wrote them).  A key tile is 128 absolute
+// positions = two pages of one key/value head, fetched as two boxes of 64 rows through tensor
+// maps over the layer's cache; the mask is by absolute position.  Positions of a page beyond a
+// sequence's end hold finite leftovers (storage is zeroed once and only ever written by
+// kernels); causality masks them.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -46,6 +56,11 @@ struct FaArgs {
     unsigned* status;
     int n_heads, n_kv, window;
     float scale_log2;         // scale * log2(e)
+    // PAGED only
+    const int* seq_end;       // [sequences] length after this step
+    const int* page_table;    // [sequences][table_stride] pages of 64 positions, -1 = none
+    int table_stride;
+    int ring;                 // 0 = linear, else position p lies at p % ring
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------
@@ -152,7 +167,7 @@ __device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int HD>
+template <int HD, bool PAGED>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const FaArgs a) {
@@ -185,14 +200,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int q0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * FA_CTA_Q;     // heavy tiles first
     if (q0 >= len) return;
     const int hk = head / (a.n_heads / a.n_kv);
+    // position of the step's first token of this sequence (0 for whole prompts), and the end of
+    // the keys that exist: packed keys end with the sequence, cached ones are masked by causality
+    const int pos0 = PAGED ? a.seq_end[seq] - len : 0;
+    const int key_end = PAGED ? 0x7fffffff : len;
     // the key tiles of each query tile: [kb, ke); the second tile may be beyond the sequence
     int kb[2], ke[2];
 #pragma unroll
     for (int t = 0; t < 2; ++t) {
         const int q0t = q0 + t * FA_Q;
         if (q0t < len) {
-            kb[t] = a.window > 0 ? max(0, q0t - a.window + 1) / FA_KEYS : 0;
-            ke[t] = (min(q0t + FA_Q, len) - 1) / FA_KEYS + 1;
+            kb[t] = a.window > 0 ? max(0, pos0 + q0t - a.window + 1) / FA_KEYS : 0;
+            ke[t] = (pos0 + min(q0t + FA_Q, len) - 1) / FA_KEYS + 1;
         } else {
             kb[t] = ke[t] = 0;
         }
@@ -241,6 +260,33 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         for (int i = 0; i < n_tiles; ++i) {
             const int st = i & 1;
             const uint32_t free_parity = (uint32_t)((i >> 1) & 1) ^ 1u;
+            if (PAGED) {
+                // the tile's two pages: rows (page * n_kv + hk) * 64 .. + 63 of the cache seen as
+                // [rows][HD]; a page the sequence does not have (beyond its end) reads page 0,
+                // whose positions causality masks
+                int y[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int p = (lo + i) * FA_KEYS + h * MF_PAGE;
+                    const int idx = (a.ring > 0 ? p % a.ring : p) >> 6;
+                    int page = idx < a.table_stride ? a.page_table[(size_t)seq * a.table_stride + idx] : 0;
+                    if (page < 0) page = 0;
+                    y[h] = (page * a.n_kv + hk) * MF_PAGE;
+                }
+                if (!fa_wait(fa_smem(&k_empty[st]), free_parity, abort_flag)) break;
+                fa_expect_tx(fa_smem(&k_full[st]), T_BYTES);
+                for (int c = 0; c < NB; ++c)
+                    for (int h = 0; h < 2; ++h)
+                        fa_tma(fa_smem(k_s + st * T_BYTES + c * BLOCK + h * (BLOCK / 2)), &map_k, 64 * c, y[h],
+                               fa_smem(&k_full[st]));
+                if (!fa_wait(fa_smem(&v_empty[st]), free_parity, abort_flag)) break;
+                fa_expect_tx(fa_smem(&v_full[st]), T_BYTES);
+                for (int c = 0; c < NB; ++c)
+                    for (int h = 0; h < 2; ++h)
+                        fa_tma(fa_smem(v_s + st * T_BYTES + c * BLOCK + h * (BLOCK / 2)), &map_v, 64 * c, y[h],
+                               fa_smem(&v_full[st]));
+                continue;
+            }
             const int key0 = tok0 + (lo + i) * FA_KEYS;
             if (!fa_wait(fa_smem(&k_empty[st]), free_parity, abort_flag)) break;
             fa_expect_tx(fa_smem(&k_full[st]), T_BYTES);
@@ -323,7 +369,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int quarter = warp & 3;                    // the 32 TMEM lanes this warp may touch
         const int row = quarter * 32 + lane;             // row of the tile = TMEM lane
         const int q0t = q0 + t * FA_Q;
-        const int qpos = q0t + row;
+        const int qrow = q0t + row;                      // this thread's query among the sequence's rows
+        const int qpos = pos0 + qrow;                    // and its absolute position
+        const int wpos = pos0 + q0t + quarter * 32;      // position of this warp's first query
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         const uint32_t s_addr = lane_addr + (uint32_t)(TM_S + t * 128);
         const uint32_t o_addr = lane_addr + (uint32_t)(TM_O + t * 128);
@@ -336,8 +384,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // S of this key tile is complete, and with it every earlier product of this query tile
             if (!fa_wait(fa_smem(&s_full[t]), (uint32_t)(c & 1), abort_flag)) { ok = false; break; }
             fa_fence_after();
-            const bool need_mask = key0 + FA_KEYS - 1 > q0t + quarter * 32 || key0 + FA_KEYS > len ||
-                                   (a.window > 0 && key0 < q0t + quarter * 32 + 31 - a.window + 1);
+            const bool need_mask = key0 + FA_KEYS - 1 > wpos || key0 + FA_KEYS > key_end ||
+                                   (a.window > 0 && key0 < wpos + 31 - a.window + 1);
             // the whole row of S (128 scores) into registers, masked by position where the tile
             // touches the diagonal, the window's edge or the sequence's end
             uint32_t sr[FA_KEYS];
@@ -348,7 +396,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int i = 0; i < FA_KEYS; ++i) {
                     const int key = key0 + i;
-                    const bool vis = key <= qpos && key < len && (a.window == 0 || qpos - key < a.window);
+                    const bool vis = key <= qpos && key < key_end && (a.window == 0 || qpos - key < a.window);
                     if (!vis) sr[i] = 0xff800000u;            // -inf
                 }
             }
@@ -405,13 +453,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (ok && ke_t > kb_t && fa_wait(fa_smem(&o_done[t]), 0u, abort_flag)) {
             fa_fence_after();
             const float inv = 1.0f / l;
-            __nv_bfloat16* o = a.out + ((long long)(tok0 + qpos) * a.n_heads + head) * HD;
+            __nv_bfloat16* o = a.out + ((long long)(tok0 + qrow) * a.n_heads + head) * HD;
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 32) {
                 uint32_t r[32];
                 fa_ld32(o_addr + (uint32_t)c0, r);
                 fa_wait_ld();
-                if (qpos < len) {
+                if (qrow < len) {
 #pragma unroll
                     for (int i = 0; i < 32; i += 8) {
                         uint4 v;
@@ -472,19 +520,35 @@ static int fa_map(CUtensorMap* map, const void* ptr, long long tokens, long long
     return r == CUDA_SUCCESS ? 0 : MF_ERR_TENSORMAP;
 }
 
-template <int HD>
+// the paged cache of a layer seen as [rows][hd] bf16, box = one page of one key/value head as
+// [64 rows][64 columns]
+static int fa_cache_map(CUtensorMap* map, const void* ptr, long long rows, int hd) {
+    FaEncodeFn fn = fa_encode_fn();
+    if (!fn) return MF_ERR_NO_TENSORMAP;
+    if (rows <= 0 || rows > 0x7fffffffLL) return MF_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    cuuint32_t box[2] = {64, MF_PAGE};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : MF_ERR_TENSORMAP;
+}
+
+template <int HD, bool PAGED>
 static int fa_launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaArgs& a,
                      int n_seqs, int max_len, cudaStream_t stream) {
     constexpr int smem = (HD / 64) * 16384 * 6 + 1024 + 256;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD>,
+        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, PAGED>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     dim3 grid(a.n_heads, (max_len + FA_CTA_Q - 1) / FA_CTA_Q, n_seqs);
-    mf_launch(attention_prefill_tc_kernel<HD>, grid, dim3(FA_THREADS), smem, stream, mq, mk, mv, a);
+    mf_launch(attention_prefill_tc_kernel<HD, PAGED>, grid, dim3(FA_THREADS), smem, stream, mq, mk, mv, a);
     return MF_LAUNCH_CHECK();
 }
 
@@ -503,10 +567,39 @@ extern "C" int mf_attention_prefill_tc(const void* q, const void* k, const void*
     if (int e = fa_map(&mq, q, n_tokens, (long long)n_heads * hd)) return e;
     if (int e = fa_map(&mk, k, n_tokens, (long long)n_kv * hd)) return e;
     if (int e = fa_map(&mv, v, n_tokens, (long long)n_kv * hd)) return e;
-    FaArgs a;
+    FaArgs a{};
     a.cu_seqlens = cu_seqlens; a.out = (__nv_bfloat16*)out; a.status = status;
     a.n_heads = n_heads; a.n_kv = n_kv; a.window = window;
     a.scale_log2 = scale * 1.4426950408889634f;
-    return hd == 64 ? fa_launch<64>(mq, mk, mv, a, n_seqs, max_len, stream)
-                    : fa_launch<128>(mq, mk, mv, a, n_seqs, max_len, stream);
+    return hd == 64 ? fa_launch<64, false>(mq, mk, mv, a, n_seqs, max_len, stream)
+                    : fa_launch<128, false>(mq, mk, mv, a, n_seqs, max_len, stream);
+}
+
+// The step's tokens (q [tokens][n_heads][hd], sequence b = tokens cu_seqlens[b] .. cu_seqlens[b+1]-1,
+// max_len the most of one sequence) at positions seq_end[b] - count .. seq_end[b] - 1 attend over
+// the paged cache k/v [cache_pages][n_kv][64][hd], which already holds those positions' own keys.
+extern "C" int mf_attention_prefill_tc_paged(const void* q, const void* k_cache, const void* v_cache,
+                                             const int* cu_seqlens, const int* seq_end, const int* page_table,
+                                             int table_stride, int ring, void* out, int n_tokens, int n_seqs,
+                                             int max_len, int n_heads, int n_kv, int hd, int window,
+                                             float scale, long long cache_pages, unsigned* status,
+                                             cudaStream_t stream) {
+    if (n_seqs <= 0 || max_len <= 0 || n_tokens <= 0) return 0;
+    if ((hd != 64 && hd != 128) || n_kv <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
+    if (n_seqs > 65535 || (max_len + FA_CTA_Q - 1) / FA_CTA_Q > 65535) return MF_ERR_UNSUPPORTED;
+    if (((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15))
+        return MF_ERR_UNSUPPORTED;
+    if (cache_pages <= 0 || table_stride <= 0 || ring % MF_PAGE != 0 || !seq_end || !page_table)
+        return MF_ERR_ARGUMENT;
+    CUtensorMap mq, mk, mv;
+    if (int e = fa_map(&mq, q, n_tokens, (long long)n_heads * hd)) return e;
+    if (int e = fa_cache_map(&mk, k_cache, cache_pages * n_kv * MF_PAGE, hd)) return e;
+    if (int e = fa_cache_map(&mv, v_cache, cache_pages * n_kv * MF_PAGE, hd)) return e;
+    FaArgs a{};
+    a.cu_seqlens = cu_seqlens; a.out = (__nv_bfloat16*)out; a.status = status;
+    a.n_heads = n_heads; a.n_kv = n_kv; a.window = window;
+    a.scale_log2 = scale * 1.4426950408889634f;
+    a.seq_end = seq_end; a.page_table = page_table; a.table_stride = table_stride; a.ring = ring;
+    return hd == 64 ? fa_launch<64, true>(mq, mk, mv, a, n_seqs, max_len, stream)
+                    : fa_launch<128, true>(mq, mk, mv, a, n_seqs, max_len, stream);
 }

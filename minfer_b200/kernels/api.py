@@ -144,6 +144,8 @@ def _sig_attention_prefill(lib: ctypes.CDLL) -> None:
 
 def _sig_attention_prefill_tc(lib: ctypes.CDLL) -> None:
     lib.mf_attention_prefill_tc.argtypes = [c_void_p] * 5 + [c_int] * 7 + [c_float, c_void_p, c_void_p]
+    lib.mf_attention_prefill_tc_paged.argtypes = ([c_void_p] * 6 + [c_int, c_int, c_void_p] + [c_int] * 7 +
+                                                  [c_float, c_longlong, c_void_p, c_void_p])
 
 
 _SIGNATURES = {"attention_prefill_tc": _sig_attention_prefill_tc,
@@ -428,6 +430,27 @@ def attention_prefill_tc(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_s
         _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v"), _i32(cu_seqlens, "cu_seqlens"), _ptr(out, "out"),
         int(q.shape[0]), int(n_seqs), int(max_len), n_heads, n_kv, head_dim, int(window), float(scale),
         _i32(status, "status"), _stream()), "attention_prefill_tc")
+
+
+def attention_prefill_tc_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                               cu_seqlens: torch.Tensor, seq_end: torch.Tensor,
+                               page_table: torch.Tensor, table_stride: int, ring: int,
+                               out: torch.Tensor, n_seqs: int, max_len: int, n_heads: int, n_kv: int,
+                               head_dim: int, window: int, scale: float,
+                               status: torch.Tensor) -> None:
+    """Attention of a step's packed tokens over the paged cache on tcgen05: sequence ``b``
+    brings tokens ``cu_seqlens[b] .. cu_seqlens[b+1]-1`` at positions
+    ``seq_end[b] - count .. seq_end[b] - 1``; the cache holds every position up to there, the
+    step's own included.  ``max_len`` is the most tokens one sequence brings."""
+    for t in (q, k_cache, v_cache, out):
+        if t.dtype != torch.bfloat16:
+            raise KernelError("attention_prefill_tc_paged takes bfloat16")
+    _check(_lib("attention_prefill_tc").mf_attention_prefill_tc_paged(
+        _ptr(q, "q"), _ptr(k_cache, "k_cache"), _ptr(v_cache, "v_cache"),
+        _i32(cu_seqlens, "cu_seqlens"), _i32(seq_end, "seq_end"), _i32(page_table, "page_table"),
+        int(table_stride), int(ring), _ptr(out, "out"), int(q.shape[0]), int(n_seqs), int(max_len),
+        n_heads, n_kv, head_dim, int(window), float(scale), int(k_cache.shape[0]),
+        _i32(status, "status"), _stream()), "attention_prefill_tc_paged")
 
 
 def attention_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

@@ -29,6 +29,10 @@ from .linear import Linear
 DECODE_CHUNK = 256     # keys per block when attending over the cache
 DECODE_CTAS = int(os.environ.get("MINFER_B200_DECODE_CTAS", "296"))   # CTAs the decode kernel wants in flight: two on each of 148 SMs
 FORCE_GENERIC_ATTENTION = os.environ.get("MINFER_B200_GENERIC_ATTENTION", "0") == "1"
+# a step that is neither whole prompts nor one token a row runs the tcgen05 kernel over the
+# cache's pages from this many tokens on; below, every token is a row of the decode kernel
+# (a query tile of 128 rows for a handful of tokens wastes the tensor cores' time)
+PAGED_PROMPT_MIN_TOKENS = int(os.environ.get("MINFER_B200_PAGED_PROMPT_MIN_TOKENS", "1"))
 # "tcgen05" (tensor memory, the default) or "mma" (the mma.sync twin) for whole prompts in bfloat16
 PROMPT_ATTENTION = os.environ.get("MINFER_B200_PROMPT_ATTENTION", "tcgen05")
 
@@ -191,6 +195,16 @@ class Attention(Mixer):
                     f"a sequence brings {ctx.max_row_tokens} tokens, but a ring of {cache.ring} "
                     f"positions with a window of {self.window} takes "
                     f"{cache.ring - self.window + 1} a step (the engine runs longer rows in portions)")
+            if (not ctx.single_token and PROMPT_ATTENTION != "mma" and not FORCE_GENERIC_ATTENTION
+                    and K.attention_prefill_supported(q, nh, nk, hd)
+                    and ctx.n_tokens >= PAGED_PROMPT_MIN_TOKENS):
+                # several tokens a row: query tiles of the step's rows over the cache's pages
+                K.attention_prefill_tc_paged(q, cache.k, cache.v, ctx.cu_seqlens, ctx.seq_end,
+                                             cache.page_table, cache.table_stride, cache.ring, o,
+                                             ctx.n_rows, ctx.max_row_tokens, nh, nk, hd,
+                                             self.window, self.scale, ctx.status)
+                self._project_out(o, ctx, residual)
+                return
             chunk, n_chunks = decode_chunks(n * nk, ctx.max_end, tensor_cores=(
                 act == torch.bfloat16 and hd in (64, 128) and nh // nk <= 16
                 and not FORCE_GENERIC_ATTENTION))
@@ -202,6 +216,9 @@ class Attention(Mixer):
                               cache.table_stride, cache.ring, o, partial, nh, nk, hd, self.window,
                               chunk, n_chunks, self.scale, force_generic=FORCE_GENERIC_ATTENTION,
                               status=ctx.status, old_keys_final=ctx.single_token)
+        self._project_out(o, ctx, residual)
+
+    def _project_out(self, o: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
         pending = self.out.partial_sums(o)
         if pending is None:
             self.out.forward(o, torch.float32, out=residual, accumulate=True)
