@@ -58,7 +58,25 @@ TINY_F = {
     "rope_theta": 500000.0, "rms_norm_eps": 2e-6, "tie_word_embeddings": True,
     "use_sliding_window": False, "max_position_embeddings": 512,
 }
-TINY = {"A": (TINY_A, 0, 0.0), "B": (TINY_B, 1, 0.01), "C": (TINY_C, 2, 0.02),
+# The two tiny configurations exactly as the headline's record states them (sizes, options,
+# weights N(0, 0.02), norm weights 1 and 1 + N(0, 0.01)); A-F above are louder variants of
+# them (other vocabulary and widths that are no multiples of anything, weights N(0, 0.08)).
+TINY_A0 = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 256, "hidden_size": 64, "num_hidden_layers": 2,
+    "num_attention_heads": 4, "num_key_value_heads": 1, "intermediate_size": 128,
+    "rope_theta": 10000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": True,
+    "use_sliding_window": False, "max_position_embeddings": 128,
+}
+TINY_B0 = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 384, "hidden_size": 192, "num_hidden_layers": 3,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "intermediate_size": 320,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False,
+    "use_sliding_window": True, "sliding_window": 16, "max_window_layers": 1,
+    "max_position_embeddings": 256,
+}
+TINY = {"A0": (TINY_A0, 0, 0.0, 0.02), "B0": (TINY_B0, 1, 0.01, 0.02), "A": (TINY_A, 0, 0.0), "B": (TINY_B, 1, 0.01), "C": (TINY_C, 2, 0.02),
         "D": (TINY_D, 3, 0.01), "E": (TINY_E, 4, 0.0), "F": (TINY_F, 5, 0.01)}
 
 # Tolerances, as a fraction of the largest logit magnitude of the comparison.  float32
@@ -67,11 +85,14 @@ TINY = {"A": (TINY_A, 0, 0.0), "B": (TINY_B, 1, 0.01), "C": (TINY_C, 2, 0.02),
 TOL = {"float32": 2e-5, "bfloat16": 2.5e-2}
 
 
-def make_folder(name: str, weight_std: float = 0.08, store_dtype: str = "bfloat16") -> str:
-    """A random model folder for a tiny configuration, in a fresh temporary folder.  The
-    weights are larger than N(0, 0.02) so that logits differ visibly between tokens."""
+def make_folder(name: str, weight_std: float = None, store_dtype: str = "bfloat16") -> str:
+    """A random model folder for a tiny configuration, in a fresh temporary folder.  Unless
+    the configuration states its own, the weights are N(0, 0.08): larger than N(0, 0.02), so
+    that logits differ visibly between tokens."""
     from minfer_b200.model import write_random_model
-    cfg, seed, norm_std = TINY[name]
+    cfg, seed, norm_std, *own_std = TINY[name]
+    if weight_std is None:
+        weight_std = own_std[0] if own_std else 0.08
     folder = tempfile.mkdtemp(prefix=f"minfer_b200_tiny{name}_")
     write_random_model(folder, cfg, seed, store_dtype, norm_std=norm_std, weight_std=weight_std)
     return folder
@@ -109,3 +130,48 @@ def logits_err(got: torch.Tensor, want: torch.Tensor, dtype: str) -> tuple:
     if dtype == "float32":
         return rel_err(got, want), TOL["float32"]
     return row_rms_err(got, want), ROW_RMS_TOL
+
+
+def _draw_interval(P, logits, temp, top_k, top_p, tok):
+    """[lo, hi) of the uniform numbers for which the plain sampler draws ``tok`` from these
+    (penalised) logits, or None if it never does."""
+    import math
+    x = P.apply_top_p(P.apply_top_k(logits, top_k), top_p) * (1.0 / temp)
+    probs = torch.exp(x - x.max())
+    probs[x == -math.inf] = 0.0
+    probs = probs / probs.sum()
+    if float(probs[tok]) <= 0.0:
+        return None
+    lo = float(probs[:tok].sum())
+    return lo, lo + float(probs[tok])
+
+
+def follows_plain(P, cfg, w, prompt, tokens, dtype, *, temp=0.0, top_k=0, top_p=1.0, repeat=1.0,
+                  frequency=0.0, presence=0.0, seed=0, stream=0) -> None:
+    """Holds generated ``tokens`` to the plain implementation token by token, each on the
+    prefix the engine itself produced (so one rounding difference does not fail all later
+    tokens).  float32: the token is the plain sampler's.  bfloat16: logits are off by up to
+    TOL of the largest one, so the token must be the plain sampler's for the same uniform
+    number, or one that rounding can tip the choice to: greedy, a token within twice the
+    tolerance of the maximum; sampled, a token whose range of uniform numbers in the plain
+    cumulative distribution (with or without the top-k/top-p cut, which rounding can move by
+    one token) comes within 0.05 of the number drawn."""
+    ids = list(prompt)
+    recent = list(prompt[-64:])
+    for n, tok in enumerate(tokens):
+        logits = P.forward(cfg, w, ids)[-1]
+        r = P.philox_uniform(seed, n, stream)
+        want = P.sample(logits, temp, top_k, top_p, repeat, frequency, presence, recent, r)
+        if tok != want:
+            assert dtype == "bfloat16", (n, tok, want)
+            x = P.apply_penalties(logits, recent, repeat, frequency, presence)
+            if temp < 1e-6:
+                slack = 2 * TOL["bfloat16"] * float(logits.abs().max())
+                assert float(x[tok]) >= float(x.max()) - slack, (n, tok, want)
+            else:
+                spans = [_draw_interval(P, x, temp, top_k, top_p, tok),
+                         _draw_interval(P, x, temp, 0, 1.0, tok)]
+                assert any(sp is not None and sp[0] - 0.05 <= r <= sp[1] + 0.05 for sp in spans), \
+                    (n, tok, want, r, spans)
+        ids.append(tok)
+        recent = (recent + [tok])[-64:]

@@ -42,7 +42,7 @@ def load_folder(folder: str, dtype: torch.dtype = DT) -> Tuple[dict, Dict[str, t
 # ---------------------------------------------------------------------------------------
 def embed(ids: Sequence[int], table: torch.Tensor) -> torch.Tensor:
     """h[t] = E[ids[t]]  (src/graph/cpu_backend.rs:249-291, src/models/qwen2/graph.rs:54)."""
-    return table[torch.tensor(list(ids), dtype=torch.long)]
+    return table[torch.tensor(list(ids), dtype=torch.long, device=table.device)]
 
 
 def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
@@ -69,7 +69,8 @@ def rope_neox(x: torch.Tensor, positions: Sequence[int], theta: float,
     i = torch.arange(half, dtype=DT)
     freqs = freq_scale / torch.pow(torch.tensor(theta, dtype=DT), 2.0 * i / hd)
     ang = torch.tensor(list(positions), dtype=DT)[:, None] * freqs[None, :]     # [T, half]
-    cos, sin = torch.cos(ang)[:, None, :].to(x.dtype), torch.sin(ang)[:, None, :].to(x.dtype)
+    cos = torch.cos(ang)[:, None, :].to(device=x.device, dtype=x.dtype)
+    sin = torch.sin(ang)[:, None, :].to(device=x.device, dtype=x.dtype)
     x0, x1 = x[..., :half], x[..., half:]
     return torch.cat([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1)
 

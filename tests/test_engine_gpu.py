@@ -284,3 +284,69 @@ def test_rows_that_start_beside_rows_that_go_on(tiny_cuts, dtype):
     for s in (a, b, c, d):
         eng.release(s)
     eng.check_status()
+
+
+# ---- what a step refuses ---------------------------------------------------------------------
+def test_step_refusals():
+    """Every refusal of ``Engine.step`` and ``decode_on_device`` is an error before anything is
+    launched or written: the slot's length, its pages and the status word stay as they were."""
+    from minfer_b200.cache.paged import CacheError, OutOfPages
+    from minfer_b200.engine.step import Engine, StepError
+    from minfer_b200.model import Model
+    folder = make_folder("B")
+    cfg = TINY["B"][0]
+    eng = Engine(Model.from_folder(folder, "float32", "cuda:0"), max_tokens=256, max_seqs=3)
+    a, b = eng.acquire(), eng.acquire()
+    free_before = eng.cache.free_pages()
+    with pytest.raises(StepError, match="at least one sequence"):
+        eng.step([], [])
+    with pytest.raises(StepError, match="one entry per sequence"):
+        eng.step([a, b], [[1, 2]])
+    with pytest.raises(StepError, match="one entry per sequence"):
+        eng.step([a], [[1, 2]], [[0], [1]])
+    with pytest.raises(StepError, match="appears twice"):
+        eng.step([a, a], [[1], [2]])
+    with pytest.raises(StepError, match="at least one token"):
+        eng.step([a, b], [[1], []])
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        eng.step([a], [[1, cfg["vocab_size"]]])
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        eng.step([a], [[-1]])
+    with pytest.raises(StepError, match="wanted place"):
+        eng.step([a], [[1, 2, 3]], [[3]])
+    with pytest.raises(StepError, match="wanted place"):
+        eng.step([a], [[1, 2, 3]], [[-1]])
+    with pytest.raises(StepError, match="max_position_embeddings"):
+        eng.step([a], [[1] * (cfg["max_position_embeddings"] + 1)])
+    with pytest.raises(CacheError, match="not held"):
+        eng.step([2], [[1]])                                  # a slot nobody acquired
+    with pytest.raises(CacheError, match="out of range"):
+        eng.step([7], [[1]])
+    assert eng.length(a) == 0 and eng.length(b) == 0 and eng.steps_run == 0
+    assert eng.cache.free_pages() == free_before
+    with pytest.raises(OutOfPages):                           # 300 tokens into a cache of 256
+        eng.step([a], [[1] * 300])
+    assert eng.length(a) == 0
+    # decode_on_device: int32 device tokens, one per row, onto sequences that have a prompt
+    tok = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(StepError, match="this slot is empty"):
+        eng.decode_on_device([b], tok)
+    with pytest.raises(StepError, match="int32 token ids"):
+        eng.decode_on_device([b], tok.long())
+    with pytest.raises(StepError, match="int32 token ids"):
+        eng.decode_on_device([b], torch.zeros(2, dtype=torch.int32, device="cuda"))
+    eng.release(a)
+    a = eng.acquire()
+    eng.step([a], [[5, 6, 7]])
+    with pytest.raises(StepError, match="appears twice"):
+        eng.decode_on_device([a, a], torch.zeros(2, dtype=torch.int32, device="cuda"))
+    eng.check_status()
+    # a token id that only the device sees (the sampler's output fed back) is outside the
+    # vocabulary: the embedding kernel writes zeros for it and sets bit 1 of the status word;
+    # nothing faults, and check_status raises and clears the word
+    eng.decode_on_device([a], torch.tensor([cfg["vocab_size"] + 3], dtype=torch.int32, device="cuda"))
+    with pytest.raises(StepError, match="token id outside the vocabulary"):
+        eng.check_status()
+    eng.check_status()
+    with pytest.raises(CacheError, match="not held"):
+        eng.release(b), eng.release(b)

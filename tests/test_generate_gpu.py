@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import plain_qwen2 as P
-from helpers import TINY, make_folder, random_ids
+from helpers import TINY, follows_plain, make_folder, random_ids
 
 pytestmark = pytest.mark.gpu
 
@@ -78,6 +78,55 @@ def test_sampled_generation_equals_plain_and_ignores_the_batch(tiny, params):
     gen2 = _generator(tiny["folder"], max_batch=2)
     again = [r.tokens for r in gen2.generate(prompts, 12, sp, stop_token_ids=[])]
     assert again == got
+
+
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("params", [
+    dict(temperature=0.0, top_k=0, top_p=1.0, repeat_penalty=1.0),
+    dict(temperature=0.8, top_k=40, top_p=0.95, repeat_penalty=1.1),
+])
+def test_bfloat16_generation_follows_plain(name, params):
+    """The bfloat16 engine (tensor-core products and attention, graphs, the pipelined loop)
+    generates what the plain implementation generates, token by token on the engine's own
+    prefix, up to what bfloat16 rounding can tip (``helpers.follows_plain``); and the same
+    requests in another batch composition follow it too.  In bfloat16 the two compositions
+    need not give the same bits: the tensor-core product picks its token tile and its K
+    splits from the number of rows, which changes the order of the sums."""
+    from minfer_b200.sampling.params import SamplingParams
+    folder = make_folder(name)
+    cfg, w = P.load_folder(folder)
+    prompts = [random_ids(n, cfg["vocab_size"], 60 + n) for n in (1, 7, 20, 33, 70)]
+    sp = SamplingParams(seed=11, **params)
+    for max_batch in (5, 2):
+        gen = _generator(folder, "bfloat16", max_batch=max_batch)
+        got = gen.generate(prompts, 10, sp, stop_token_ids=[])
+        for i, (p, r) in enumerate(zip(prompts, got)):
+            assert len(r.tokens) == 10
+            follows_plain(P, cfg, w, p, r.tokens, "bfloat16", temp=sp.temperature, top_k=sp.top_k,
+                          top_p=sp.top_p, repeat=sp.repeat_penalty, seed=11, stream=i)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_loop_with_the_host_in_step_equals_the_pipelined_loop(tiny, dtype):
+    """``Generator(pipelined=False)`` reads every step's tokens before it launches the next
+    (``run_batch``); the default keeps the host one step behind (``run_batch_pipelined``).
+    The same tokens and finish reasons, stop tokens and early ends included."""
+    from minfer_b200.engine.generate import Generator
+    from minfer_b200.model import Model
+    from minfer_b200.sampling.params import SamplingParams
+    cfg, w = tiny["cfg"], tiny["w"]
+    prompts = [random_ids(n, cfg["vocab_size"], 20 + n) for n in (3, 12, 1, 40, 9)]
+    model = Model.from_folder(tiny["folder"], dtype, "cuda:0")
+    sp = SamplingParams(seed=3, temperature=0.9, top_k=20, top_p=0.9, repeat_penalty=1.2)
+    free = Generator(model, max_tokens=2048, max_batch=3).generate(prompts, 14, sp, stop_token_ids=[])
+    stop = [free[1].tokens[5], free[3].tokens[2]]
+    outs = []
+    for pipelined in (True, False):
+        gen = Generator(model, max_tokens=2048, max_batch=3, pipelined=pipelined)
+        outs.append([(r.tokens, r.finish_reason) for r in gen.generate(prompts, 14, sp, stop_token_ids=stop)])
+        assert gen.engine.cache.slots.n_free() == gen.engine.max_seqs
+    assert outs[0] == outs[1]
+    assert any(reason == "stop" for _, reason in outs[0])
 
 
 def test_sampling_kernel_alone():
