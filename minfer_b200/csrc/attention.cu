@@ -941,7 +941,7 @@ static int launch_decode_mma(const AttnArgs& a, cudaStream_t stream) {
     // chunks of several blocks carry more state in registers: two CTAs per SM
     if (a.chunk > 256) return launch_decode_mma_as<HD, 2, true>(a, stream);
     const long long ctas = (long long)a.n_chunks * a.n_kv * a.rows;
-    return ctas > 2 * 296 ? launch_decode_mma_as<HD, 3, false>(a, stream)
+    return ctas > 4 * mf_sm_count() ? launch_decode_mma_as<HD, 3, false>(a, stream)
                           : launch_decode_mma_as<HD, 2, false>(a, stream);
 }
 

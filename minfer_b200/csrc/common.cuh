@@ -128,6 +128,19 @@ static inline void mf_launch_ex(bool early, void (*kernel)(KArgs...), dim3 grid,
     cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// SMs of the current device (asked once per device); launchers size grids from it
+static inline int mf_sm_count() {
+    static int sms[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (sms[dev] == 0) {
+        int n = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        sms[dev] = n < 2 ? 2 : n;
+    }
+    return sms[dev];
+}
+
 template <typename... KArgs, typename... Args>
 static inline void mf_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                              cudaStream_t stream, Args&&... args) {

@@ -652,16 +652,7 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmA
     return MF_LAUNCH_CHECK();
 }
 
-static int sm_count() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms < 2) sms = 2;
-    }
-    return sms;
-}
+static int sm_count() { return mf_sm_count(); }
 
 // The token tile of the CTA-pair kernel: the one whose tiles fill the fewest, shortest rounds
 // over the pairs (14 weight tiles x 8 token tiles of 256 are 112 tiles for 74 pairs: the second
@@ -702,7 +693,7 @@ extern "C" int mf_gemm_tc_plan(int M, int N, int K, int epi, int* token_tile, in
         // (64 sequences, 24 layers): 1.50 -> 1.35 ms a step; 4 k-blocks a CTA 1.37-1.39,
         // at most 8 splits 1.39-1.47; a ring twice as deep for grids of at most one CTA an
         // SM gained nothing without the cut and lost 0.08 ms with it.
-        s = 296 / tiles;
+        s = 2 * sm_count() / tiles;
         if (s > kblocks / 2) s = kblocks / 2;
         if (s > 16) s = 16;
         if (s < 1) s = 1;
@@ -710,7 +701,7 @@ extern "C" int mf_gemm_tc_plan(int M, int N, int K, int epi, int* token_tile, in
         // up to two CTAs per SM (the small-token kernels are sized for that), each with at
         // least 4 k-blocks; the partial sums (written and read once) stay under half of the
         // weight bytes: splits * M * N * 8 <= N * K  =>  splits <= K / (8 M)
-        const int slots = nt <= 64 ? 296 : 148;
+        const int slots = nt <= 64 ? 2 * sm_count() : sm_count();
         s = slots / tiles;
         if (s > kblocks / 4) s = kblocks / 4;
         if (s > K / (8 * M)) s = K / (8 * M);
@@ -792,8 +783,8 @@ extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long
     }
     const long long total = (long long)M * N;
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads
-                                                                       : 148 * 8);
+    const long long cap = (long long)sm_count() * 8;
+    const int blocks = (int)((total + threads - 1) / threads < cap ? (total + threads - 1) / threads : cap);
     if (out_dtype == MF_DTYPE_F32)
         mf_launch(splitk_reduce_kernel<float>, dim3(blocks), dim3(threads), 0, stream, 
             workspace, bias, (float*)out, ldo, M, N, splits, epi == EPI_ACCUM);
@@ -813,8 +804,8 @@ extern "C" int mf_splitk_reduce(const float* partial, int splits, const float* b
     if (accumulate && out_dtype != MF_DTYPE_F32) return MF_ERR_UNSUPPORTED;
     const long long total = (long long)M * N;
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 8 ? (total + threads - 1) / threads
-                                                                       : 148 * 8);
+    const long long cap = (long long)sm_count() * 8;
+    const int blocks = (int)((total + threads - 1) / threads < cap ? (total + threads - 1) / threads : cap);
     if (out_dtype == MF_DTYPE_F32)
         mf_launch(splitk_reduce_kernel<float>, dim3(blocks), dim3(threads), 0, stream, partial, bias, (float*)out, ldo, M,
                                                                     N, splits, accumulate);

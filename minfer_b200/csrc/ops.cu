@@ -641,8 +641,8 @@ extern "C" int mf_swiglu(const void* gu, int in_dtype, void* out, int out_dtype,
     const long long total = (long long)n_rows * nf;
     if (total <= 0) return 0;
     const int threads = 256;
-    const int blocks = (int)((total + threads - 1) / threads < 148 * 16
-                                 ? (total + threads - 1) / threads : 148 * 16);
+    const long long cap = (long long)mf_sm_count() * 16;
+    const int blocks = (int)((total + threads - 1) / threads < cap ? (total + threads - 1) / threads : cap);
 #define MF_SWIGLU(TI, TO) \
     mf_launch(swiglu_kernel<TI, TO>, dim3(blocks), dim3(threads), 0, stream, (const TI*)gu, (TO*)out, nf, total, \
                                                           interleaved)
@@ -689,7 +689,8 @@ extern "C" int mf_cast(const void* in, int in_dtype, void* out, int out_dtype, l
     if (n <= 0) return 0;
     const int threads = 256;
     const long long want = (n + threads - 1) / threads;
-    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    const long long cap = (long long)mf_sm_count() * 16;
+    const int blocks = (int)(want < cap ? want : cap);
     if (in_dtype == MF_DTYPE_F32 && out_dtype == MF_DTYPE_BF16)
         mf_launch(cast_kernel<float, __nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, 
             (const float*)in, (__nv_bfloat16*)out, n);

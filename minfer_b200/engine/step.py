@@ -96,22 +96,32 @@ class Engine:
             for req in model.blocks[call.layer].mixer.state_request():
                 tensors[req.name] = self.cache.state.add(f"call{i}.{req.name}", req.shape, req.dtype)
             self._call_state.append(tensors)
-        from ..kernels import build, gemm
-        # what this model's steps will load, compiled side by side if it is not built yet
-        if self.dtype == torch.bfloat16:
-            build.prebuild(["ops", "gemm_tc", "attention", "attention_prefill_tc"])
-        else:
-            build.prebuild(["ops", "gemm_simt", "attention"])
-        self.status = gemm.status_word(self.device)       # one word for every kernel's error bits
+        from ..kernels import build
+        # every part of the model, asked of the blocks themselves
+        parts = [model.final_norm]
+        for block in model.blocks:
+            parts.append(block)
+            parts.extend(block.parts())
+        # what this model's steps will load, compiled side by side if it is not built yet: the
+        # engine's own kernels (embedding, row selection, the head's product) and the parts'
+        libs = ["ops", "gemm_tc" if self.dtype == torch.bfloat16 else "gemm_simt"]
+        for p in parts:
+            for name in p.libraries(self.dtype):
+                if name not in libs:
+                    libs.append(name)
+        build.prebuild(libs)
+        # one word for the error bits of this engine's kernels, read back without waiting: after
+        # every step it is copied to pinned host memory, and the next step (or check_status)
+        # raises if a copy that has arrived shows a bit
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._status_event = torch.cuda.Event()
+        self._status_in_flight = False
         self._graphs: Dict[tuple, dict] = {}
         self._seen_shapes: set = set()
         # a part that reads device memory on the host, or changes state outside its kernels,
         # cannot be captured: every part has to declare itself capturable
-        parts = [model.final_norm]
-        for block in model.blocks:
-            parts += [block, block.mixer, getattr(block, "feed_forward", None),
-                      getattr(block, "mixer_norm", None), getattr(block, "feed_forward_norm", None)]
-        if not all(getattr(p, "capturable", False) for p in parts if p is not None):
+        if not all(getattr(p, "capturable", False) for p in parts):
             self.cuda_graphs = False
         self._graph_pool = None
         self.steps_run = 0
@@ -135,6 +145,7 @@ class Engine:
         places among them whose logits are asked for (default: the last).  Returns float32
         logits ``[wanted, vocab]`` in the order of the rows and of ``want``."""
         plan = self.model.plan
+        self._raise_if_flagged()
         n_rows = len(slots)
         if n_rows == 0:
             raise StepError("a step needs at least one sequence")
@@ -170,6 +181,7 @@ class Engine:
         else:
             logits = self._step_once(slots, tokens, want, counts, starts)
         self.steps_run += 1
+        self._post_status()
         return logits
 
     def _step_once(self, slots, tokens, want, counts, starts) -> torch.Tensor:
@@ -225,6 +237,7 @@ class Engine:
         another without the host waiting.  Out-of-range ids set the status word.  With CUDA
         graphs the returned logits live in the graph's own memory and are overwritten by the
         next step of the same shape."""
+        self._raise_if_flagged()
         n_rows = len(slots)
         if tokens.dtype != torch.int32 or tokens.numel() != n_rows or not tokens.is_cuda:
             raise StepError("decode_on_device takes int32 token ids on the device, one per row")
@@ -248,6 +261,7 @@ class Engine:
         for b in range(n_rows):
             self.cache.set_length(slots[b], starts[b] + 1)
         self.steps_run += 1
+        self._post_status()
         return logits
 
     # ---- metadata -----------------------------------------------------------------------
@@ -412,7 +426,9 @@ class Engine:
 
     # ---- the model ------------------------------------------------------------------------
     def _run(self, ctx: StepContext, want_rows: Optional[torch.Tensor]) -> torch.Tensor:
+        from ..kernels import gemm
         model, plan = self.model, self.model.plan
+        gemm.use_status_word(self.status)           # this engine's products report into its word
         h = torch.empty((ctx.n_tokens, plan.hidden_size), dtype=torch.float32, device=self.device)
         K.embed(model.embedding, ctx.token_ids, h, self.status)
         bindings = self._bindings(ctx)
@@ -444,16 +460,41 @@ class Engine:
             x = model.final_norm.forward(h, self.dtype)
         return model.head.forward(x, torch.float32)
 
+    # ---- the status word ----------------------------------------------------------------------
+    def _post_status(self) -> None:
+        """Sends the status word on its way to the host behind the step just launched."""
+        if self._status_in_flight and not self._status_event.query():
+            return                                   # the last copy is still under way
+        self._status_host.copy_(self.status, non_blocking=True)
+        self._status_event.record()
+        self._status_in_flight = True
+
+    def _raise_if_flagged(self) -> None:
+        """Raises if a copy of the status word that has arrived shows an error bit (no wait)."""
+        if self._status_in_flight and self._status_event.query():
+            self._status_in_flight = False
+            if int(self._status_host[0]) != 0:
+                self.check_status()
+
     def check_status(self) -> None:
-        """Raises if a kernel flagged a bad token or position (reads the device: a sync)."""
+        """Raises if a kernel of this engine flagged a bad token or position or gave up a
+        bounded wait (reads the device: a sync).  ``step`` and ``decode_on_device`` look at
+        the word themselves without waiting, so an error surfaces at the latest one call after
+        the step it belongs to has finished; callers that must know now call this."""
         bits = int(self.status.item())
+        self._status_in_flight = False
         if bits:
             self.status.zero_()
-            what = []
-            if bits & 1:
-                what.append("a token id outside the vocabulary")
-            if bits & 2:
-                what.append("a position outside its sequence's pages")
-            if bits & 4:
-                what.append("a bounded wait on a barrier ran out")
-            raise StepError("a kernel reported: " + ", ".join(what or [f"status {bits}"]))
+            raise StepError("a kernel reported: " + ", ".join(status_bits(bits)))
+
+
+def status_bits(bits: int) -> List[str]:
+    """What the bits of a status word say (the meanings of ``MF_STATUS_*`` in csrc/common.cuh)."""
+    what = []
+    if bits & 1:
+        what.append("a token id outside the vocabulary")
+    if bits & 2:
+        what.append("a position outside its sequence's pages")
+    if bits & 4:
+        what.append("a bounded wait on a barrier ran out")
+    return what or [f"status {bits}"]

@@ -10,14 +10,27 @@ import torch
 from . import api as K
 
 _status: dict = {}
+_current: dict = {}
 
 
 def status_word(device: torch.device) -> torch.Tensor:
-    """A device word the tensor-core kernels set bits in when a bounded wait runs out."""
+    """The device word the tensor-core kernels set bits in when a bounded wait runs out: the
+    word of the engine whose step is running on ``device`` (``use_status_word``), else one
+    word per device for products launched outside any engine."""
     key = str(device)
+    word = _current.get(key)
+    if word is not None:
+        return word
     if key not in _status:
         _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _status[key]
+
+
+def use_status_word(word) -> None:
+    """Products launched on the word's device from now on report into ``word`` (an engine
+    calls this at the start of each of its steps); ``None`` has no effect."""
+    if word is not None:
+        _current[str(word.device)] = word
 
 
 _USE_TENSOR_CORES = os.environ.get("MINFER_B200_NO_TCGEN05", "0") != "1"     # read once

@@ -27,7 +27,20 @@ from .base import CacheRequest, CallBinding, Mixer, StepContext, settle_pending
 from .linear import Linear
 
 DECODE_CHUNK = 256     # keys per block when attending over the cache
-DECODE_CTAS = int(os.environ.get("MINFER_B200_DECODE_CTAS", "296"))   # CTAs the decode kernel wants in flight: two on each of 148 SMs
+_DECODE_CTAS = os.environ.get("MINFER_B200_DECODE_CTAS")
+_decode_ctas_of: Dict[int, int] = {}
+
+
+def decode_ctas(device: Optional[torch.device] = None) -> int:
+    """CTAs the decode kernel wants in flight: two on each SM of the device."""
+    if _DECODE_CTAS:
+        return int(_DECODE_CTAS)
+    index = torch.cuda.current_device() if device is None or device.index is None else device.index
+    if index not in _decode_ctas_of:
+        _decode_ctas_of[index] = 2 * torch.cuda.get_device_properties(index).multi_processor_count
+    return _decode_ctas_of[index]
+
+
 FORCE_GENERIC_ATTENTION = os.environ.get("MINFER_B200_GENERIC_ATTENTION", "0") == "1"
 # a step that is neither whole prompts nor one token a row runs the tcgen05 kernel over the
 # cache's pages from this many tokens on; below, every token is a row of the decode kernel
@@ -37,7 +50,8 @@ PAGED_PROMPT_MIN_TOKENS = int(os.environ.get("MINFER_B200_PAGED_PROMPT_MIN_TOKEN
 PROMPT_ATTENTION = os.environ.get("MINFER_B200_PROMPT_ATTENTION", "tcgen05")
 
 
-def decode_chunks(items: int, max_end: int, tensor_cores: bool = True) -> tuple:
+def decode_chunks(items: int, max_end: int, tensor_cores: bool = True,
+                  ctas: Optional[int] = None) -> tuple:
     """How attention over the cache cuts the keys: (keys per chunk, chunks).  A chunk is a
     CTA's work and a multiple of 256 keys.  The tensor-core kernel is fastest when the CTAs of
     all ``items`` (rows x key/value heads) fill the GPU about once, two to an SM: with few
@@ -45,15 +59,27 @@ def decode_chunks(items: int, max_end: int, tensor_cores: bool = True) -> tuple:
     positions: 36.7 us with 4 blocks a CTA against 46.0 with one; at 32,000: 108 against
     157 us), and fewer chunks are left to merge."""
     blocks = max(1, -(-max_end // DECODE_CHUNK))
-    if not tensor_cores or items * blocks <= DECODE_CTAS * 3 // 2:
+    if not tensor_cores:
+        return DECODE_CHUNK, blocks
+    if ctas is None:
+        ctas = decode_ctas()
+    if items * blocks <= ctas * 3 // 2:
         return DECODE_CHUNK, blocks                    # one block a CTA: up to three CTAs on an SM
-    n_chunks = max(1, min(blocks, DECODE_CTAS // max(items, 1)))
+    n_chunks = max(1, min(blocks, ctas // max(items, 1)))
     per = -(-blocks // n_chunks)
     return per * DECODE_CHUNK, -(-blocks // per)
 
 
 class Attention(Mixer):
     capturable = True      # launches kernels only; safe inside a CUDA graph capture
+
+    def libraries(self, dtype: torch.dtype) -> List[str]:
+        libs = ["ops", "attention"]
+        if dtype == torch.bfloat16:
+            libs += ["gemm_tc", "attention_prefill_tc"]
+        else:
+            libs.append("gemm_simt")
+        return libs
 
     def __init__(self, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  scale: float, window: int = 0, qkv_bias: bool = True, out_bias: bool = False,

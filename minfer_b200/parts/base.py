@@ -126,6 +126,11 @@ class Part:
 
     capturable = False
 
+    def libraries(self, dtype: torch.dtype) -> List[str]:
+        """Names of the kernel libraries this part launches from when the engine runs in
+        ``dtype``; the engine compiles them side by side before the first step."""
+        return []
+
     def tensor_specs(self, prefix: str) -> List[TensorSpec]:
         return []
 
@@ -182,6 +187,11 @@ class FeedForward(Part):
 
 class Block(Part):
     mixer: Mixer
+
+    def parts(self) -> Sequence[Part]:
+        """Every part this block runs, whatever it calls them; the engine asks each whether it
+        can be captured into a CUDA graph and which kernel libraries it needs."""
+        raise NotImplementedError
 
     def mix(self, h: torch.Tensor, ctx: StepContext, binding: CallBinding) -> None:
         raise NotImplementedError

@@ -21,22 +21,22 @@ class PreNormBlock(Block):
         self.feed_forward_norm = build_part("norm", layer.feed_forward_norm)
         self.feed_forward = build_part("feed_forward", layer.feed_forward)
 
-    def _parts(self):
+    def parts(self):
         return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
 
     def tensor_specs(self, prefix: str = "") -> List:
         specs = []
-        for part in self._parts():
+        for part in self.parts():
             specs += part.tensor_specs(self.prefix)
         return specs
 
     def load(self, prefix: str, weights: Dict[str, torch.Tensor]) -> None:
-        for part in self._parts():
+        for part in self.parts():
             part.load(self.prefix, weights)
 
     def export(self, prefix: str = "") -> Dict[str, torch.Tensor]:
         out: Dict[str, torch.Tensor] = {}
-        for part in self._parts():
+        for part in self.parts():
             out.update(part.export(self.prefix))
         return out
 

@@ -21,6 +21,9 @@ from .linear import Linear
 class GatedMlp(FeedForward):
     capturable = True      # launches kernels only; safe inside a CUDA graph capture
 
+    def libraries(self, dtype: torch.dtype) -> List[str]:
+        return ["ops", "gemm_tc"] if dtype == torch.bfloat16 else ["ops", "gemm_simt"]
+
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
                  init_std: float = 0.02):
         if activation != "silu":

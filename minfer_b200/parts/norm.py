@@ -14,6 +14,9 @@ from .base import Norm
 class RmsNorm(Norm):
     capturable = True      # launches kernels only; safe inside a CUDA graph capture
 
+    def libraries(self, dtype: torch.dtype) -> List[str]:
+        return ["ops"]
+
     def __init__(self, size: int, eps: float, name: str = "norm", init_std: float = 0.0):
         self.size = int(size)
         self.eps = float(eps)

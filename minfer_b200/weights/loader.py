@@ -14,6 +14,8 @@ Integer tables become int32.
 """
 from __future__ import annotations
 
+import sys
+
 from typing import Iterable, Mapping, Sequence
 
 import torch
@@ -97,9 +99,21 @@ def load_weights(folder: str, specs: Sequence[TensorSpec], engine_dtype: torch.d
         found = {n: (ck.entry(n).shape, ck.entry(n).dtype) for n in ck.names()}
         check_against(specs, found, folder, ignorable)
         out: dict[str, torch.Tensor] = {}
+        wide = []
         for spec in specs:
             t = ck.tensor(spec.name)
-            out[spec.name] = t.to(held_dtype(spec, t.dtype, engine_dtype)).to(device).contiguous()
+            held = held_dtype(spec, t.dtype, engine_dtype)
+            if (engine_dtype == torch.bfloat16 and held == torch.float32
+                    and spec.role not in (VECTOR, INT_TABLE)):
+                wide.append(spec.name)
+            out[spec.name] = t.to(held).to(device).contiguous()
+        if wide:
+            # kept as stored, as the rule says, but the user should know what it costs
+            print(f"[minfer_b200] {len(wide)} matrices of {folder} are stored in 32-bit and stay "
+                  f"float32 in the bfloat16 engine: their products run on the FP32 pipe (about "
+                  f"40 times slower) and take twice the memory; store them in bfloat16 to use "
+                  f"the tensor cores ({', '.join(wide[:3])}{', ...' if len(wide) > 3 else ''})",
+                  file=sys.stderr, flush=True)
         return out
     finally:
         ck.close()

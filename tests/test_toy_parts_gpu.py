@@ -339,3 +339,125 @@ def test_toy_routed_feed_forward_and_a_layer_that_runs_twice():
     for b in range(2):
         assert rel_err(torch.cat(got[b]), want[b]) < 2e-5, b
     eng.check_status()
+
+
+# ---------------------------------------------------------------------------------------------
+# A toy block kind with members of other names than the shipped block's: ONE norm used before
+# the mixer and again before the feed-forward.  The engine learns its parts from ``parts()``:
+# decode steps are replayed as graphs only if every one of them says it can be captured, and
+# the libraries to build come from the parts too.
+# ---------------------------------------------------------------------------------------------
+def _register_shared_norm_block():
+    from minfer_b200 import registry
+    from minfer_b200.config.base import ConfigReader, LayerSpec, ModelPlan, PartSpec, default_schedule
+    from minfer_b200.parts.base import Block
+    from minfer_b200.registry import build_part
+
+    class SharedNormBlock(Block):
+        capturable = True
+
+        def __init__(self, layer):
+            self.prefix = layer.prefix
+            self.pre = build_part("norm", layer.mixer_norm)
+            self.mixer = build_part("mixer", layer.mixer)
+            self.ff = build_part("feed_forward", layer.feed_forward)
+
+        def parts(self):
+            return (self.pre, self.mixer, self.ff)
+
+        def tensor_specs(self, prefix=""):
+            return [s for part in self.parts() for s in part.tensor_specs(self.prefix)]
+
+        def load(self, prefix, weights):
+            for part in self.parts():
+                part.load(self.prefix, weights)
+
+        def mix(self, h, ctx, binding):
+            self.mixer.forward_add(self.pre.forward(h, ctx.act_dtype), ctx, binding, h)
+
+        def feed(self, h, ctx):
+            self.ff.forward_add(self.pre.forward(h, ctx.act_dtype), ctx, h)
+
+    class SharedNormConfig:
+        def __init__(self, d):
+            r = ConfigReader(d)
+            self.vocab, self.width, self.layers = r.integer("vocab"), r.integer("width"), r.integer("layers")
+            self.ff = r.string("ff")
+
+        def plan(self):
+            norm = PartSpec("rms_norm", {"size": self.width, "eps": 1e-5, "name": "n"})
+            mixer = PartSpec("attention", dict(
+                hidden_size=self.width, n_heads=2, n_kv_heads=1, head_dim=16, scale=0.25, window=0,
+                qkv_bias=True, position=PartSpec("rotary", dict(head_dim=16, rotary_dim=16, theta=100.0))))
+            ffn = (PartSpec("gated_mlp", dict(hidden_size=self.width, intermediate_size=24))
+                   if self.ff == "gated" else PartSpec("toy_square", dict(width=self.width, inner=24)))
+            layers = [LayerSpec(f"s.{l}.", PartSpec("toy_shared_norm", {}), mixer, norm, ffn, norm)
+                      for l in range(self.layers)]
+            return ModelPlan("ToySharedNormLM", self.vocab, self.width, "s.embed", None,
+                             norm.with_params(name="final"), "s.", layers,
+                             default_schedule(self.layers), 512, ())
+
+    _register()                                                       # toy_square
+    registry.register_part("block", "toy_shared_norm", SharedNormBlock, replace=True)
+    registry.register_architecture("ToySharedNormLM", lambda d, where: SharedNormConfig(d), replace=True)
+
+
+def _shared_norm_reference(w, ids):
+    def norm(x, wt):
+        return x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5) * wt
+    T = len(ids)
+    h = w["s.embed"][torch.tensor(ids)]
+    ang = torch.arange(T, dtype=torch.float64)[:, None] * (100.0 ** (-torch.arange(0, 16, 2, dtype=torch.float64) / 16))[None, :]
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+    def rope(x):
+        a, b = x[..., :8], x[..., 8:]
+        return torch.cat([a * cos - b * sin, a * sin + b * cos], -1)
+    for l in range(2):
+        p, a = f"s.{l}.", f"s.{l}.self_attn."
+        x = norm(h, w[p + "n.weight"])
+        q = rope((x @ w[a + "q_proj.weight"].t() + w[a + "q_proj.bias"]).reshape(T, 2, 16))
+        k = rope((x @ w[a + "k_proj.weight"].t() + w[a + "k_proj.bias"]).reshape(T, 1, 16))
+        v = (x @ w[a + "v_proj.weight"].t() + w[a + "v_proj.bias"]).reshape(T, 1, 16)
+        o = torch.zeros(T, 2, 16, dtype=torch.float64)
+        for hh in range(2):
+            sc = (q[:, hh] @ k[:, 0].t()) * 0.25
+            sc = sc.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf"))
+            o[:, hh] = torch.softmax(sc, -1) @ v[:, 0]
+        h = h + o.reshape(T, 32) @ w[a + "o_proj.weight"].t()
+        x = norm(h, w[p + "n.weight"])
+        g, u = x @ w[p + "mlp.gate_proj.weight"].t(), x @ w[p + "mlp.up_proj.weight"].t()
+        h = h + (torch.nn.functional.silu(g) * u) @ w[p + "mlp.down_proj.weight"].t()
+    return norm(h, w["s.final.weight"]) @ w["s.embed"].t()
+
+
+def test_toy_block_with_other_member_names_gets_the_capture_check():
+    _register_shared_norm_block()
+    from minfer_b200.engine.step import Engine
+    from minfer_b200.model import Model
+    from minfer_b200.registry import read_config
+    from minfer_b200.weights.random_init import write_model_folder
+    from minfer_b200.weights.safetensors_io import load_all
+    engines = {}
+    for ff in ("gated", "square"):
+        config = {"architectures": ["ToySharedNormLM"], "vocab": 53, "width": 32, "layers": 2, "ff": ff}
+        with tempfile.TemporaryDirectory() as folder:
+            json.dump(config, open(os.path.join(folder, "config.json"), "w"))
+            cfg = read_config(config)
+            write_model_folder(folder, config, Model(cfg.plan(), "float32", cfg).tensor_specs(), 3, "float32")
+            w = {k: v.double() for k, v in load_all(folder).items()}
+            engines[ff] = (Engine(Model.from_folder(folder, "float32", "cuda:0"), 512, max_seqs=2), w)
+    # every part of the first model launches kernels only: graphs; the second one's feed-forward
+    # (plain tensor code, ``capturable`` left False) switches them off for its engine
+    assert engines["gated"][0].cuda_graphs is True
+    assert engines["square"][0].cuda_graphs is False
+    eng, w = engines["gated"]
+    ids = random_ids(60, 53, 8)
+    want = _shared_norm_reference(w, ids)
+    s = eng.acquire()
+    rows = [eng.step([s], [ids[:20]], [list(range(20))]),             # whole, a portion, then one by one
+            eng.step([s], [ids[20:45]], [list(range(25))])]
+    rows += [eng.step([s], [[t]]) for t in ids[45:]]
+    assert len(eng._graphs) >= 1
+    assert rel_err(torch.cat(rows), want) < 2e-5
+    eng.check_status()
