@@ -54,6 +54,32 @@ def ring_positions(window: int, step_tokens: int = 1) -> int:
     return pages_for(window + max(1, int(step_tokens)) - 1) * PAGE
 
 
+GUARD_BYTES = 256
+GUARD_VALUE = 0xA5
+
+
+class Guarded:
+    """Device storage with a guard of 256 bytes before and after it.  The host writes a fixed
+    value into the guards when the storage is made and reads them back on request: a kernel
+    that wrote past either end of the tensor has changed them.  Costs nothing in a step."""
+
+    def __init__(self, shape: Sequence[int], dtype: torch.dtype, device: torch.device | str,
+                 what: str):
+        n_bytes = int(np.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+        self.what = what
+        self.raw = torch.empty(n_bytes + 2 * GUARD_BYTES, dtype=torch.uint8, device=device)
+        self.raw[:GUARD_BYTES] = GUARD_VALUE
+        self.raw[GUARD_BYTES + n_bytes:] = GUARD_VALUE
+        body = self.raw[GUARD_BYTES:GUARD_BYTES + n_bytes]
+        body.zero_()
+        self.tensor = body.view(dtype).view(*shape)
+
+    def intact(self) -> bool:
+        n = self.raw.numel()
+        ends = torch.cat([self.raw[:GUARD_BYTES], self.raw[n - GUARD_BYTES:]])
+        return bool((ends == GUARD_VALUE).all().item())
+
+
 class SlotTable:
     """Hands out slot numbers; a slot is held by at most one sequence at a time."""
 
@@ -153,8 +179,10 @@ class CacheGroup:
         shape = (len(self.entries), n_pages + 1, key.n_kv_heads, PAGE, key.head_dim)
         # zeros, once: a page's unwritten positions are masked by length but still multiplied
         # by a zero weight in the tensor-core kernels, so they must never hold NaN or Inf
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self._guarded = [Guarded(shape, dtype, device, f"keys of cache group {key}"),
+                         Guarded(shape, dtype, device, f"values of cache group {key}")]
+        self.k = self._guarded[0].tensor
+        self.v = self._guarded[1].tensor
         self._index = {e: i for i, e in enumerate(self.entries)}
 
     def max_new_positions(self) -> Optional[int]:
@@ -225,13 +253,15 @@ class StatePool:
         self.n_slots = n_slots
         self.device = device
         self.tensors: Dict[str, torch.Tensor] = {}
+        self._guarded: List[Guarded] = []
 
     def add(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
         if name in self.tensors:
             raise CacheError(f"state '{name}' is already defined")
-        t = torch.zeros((self.n_slots, *shape), dtype=dtype, device=self.device)
-        self.tensors[name] = t
-        return t
+        g = Guarded((self.n_slots, *shape), dtype, self.device, f"state '{name}'")
+        self._guarded.append(g)
+        self.tensors[name] = g.tensor
+        return g.tensor
 
     def reset(self, slot: int) -> None:
         for t in self.tensors.values():
@@ -304,6 +334,14 @@ class Cache:
         bound): the smallest bound of the groups."""
         bounds = [b for b in (g.max_new_positions() for g in self.groups) if b is not None]
         return min(bounds) if bounds else None
+
+    def check_canaries(self) -> None:
+        """Raises if a guard before or after a group's keys or values or a state tensor no longer
+        holds the value the host wrote there (reads the device: a sync; for tests and audits)."""
+        broken = [g.what for group in self.groups for g in group._guarded if not g.intact()]
+        broken += [g.what for g in self.state._guarded if not g.intact()]
+        if broken:
+            raise CacheError("something wrote outside " + "; ".join(broken))
 
     def bytes(self) -> int:
         """Bytes of key/value storage that sequences can hold (the spare pages not counted)."""

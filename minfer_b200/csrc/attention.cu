@@ -505,18 +505,43 @@ __global__ void __launch_bounds__(DEC_WARPS * 32, MINB) attention_decode_mma_ker
     }
 }
 
+#define MF_MAX_DEVICES 64
+
+// The kernel's dynamic shared memory is opened once per device (a function attribute belongs
+// to the device that is current when it is set).
+template <int HD, int MINB, bool LOOP>
+static int configure_decode_mma() {
+    constexpr int smem = DEC_WARPS * 16 * (HD + 8) * 4 + DEC_WARPS * 16 * 3 * 4 + 16 * 4;
+    static bool configured[MF_MAX_DEVICES] = {false};
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= MF_MAX_DEVICES) return MF_ERR_UNSUPPORTED;
+    if (!configured[device]) {
+        e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, MINB, LOOP>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured[device] = true;
+    }
+    return 0;
+}
+
+// every variant mf_attention_paged may pick without a status word, for the current device
+static int configure_decode_mma_all() {
+    if (int e = configure_decode_mma<64, 2, false>()) return e;
+    if (int e = configure_decode_mma<64, 3, false>()) return e;
+    if (int e = configure_decode_mma<64, 2, true>()) return e;
+    if (int e = configure_decode_mma<128, 2, false>()) return e;
+    if (int e = configure_decode_mma<128, 3, false>()) return e;
+    return configure_decode_mma<128, 2, true>();
+}
+
 template <int HD, int MINB, bool LOOP>
 static int launch_decode_mma_as(const AttnArgs& a, cudaStream_t stream) {
     constexpr int smem = DEC_WARPS * 16 * (HD + 8) * 4 + DEC_WARPS * 16 * 3 * 4 + 16 * 4;
     static_assert(DEC_WARPS * DEC_KEYS * HD * 2 <= DEC_WARPS * 16 * (HD + 8) * 4, "values fit the staging area");
     static_assert(DEC_WARPS * DEC_KEYS == 256, "a CTA walks its chunk in blocks of 256 keys");
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, MINB, LOOP>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    if (int e = configure_decode_mma<HD, MINB, LOOP>()) return e;
     dim3 grid(a.n_chunks, a.n_kv, a.rows);
     mf_launch(attention_decode_mma_kernel<HD, MINB, LOOP>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, a);
     return MF_LAUNCH_CHECK();
@@ -945,6 +970,13 @@ static int launch_decode_mma(const AttnArgs& a, cudaStream_t stream) {
                           : launch_decode_mma_as<HD, 2, false>(a, stream);
 }
 
+// MINFER_B200_DECODE_RING=0 keeps the kernel whose warps load their own keys (read once)
+static int decode_ring_mode() {
+    static int mode = -1;
+    if (mode < 0) { const char* ev = getenv("MINFER_B200_DECODE_RING"); mode = ev ? atoi(ev) : 1; }
+    return mode;
+}
+
 static int check_sizes(int n_heads, int n_kv, int hd) {
     if (hd <= 0 || hd % 16 != 0 || hd > ATT_MAX_HD) return MF_ERR_UNSUPPORTED;
     if (n_kv <= 0 || n_heads <= 0 || n_heads % n_kv != 0) return MF_ERR_UNSUPPORTED;
@@ -1009,8 +1041,7 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
         // bounded waits; without them, or with MINFER_B200_DECODE_RING=0, the kernel whose warps
         // load their own keys runs (measured, 64 sequences at 2,048 positions: 44.5 against
         // 60.7 us; 8 at 8,192: 30.4 against 37.4; equal on chunks of a single block)
-        static int ring_mode = -1;
-        if (ring_mode < 0) { const char* ev = getenv("MINFER_B200_DECODE_RING"); ring_mode = ev ? atoi(ev) : 1; }
+        const int ring_mode = decode_ring_mode();
         int e;
         if (ring_mode && cache_pages > 0 && status != nullptr) {
             const long long cache_rows = cache_pages * n_kv * MF_PAGE;
@@ -1061,8 +1092,7 @@ extern "C" int mf_attention_paged(const void* q, const void* k_cache, const void
 
 static __device__ __align__(256) float mf_noalloc_scratch[MF_ATTENTION_NOALLOC_FLOATS];
 
-#define MF_NOALLOC_MAX_DEVICES 64
-static float* noalloc_scratch_of_device[MF_NOALLOC_MAX_DEVICES];
+static float* noalloc_scratch_of_device[MF_MAX_DEVICES];
 
 extern "C" long long mf_attention_noalloc_capacity(void) {
     return (long long)MF_ATTENTION_NOALLOC_FLOATS;
@@ -1075,18 +1105,31 @@ extern "C" int mf_attention_paged_noalloc(const void* q, const void* k_cache, co
                                           int window, int chunk, int n_chunks, float scale,
                                           int dtype, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (n_heads <= 0 || n_chunks < 1 || hd <= 0) return MF_ERR_ARGUMENT;
-    const long long need = (long long)rows * n_heads * n_chunks * (hd + 2);
-    if (need > (long long)MF_ATTENTION_NOALLOC_FLOATS) return MF_ERR_SCRATCH_LIMIT;
+    if (n_chunks < 1) return MF_ERR_ARGUMENT;
+    if (int bad = check_sizes(n_heads, n_kv, hd)) return bad;
+    // every factor is checked against the array before it is multiplied in: no overflow
+    const long long cap = (long long)MF_ATTENTION_NOALLOC_FLOATS;
+    long long need = (long long)hd + 2;
+    const int factors[3] = {rows, n_heads, n_chunks};
+    for (int f : factors) {
+        if ((long long)f > cap) return MF_ERR_SCRATCH_LIMIT;
+        need *= f;
+        if (need > cap) return MF_ERR_SCRATCH_LIMIT;
+    }
     int device = -1;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return (int)e;
-    if (device < 0 || device >= MF_NOALLOC_MAX_DEVICES) return MF_ERR_UNSUPPORTED;
+    if (device < 0 || device >= MF_MAX_DEVICES) return MF_ERR_UNSUPPORTED;
     if (noalloc_scratch_of_device[device] == nullptr) {
-        // set-up, once per device, with that device current
+        // set-up, once per device, with that device current: the array's address, the shared
+        // memory of every kernel variant a later call may pick, and the environment switch.
+        // (Two host threads that make their first calls at once both do this and store the
+        // same values: harmless.)
         float* address = nullptr;
         e = cudaGetSymbolAddress((void**)&address, mf_noalloc_scratch);
         if (e != cudaSuccess) return (int)e;
+        if (int bad = configure_decode_mma_all()) return bad;
+        (void)decode_ring_mode();
         noalloc_scratch_of_device[device] = address;
     }
     return mf_attention_paged(q, k_cache, v_cache, row_seq, row_pos, page_table, table_stride, ring,

@@ -3,11 +3,10 @@
 // This entry point has no counterpart in yusiwen/minfer; it exists for users of this
 // library's C interface.
 //
-// Who needs it: code that runs where cudaMalloc is off limits.  Examples are a caller in
-// the middle of a CUDA-graph capture or inside a real-time loop that may not block on the
-// allocator, a plug-in that lives inside a host application which owns all device memory and
-// hands out none, and a process that has pinned its memory budget and treats any later
-// allocation as a fault.  mf_attention_paged needs float32 scratch to merge the key chunks
+// Who needs it: code that runs where cudaMalloc is off limits.  Examples are a real-time
+// loop that may not block on the allocator, a plug-in that lives inside a host application
+// which owns all device memory and hands out none, and a process that has pinned its memory
+// budget and treats any later allocation as a fault.  mf_attention_paged needs float32 scratch to merge the key chunks
 // of a long sequence, and its callers normally allocate that scratch themselves; here the
 // scratch is a fixed array that is part of the loaded library image instead.
 //
@@ -16,9 +15,12 @@
 //     which the library is loaded keeps that much memory until the process exits.
 //   * A call needs rows * n_heads * n_chunks * (head_dim + 2) floats.  A call that needs more
 //     is refused with MF_ERR_SCRATCH_LIMIT (2005) before anything is launched.
-//   * The first call on each device looks up the array's device address
-//     (cudaGetSymbolAddress, with that device current) and remembers it.  Make that first
-//     call before any stream capture begins; later calls only launch kernels.
+//   * The first call on each device does the set-up for that device, with that device
+//     current: it looks up the array's device address (cudaGetSymbolAddress), opens the
+//     shared memory of every kernel variant a later call may pick (cudaFuncSetAttribute) and
+//     reads the environment.  Make that first call before any stream capture begins.  Two host
+//     threads that make their first calls on a device at the same moment both do the set-up
+//     and store the same values, which is harmless.
 //   * It calls no cudaMalloc, no cudaFree and no routine of an allocating library.
 //   * All calls share the one array, and the array keeps what the last call left in it.
 //     Nothing in it has to start at zero: the kernels write every entry they later read.

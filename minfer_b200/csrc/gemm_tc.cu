@@ -79,15 +79,17 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 // (bounded both by a number of tries and by wall time: a try may itself block for a while)
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t max_spin = MAX_SPIN,
+                                          unsigned long long max_wait_ns = MAX_WAIT_NS) {
     unsigned long long t0 = 0;
-    for (uint32_t it = 0; it < MAX_SPIN; ++it) {
+    for (uint32_t it = 0; it < max_spin; ++it) {
         if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
         if ((it & 1023u) == 1023u) {
             const unsigned long long now = global_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > MAX_WAIT_NS) break;
+            else if (now - t0 > max_wait_ns) break;
         }
     }
     *abort_flag = 1;
@@ -336,6 +338,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
                      ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
     }
+}
+
+// What a wait that runs out does, shown without a product around it: one thread waits, with
+// the limits it is given, on a barrier that nothing ever arrives at (no copy in flight, no
+// tensor memory held).  The wait gives up, the kernel sets MF_STATUS_WAIT_TIMEOUT in the
+// status word as the product kernels do, and returns; the context stays usable.
+__global__ void wait_probe_kernel(unsigned* status, uint32_t max_spin, unsigned long long max_wait_ns,
+                                  unsigned long long* waited_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const unsigned long long t0 = global_ns();
+        const bool ok = mbar_wait(smem_u32(&bar), 0u, &abort_flag, max_spin, max_wait_ns);
+        if (waited_ns) *waited_ns = global_ns() - t0;
+        if (!ok) atomicOr(status, MF_STATUS_WAIT_TIMEOUT);
+    }
+}
+
+extern "C" int mf_wait_probe(unsigned* status, unsigned max_spin, unsigned long long max_wait_ns,
+                             unsigned long long* waited_ns, cudaStream_t stream) {
+    if (status == nullptr) return MF_ERR_ARGUMENT;
+    // the probe may never wait longer than a product kernel would
+    if (max_spin > MAX_SPIN) max_spin = MAX_SPIN;
+    if (max_wait_ns > MAX_WAIT_NS) max_wait_ns = MAX_WAIT_NS;
+    wait_probe_kernel<<<1, 32, 0, stream>>>(status, max_spin, max_wait_ns, waited_ns);
+    return MF_LAUNCH_CHECK();
 }
 
 // adds the K splits in order: out (+)= sum_s partial[s] + bias

@@ -33,12 +33,39 @@ class GenerationResult:
 
 @dataclass
 class GenerationStats:
+    """Counts and times of ``generate`` calls.  ``*_seconds`` is the host's clock around each
+    step (what a caller waits for); ``*_device_seconds`` is the time between events recorded
+    on the device's stream (before the prompts' step, after the first tokens are sampled, after
+    the batch's last step), where the engine offers such marks.  The reference prints the same
+    two calibres from host timers (src/main.rs:552-609)."""
+
     prefill_tokens: int = 0
     prefill_seconds: float = 0.0
     decode_tokens: int = 0
     decode_seconds: float = 0.0
     batches: int = 0
     steps: int = 0
+    prefill_device_seconds: float = 0.0
+    decode_device_seconds: float = 0.0
+
+
+class _DeviceClock:
+    """Three marks on the engine's stream per batch, if the engine has ``time_mark`` and
+    ``seconds_between`` (the mock engines of the loop's tests have not)."""
+
+    def __init__(self, engine: Any):
+        self.mark = getattr(engine, "time_mark", None)
+        self.between = getattr(engine, "seconds_between", None)
+        self.marks: List[Any] = []
+
+    def tick(self) -> None:
+        if self.mark is not None and self.between is not None:
+            self.marks.append(self.mark())
+
+    def add_to(self, stats: GenerationStats) -> None:
+        if len(self.marks) == 3:
+            stats.prefill_device_seconds += self.between(self.marks[0], self.marks[1])
+            stats.decode_device_seconds += self.between(self.marks[1], self.marks[2])
 
 
 def plan_batches(prompt_lengths: Sequence[int], max_new_tokens: int, max_batch: int,
@@ -78,6 +105,8 @@ def run_batch(engine: Any, sampler: Any, prompts: Sequence[Sequence[int]], strea
     try:
         sampler.begin(slots, prompts)
         live = list(range(n))
+        clock = _DeviceClock(engine)
+        clock.tick()
         t0 = time.perf_counter()
         logits = engine.step([slots[i] for i in live], [list(prompts[i]) for i in live])
         first = True
@@ -85,6 +114,7 @@ def run_batch(engine: Any, sampler: Any, prompts: Sequence[Sequence[int]], strea
             tokens = sampler.sample(logits, [slots[i] for i in live], [streams[i] for i in live])
             now = time.perf_counter()
             if first:
+                clock.tick()
                 stats.prefill_tokens += sum(len(prompts[i]) for i in live)
                 stats.prefill_seconds += now - t0
                 first = False
@@ -112,6 +142,8 @@ def run_batch(engine: Any, sampler: Any, prompts: Sequence[Sequence[int]], strea
             live = still
             if live:
                 logits = engine.step([slots[i] for i in live], feed)
+        clock.tick()
+        clock.add_to(stats)
     finally:
         for s in slots:
             engine.release(s)
@@ -142,10 +174,13 @@ def run_batch_pipelined(engine: Any, sampler: Any, prompts: Sequence[Sequence[in
     slots = [engine.acquire() for _ in range(n)]
     try:
         sampler.begin(slots, prompts)
+        clock = _DeviceClock(engine)
+        clock.tick()
         t0 = time.perf_counter()
         logits = engine.step(list(slots), [list(p) for p in prompts])
         cur = list(range(n))                       # sequences in the order of `tokens`
         tokens = sampler.sample_on_device(logits, slots, list(streams))
+        clock.tick()
         fetch = sampler.fetch(tokens)
         drawn = [1] * n                            # tokens drawn so far (the last may be unread)
         stopped = [False] * n
@@ -190,6 +225,8 @@ def run_batch_pipelined(engine: Any, sampler: Any, prompts: Sequence[Sequence[in
             for i in nxt:
                 drawn[i] += 1
             cur, tokens, fetch = nxt, next_tokens, next_fetch
+        clock.tick()
+        clock.add_to(stats)
     finally:
         for s in slots:
             engine.release(s)

@@ -460,6 +460,18 @@ class Engine:
             x = model.final_norm.forward(h, self.dtype)
         return model.head.forward(x, torch.float32)
 
+    # ---- marks on the stream, for device times -------------------------------------------------
+    def time_mark(self) -> torch.cuda.Event:
+        """An event recorded now on the current stream."""
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        return ev
+
+    def seconds_between(self, first: torch.cuda.Event, second: torch.cuda.Event) -> float:
+        """Device time between two marks (waits for the second to have happened)."""
+        second.synchronize()
+        return first.elapsed_time(second) * 1e-3
+
     # ---- the status word ----------------------------------------------------------------------
     def _post_status(self) -> None:
         """Sends the status word on its way to the host behind the step just launched."""

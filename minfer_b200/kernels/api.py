@@ -136,6 +136,7 @@ def _sig_gemm_tc(lib: ctypes.CDLL) -> None:
     lib.mf_gemm_tc_workspace_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mf_gemm_tc_workspace_floats.restype = c_longlong
     lib.mf_gemm_tc_plan.argtypes = [c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+    lib.mf_wait_probe.argtypes = [c_void_p, ctypes.c_uint, c_ulonglong, c_void_p, c_void_p]
 
 
 def _sig_attention_prefill(lib: ctypes.CDLL) -> None:
@@ -371,6 +372,19 @@ def gemm_tc_partial_sums(x: torch.Tensor, w: torch.Tensor,
     if splits.value < 1:
         raise KernelError("gemm_tc: a split product reported no splits")
     return ws[:splits.value * m * n].view(splits.value, m, n)
+
+
+def wait_probe(status: torch.Tensor, max_tries: int, max_wait_ns: int,
+               waited_ns: Optional[torch.Tensor] = None) -> None:
+    """Runs the product kernels' bounded barrier wait on a barrier that nothing arrives at,
+    with the given limits (never above the kernels' own).  The wait runs out, bit 4 of
+    ``status`` is set and the kernel returns; ``waited_ns`` (int64 [1]) receives how long the
+    wait lasted.  Nothing faults and nothing is left in flight."""
+    if waited_ns is not None and (waited_ns.dtype != torch.int64 or not waited_ns.is_cuda):
+        raise KernelError("wait_probe: waited_ns must be an int64 tensor on the device")
+    _check(_lib("gemm_tc").mf_wait_probe(_i32(status, "status"), int(max_tries), int(max_wait_ns),
+                                         None if waited_ns is None else waited_ns.data_ptr(),
+                                         _stream()), "wait_probe")
 
 
 def splitk_reduce(partial: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,

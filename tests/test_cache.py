@@ -118,3 +118,24 @@ def test_state_is_zeroed_when_a_slot_is_handed_out():
     s2 = c.acquire()
     assert s2 == s and float(t[s2].abs().sum()) == 0.0
     assert c.state.bytes_per_slot() == 12
+
+
+def test_guards_around_storage():
+    """The bytes before and after a tensor hold a fixed value; changing one is seen."""
+    import torch
+    from minfer_b200.cache.paged import Cache, CacheError, GroupKey, Guarded
+    g = Guarded((3, 5), torch.float32, "cpu", "a test tensor")
+    assert g.tensor.shape == (3, 5) and float(g.tensor.abs().sum()) == 0.0
+    g.tensor.fill_(7.0)                                 # writing the tensor itself is fine
+    assert g.intact()
+    g.raw[255] = 0
+    assert not g.intact()
+    cache = Cache({0: GroupKey(2, 16, 0), 1: GroupKey(2, 16, 40)}, 256, 2, torch.float32, "cpu")
+    cache.state.add("x", (4,), torch.int32)
+    cache.check_canaries()
+    cache.groups[1]._guarded[0].raw[-1] = 1
+    try:
+        cache.check_canaries()
+        raise AssertionError("a changed guard was not seen")
+    except CacheError as e:
+        assert "keys of cache group" in str(e)

@@ -93,6 +93,7 @@ def test_unequal_batches_slots_reused(tiny, dtype):
     assert set(seen_slots[1]) & set(seen_slots[0]), "the second batch did not reuse a slot"
     assert all(n == eng.cache.groups[i].n_pages for i, n in enumerate(eng.cache.free_pages()))
     eng.check_status()
+    eng.cache.check_canaries()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -255,6 +256,7 @@ def test_short_rings_run_long_portions_in_passes(tiny_cuts, dtype):
         assert _close(got, want, dtype), (tiny_cuts["name"], len(ids))
     assert all(n == eng.cache.groups[i].n_pages for i, n in enumerate(eng.cache.free_pages()))
     eng.check_status()
+    eng.cache.check_canaries()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -284,6 +286,7 @@ def test_rows_that_start_beside_rows_that_go_on(tiny_cuts, dtype):
     for s in (a, b, c, d):
         eng.release(s)
     eng.check_status()
+    eng.cache.check_canaries()
 
 
 # ---- what a step refuses ---------------------------------------------------------------------

@@ -3,9 +3,9 @@
 equal the ordinary entry point's, on two calls in a row that share the fixed scratch array,
 and a request beyond the array's size must be refused.
 
-Such callers exist where cudaMalloc is not allowed: inside a stream capture, inside a host
-application that owns all device memory, or under a fixed memory budget.  This file is
-named so that it is collected last."""
+Such callers exist where cudaMalloc is not allowed: in a real-time loop that may not block
+on the allocator, inside a host application that owns all device memory, or under a fixed
+memory budget.  This file is named so that it is collected last."""
 import ctypes
 import math
 
@@ -91,6 +91,12 @@ def test_no_alloc_entry_point_refuses_more_than_its_array_holds():
     too_many_chunks = (4 << 20) // (28 * 130) + 1
     rc = _call_noalloc(lib, q, kc, vc, row_seq, row_pos, table, width, out, 28, 4, 128,
                        too_many_chunks, K.BF16)
+    assert rc == 2005
+    # sizes whose product would not fit 64 bits are refused the same way, not multiplied out
+    fn = lib.mf_attention_paged_noalloc
+    rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), row_seq.data_ptr(), row_pos.data_ptr(),
+            table.data_ptr(), width, 0, out.data_ptr(), 2 ** 31 - 1, 2 ** 31 - 4, 4, 128, 0, 256,
+            6000, 0.1, K.BF16, torch.cuda.current_stream().cuda_stream)
     assert rc == 2005
     torch.cuda.synchronize()
     assert float(out.float().abs().sum()) == 0.0          # nothing was launched
