@@ -16,6 +16,16 @@
 // Work that does not fill the GPU is split along K: each split writes float32 partial sums
 // that mf_splitk_reduce adds in split order (no atomics, so results are reproducible).
 //
+// A norm between two products need not be a kernel of its own.  The product that completes the
+// residual stream (EPI_ACCUM with `prep_x` set) also writes, for the norm that reads it next,
+// x' = bfloat16(h * g) (g: that norm's weight) and, per group of output columns, the sum of h^2
+// of every token (`prep_ssq`).  The product that follows takes x' as its token operand and
+// multiplies token t's accumulators by 1 / sqrt(sum_parts ssq[.][t] / width + eps) in its
+// epilogue (`row_ssq`): the same numbers as norm, then product, up to the place of one
+// rounding.  Few tokens: the product that completes the residual is split along K over a
+// CLUSTER of CTAs, which add their partial tiles in rank order through distributed shared
+// memory (no atomics: reproducible), each finishing 128 / splits columns.
+//
 // Every wait on an mbarrier is bounded: when it runs out the kernel sets
 // MF_STATUS_WAIT_TIMEOUT in the status word, stops issuing work, lets its copies land,
 // frees its tensor memory and returns.
@@ -49,7 +59,40 @@ struct GemmArgs {
     int kblocks_per_split;
     int epi;
     int out_dtype;
+    // this product's token rows are x' = h * g of a norm whose 1/rms is still to be applied:
+    // scale[t] = rsqrt(sum_{p < ssq_parts} row_ssq[p * M + t] / ssq_width + ssq_eps); null = none
+    const float* row_ssq;
+    int ssq_parts, ssq_width;
+    float ssq_eps;
+    // EPI_ACCUM only, null = none: after out[t][n] += acc, prep_x[t][n] = bfloat16(out[t][n] * prep_g[n])
+    // and prep_ssq[part][t] = sum over the part's columns of out[t][n]^2
+    __nv_bfloat16* prep_x;
+    const float* prep_g;
+    float* prep_ssq;
+    long long ldp;            // elements between consecutive tokens of prep_x
 };
+
+// 1 / rms of the token rows [m0, m0 + n_tok) into `out` (shared memory), by one warp: every lane
+// adds the parts p = lane, lane + 32, .. of up to 16 tokens at a time (all loads in flight
+// together), then the lanes' sums are added in a fixed order.
+__device__ __forceinline__ void row_scales_by_warp(const GemmArgs& a, int m0, int n_tok, float* out, int lane) {
+    for (int t0 = 0; t0 < n_tok; t0 += 16) {
+        float acc[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+        for (int p = lane; p < a.ssq_parts; p += 32) {
+            const float* row = a.row_ssq + (size_t)p * a.M + m0 + t0;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (t0 + j < n_tok && m0 + t0 + j < a.M) acc[j] += row[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const float sum = warp_sum(acc[j]);
+            if (lane == 0 && t0 + j < n_tok) out[t0 + j] = rsqrtf(sum / (float)a.ssq_width + a.ssq_eps);
+        }
+    }
+}
 
 // ---- PTX wrappers --------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -153,8 +196,14 @@ __host__ __device__ constexpr uint32_t umma_idesc(int nt) {
 }
 
 // One chunk of the epilogue: this thread's 16 consecutive tokens (tok0 ..) of output row n.
-__device__ __forceinline__ void store_chunk(const GemmArgs& a, const uint32_t* r, int n, bool n_ok,
-                                            float bias, int tok0, int lane, int split) {
+// `scale` (may be null): 1 / rms of these 16 tokens, applied to the accumulators first.
+__device__ __forceinline__ void store_chunk(const GemmArgs& a, const uint32_t* r_in, int n, bool n_ok,
+                                            float bias, int tok0, int lane, int split,
+                                            const float* scale = nullptr) {
+    uint32_t r[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+        r[j] = scale ? __float_as_uint(__uint_as_float(r_in[j]) * scale[j]) : r_in[j];
     if (a.epi == EPI_SWIGLU) {
         // Lanes come in pairs: the even lane holds the gate row, the odd lane the up row of the
         // same output column, both for these 16 tokens.  They swap halves (one shuffle per two
@@ -217,6 +266,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);   // full[S], empty[S], acc
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* scale_s = (float*)(tmem_slot + 2);        // [NT] 1 / rms of this tile's tokens
 
     pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -284,6 +334,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else {
         pdl_wait();          // every other thread: nothing below may run ahead of the kernel before
     }
+    // the tokens' 1 / rms, by the two warps that have nothing to do while the weights stream
+    if (a.row_ssq != nullptr && warp >= 2)
+        row_scales_by_warp(a, m0 + (warp - 2) * (NT / 2), NT / 2, scale_s + (warp - 2) * (NT / 2), lane);
     if (warp == 1 && lane == 0) {
         // ---- MMA issuer --------------------------------------------------------------
         constexpr uint32_t idesc = umma_idesc(NT);
@@ -309,6 +362,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     __syncwarp();
 
     // ---- epilogue: all four warps, warp w owns TMEM lanes 32w..32w+31 -------------------
+    if (a.row_ssq != nullptr) __syncthreads();           // the scales are in shared memory
     const bool acc_ok = mbar_wait(smem_u32(&bars[2 * STAGES]), 0u, abort_flag);
     tc_fence_after();
     if (acc_ok) {
@@ -321,7 +375,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             uint32_t r[16];
             tc_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
             tc_wait_ld();
-            store_chunk(a, r, n, n_ok, bias, m0 + c0, lane, split);
+            store_chunk(a, r, n, n_ok, bias, m0 + c0, lane, split,
+                        a.row_ssq != nullptr ? scale_s + c0 : nullptr);
         }
     }
     tc_fence_before();
@@ -330,6 +385,226 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (tid == 0) {
             atomicOr(a.status, MF_STATUS_WAIT_TIMEOUT);
             // give copies that are still in flight time to land before the memory is reused
+            for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                     ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Few tokens, the product that completes the residual stream (out += x W^T): split along K
+// over a CLUSTER of CSPLIT CTAs (grid z = cluster z), whose partial tiles never leave the
+// chip.  Main loop as in gemm_tc_kernel.  Then, by distributed shared memory:
+//   1. every CTA's accumulator is complete and its operand ring idle: cluster barrier
+//   2. CTA r sends, for each of the CSPLIT column groups (128 / CSPLIT columns each), its
+//      partial sums of that group to the CTA that owns the group (rank = group), into that
+//      CTA's idle ring: cluster barrier
+//   3. every CTA adds the CSPLIT partial sums of its group in rank order (reproducible), adds
+//      them (and the bias) into `out`, and, if asked, writes the next norm's x' = h * g and the
+//      sums of h^2 of its columns (see the head of this file).
+// No partial sums in global memory, no kernel to add them, and the norm that follows is left
+// with a scale that the next product applies.
+// ------------------------------------------------------------------------------------------
+#define CSPLIT 8
+#define CGROUP (TILE_N / CSPLIT)          // columns a CTA finishes
+
+__device__ __forceinline__ uint32_t rank_in_cluster() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
+                 ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int NT, int STAGES>
+__global__ void __launch_bounds__(128)
+gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                       const GemmArgs a) {
+    constexpr int B_BYTES = NT * TILE_K * 2;
+    constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int TMEM_COLS = TmemCols<NT>::value;
+    static_assert(CSPLIT * CGROUP * NT * 4 <= STAGES * STAGE_BYTES, "the partial sums fit the idle ring");
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);   // full[S], empty[S], acc
+    uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* scale_s = (float*)(tmem_slot + 2);        // [NT] 1 / rms of this tile's tokens
+
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.x * NT;
+    const int n0 = blockIdx.y * TILE_N;
+    const uint32_t rank = rank_in_cluster();         // = blockIdx.z: the K split
+    const int kblocks = (a.K + TILE_K - 1) / TILE_K;
+    const int kb0 = (int)rank * a.kblocks_per_split;
+    const int kb1 = min(kblocks, kb0 + a.kblocks_per_split);
+    const int n_iter = max(0, kb1 - kb0);
+
+    if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bars[s]), 1);
+            mbar_init(smem_u32(&bars[STAGES + s]), 1);
+        }
+        mbar_init(smem_u32(&bars[2 * STAGES]), 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---- TMA producer (weights first: they are constant over the step) --------------------
+        const int pre = n_iter < STAGES ? n_iter : STAGES;
+        for (int i = 0; i < pre; ++i) {
+            const uint32_t full = smem_u32(&bars[i]);
+            mbar_expect_tx(full, STAGE_BYTES);
+            tma_load_2d(smem_u32(smem + i * STAGE_BYTES), &map_w, (kb0 + i) * TILE_K, n0, full);
+        }
+        if (n_iter <= STAGES + 2)
+            for (int i = pre; i < n_iter; ++i)
+                asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                             ::"l"(&map_w), "r"((kb0 + i) * TILE_K), "r"(n0) : "memory");
+        pdl_wait();
+        for (int i = 0; i < pre; ++i)
+            tma_load_2d(smem_u32(smem + i * STAGE_BYTES) + A_BYTES, &map_x, (kb0 + i) * TILE_K, m0,
+                        smem_u32(&bars[i]));
+        for (int i = pre; i < n_iter; ++i) {
+            const int s = i % STAGES;
+            const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+            if (!mbar_wait(smem_u32(&bars[STAGES + s]), ph ^ 1u, abort_flag)) break;
+            const uint32_t full = smem_u32(&bars[s]);
+            mbar_expect_tx(full, STAGE_BYTES);
+            const uint32_t dst = smem_u32(smem + s * STAGE_BYTES);
+            tma_load_2d(dst, &map_w, (kb0 + i) * TILE_K, n0, full);
+            tma_load_2d(dst + A_BYTES, &map_x, (kb0 + i) * TILE_K, m0, full);
+        }
+    } else {
+        pdl_wait();
+    }
+    if (a.row_ssq != nullptr && warp >= 2)
+        row_scales_by_warp(a, m0 + (warp - 2) * (NT / 2), NT / 2, scale_s + (warp - 2) * (NT / 2), lane);
+    if (warp == 1 && lane == 0) {
+        // ---- MMA issuer ---------------------------------------------------------------------
+        constexpr uint32_t idesc = umma_idesc(NT);
+        bool ok = true;
+        for (int i = 0; i < n_iter && ok; ++i) {
+            const int s = i % STAGES;
+            const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+            ok = mbar_wait(smem_u32(&bars[s]), ph, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+            const uint64_t da = umma_desc(sa), db = umma_desc(sa + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < TILE_K / 16; ++k)
+                tc_mma(tmem_base, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
+                       (i > 0 || k > 0) ? 1u : 0u);
+            tc_commit(smem_u32(&bars[STAGES + s]));
+        }
+        if (ok && n_iter > 0) tc_commit(smem_u32(&bars[2 * STAGES]));
+    }
+    __syncwarp();
+
+    // ---- 1. this CTA's accumulator is complete (every MMA has read its operands: the ring is idle)
+    const bool acc_ok = n_iter > 0 ? mbar_wait(smem_u32(&bars[2 * STAGES]), 0u, abort_flag) : true;
+    tc_fence_after();
+    __syncthreads();                                  // also: the scales are in shared memory
+    // Every thread of every CTA of the cluster comes here, whatever happened above (a wait that
+    // ran out only sets the abort flag): the cluster's barriers cannot be left waiting.
+    cluster_barrier();
+
+    // ---- 2. the partial sums go to the owners of their column groups --------------------------
+    // ring of the owner: part[src rank][column of the group][token], float32
+    float* part = (float*)smem;
+    {
+        const int n_local = warp * 32 + lane;         // this thread's accumulator row = column of W
+        const uint32_t owner = (uint32_t)(n_local / CGROUP);
+        const uint32_t dst0 = map_to_rank(smem_u32(part + ((size_t)rank * CGROUP + (n_local % CGROUP)) * NT), owner);
+#pragma unroll 1
+        for (int c0 = 0; c0 < NT; c0 += 16) {
+            if (m0 + c0 >= a.M) break;
+            uint32_t r[16];
+            if (acc_ok && n_iter > 0) {
+                tc_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+                tc_wait_ld();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) r[j] = 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; j += 4)
+                st_cluster_v4(dst0 + (uint32_t)((c0 + j) * 4), __uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                              __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+        }
+    }
+    cluster_barrier();
+
+    // ---- 3. this CTA's column group: sums in rank order, residual, the next norm's input ---------
+    {
+        const int c = tid % CGROUP;                   // column of the group
+        const int tg = tid / CGROUP;                  // tokens tg, tg + 128 / CGROUP, ..
+        constexpr int TSTEP = 128 / CGROUP;
+        const int n = n0 + (int)rank * CGROUP + c;
+        const bool n_ok = n < a.N;
+        const float bias = (a.bias != nullptr && n_ok) ? a.bias[n] : 0.0f;
+        const float g = (a.prep_x != nullptr && n_ok) ? a.prep_g[n] : 0.0f;
+#pragma unroll 1
+        for (int t = tg; t < NT; t += TSTEP) {
+            const int tok = m0 + t;
+            float sq = 0.0f;
+            if (tok < a.M && n_ok) {
+                float v = 0.0f;
+#pragma unroll
+                for (int s = 0; s < CSPLIT; ++s) v += part[((size_t)s * CGROUP + c) * NT + t];
+                if (a.row_ssq != nullptr) v *= scale_s[t];
+                float* o = (float*)a.out + (size_t)tok * a.ldo + n;
+                const float hn = (a.epi == EPI_ACCUM ? *o : 0.0f) + v + bias;
+                *o = hn;
+                if (a.prep_x != nullptr) {
+                    a.prep_x[(size_t)tok * a.ldp + n] = __float2bfloat16_rn(hn * g);
+                    sq = hn * hn;
+                }
+            }
+            if (a.prep_x != nullptr) {
+                // the CGROUP lanes that hold this token's columns are neighbours in the warp
+#pragma unroll
+                for (int o = CGROUP / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+                if (c == 0 && tok < a.M)
+                    a.prep_ssq[((size_t)blockIdx.y * CSPLIT + rank) * a.M + tok] = sq;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (*abort_flag) {
+        if (tid == 0) {
+            atomicOr(a.status, MF_STATUS_WAIT_TIMEOUT);
             for (int i = 0; i < 2000; ++i) __nanosleep(1000);
         }
         __syncthreads();
@@ -454,7 +729,7 @@ static int weight_map(CUtensorMap* out, const void* ptr, int rows, int K, long l
 template <int NT, int STAGES>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a, int splits,
                   cudaStream_t stream) {
-    constexpr int smem = STAGES * (A_BYTES + NT * TILE_K * 2) + 1024 + 256;
+    constexpr int smem = STAGES * (A_BYTES + NT * TILE_K * 2) + 1024 + 256 + NT * 4;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<NT, STAGES>,
@@ -467,6 +742,37 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& 
     return MF_LAUNCH_CHECK();
 }
 
+
+template <int NT, int STAGES>
+static int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
+                          cudaStream_t stream) {
+    constexpr int smem = STAGES * (A_BYTES + NT * TILE_K * 2) + 1024 + 256 + NT * 4;
+    static bool configured[64] = {false};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MF_ERR_UNSUPPORTED;
+    if (!configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_cluster_kernel<NT, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((a.M + NT - 1) / NT, (a.N + TILE_N - 1) / TILE_N, CSPLIT);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = 1;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = CSPLIT;
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = mf_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, gemm_tc_cluster_kernel<NT, STAGES>, mw, mx, a);
+    return MF_LAUNCH_CHECK();
+}
 
 // ------------------------------------------------------------------------------------------
 // Many tokens: a PAIR of CTAs (a cluster of two SMs) works on one 256 x NT tile with
@@ -543,6 +849,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     uint64_t* acc_empty = acc_full + 2;       // [2]       leader's are used
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    float* scale_s = (float*)(tmem_slot + 2);                 // [2][NT] 1 / rms of a tile's tokens
+    float* sq_s = scale_s + 2 * NT;                           // [2][4][NT] sums of squares by warp
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = cluster_ctarank();
@@ -633,13 +941,66 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             const int n = n0 + (int)rank * TILE_N + q * 32 + lane;
             const bool n_ok = n < a.N;
             const float bias = (a.bias != nullptr && n_ok) ? a.bias[n] : 0.0f;
+            float* scale_b = scale_s + b * NT;
+            if (a.row_ssq != nullptr) {
+                // 1 / rms of this tile's tokens: each epilogue warp a quarter of them, into the
+                // buffer of this accumulator (the other one may still be read for the last tile)
+                constexpr int QUARTER = (NT / 4 + 15) / 16 * 16;
+                const int t_lo = q * QUARTER;
+                if (t_lo < NT)
+                    row_scales_by_warp(a, m0 + t_lo, min(QUARTER, NT - t_lo), scale_b + t_lo, lane);
+                asm volatile("bar.sync 1, 128;" ::: "memory");        // the four epilogue warps
+            }
+            if (a.epi == EPI_ACCUM && a.prep_x != nullptr) {
+                // the residual is complete after this product: write it, the next norm's
+                // x' = h * g, and the sums of h^2 over this CTA's 128 columns
+                float* sq_b = sq_s + (b * 4 + q) * NT;
+                const float g = n_ok ? a.prep_g[n] : 0.0f;
 #pragma unroll 1
-            for (int c0 = 0; c0 < NT; c0 += 16) {
-                if (m0 + c0 >= a.M) break;
-                uint32_t r[16];
-                tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * NT + c0), r);
-                tc_wait_ld();
-                store_chunk(a, r, n, n_ok, bias, m0 + c0, lane, 0);
+                for (int c0 = 0; c0 < NT; c0 += 16) {
+                    if (m0 + c0 >= a.M) break;
+                    uint32_t r[16];
+                    tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * NT + c0), r);
+                    tc_wait_ld();
+                    float old[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int tok = m0 + c0 + j;
+                        old[j] = (tok < a.M && n_ok) ? ((const float*)a.out)[(size_t)tok * a.ldo + n] : 0.0f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int tok = m0 + c0 + j;
+                        float sq = 0.0f;
+                        if (tok < a.M && n_ok) {
+                            const float hn = old[j] + __uint_as_float(r[j]) + bias;
+                            ((float*)a.out)[(size_t)tok * a.ldo + n] = hn;
+                            a.prep_x[(size_t)tok * a.ldp + n] = __float2bfloat16_rn(hn * g);
+                            sq = hn * hn;
+                        }
+                        sq = warp_sum(sq);
+                        if (lane == 0) sq_b[c0 + j] = sq;
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                // (this CTA's 128 columns may lie beyond N altogether: then it has no part to write)
+                const int part = (n0 >> 7) + (int)rank;
+                for (int t = (warp - 2) * 32 + lane; t < NT; t += 128) {
+                    if (m0 + t < a.M && n0 + (int)rank * TILE_N < a.N) {
+                        const float* sq0 = sq_s + (size_t)(b * 4) * NT + t;
+                        a.prep_ssq[(size_t)part * a.M + m0 + t] = (sq0[0] + sq0[NT]) + (sq0[2 * NT] + sq0[3 * NT]);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < NT; c0 += 16) {
+                    if (m0 + c0 >= a.M) break;
+                    uint32_t r[16];
+                    tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * NT + c0), r);
+                    tc_wait_ld();
+                    store_chunk(a, r, n, n_ok, bias, m0 + c0, lane, 0,
+                                a.row_ssq != nullptr ? scale_b + c0 : nullptr);
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -666,7 +1027,7 @@ static int sm_count();
 template <int NT, int STAGES>
 static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
                        cudaStream_t stream) {
-    constexpr int smem = STAGES * (A_BYTES + (NT / 2) * TILE_K * 2) + 1024 + 256;
+    constexpr int smem = STAGES * (A_BYTES + (NT / 2) * TILE_K * 2) + 1024 + 256 + 10 * NT * 4;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<NT, STAGES>,
@@ -750,17 +1111,40 @@ extern "C" long long mf_gemm_tc_workspace_floats(int M, int N, int K, int epi) {
     return s > 1 ? (long long)s * M * N : 0;
 }
 
-// out[M][N] (+)= x[M][K] * w[N][K]^T (+ bias).  x, w bfloat16; for EPI_SWIGLU the rows of w
-// alternate gate,up and out is [M][N/2] bfloat16.  `workspace` must hold
-// mf_gemm_tc_workspace_floats floats when that is not zero.
-// `deferred` (may be null): if the product is split along K, the partial sums are LEFT in
-// `workspace` as [splits][M][N], nothing is written to `out`, and *deferred receives the number
-// of splits, so that the caller's next kernel can add them (and the bias) itself; otherwise
-// *deferred is 0 and `out` is complete.
-extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long ldw,
-                          const float* bias, void* out, long long ldo, int out_dtype, int M, int N,
-                          int K, int epi, float* workspace, int* deferred, unsigned* status,
-                          cudaStream_t stream) {
+// What the caller may fold into a product (all null / zero: a plain product).
+struct FusedNorm {
+    const float* row_ssq;     // consumer: sums of squares [ssq_parts][M] of the norm whose x' this product reads
+    int ssq_parts, ssq_width;
+    float ssq_eps;
+    __nv_bfloat16* prep_x;    // producer (EPI_ACCUM): the next norm's x' [M][N] ...
+    long long ldp;
+    const float* prep_g;      // ... its weight [N] ...
+    float* prep_ssq;          // ... and the sums of squares [parts][M] this product writes
+};
+
+static int pair_mode_on() {
+    static int pair_mode = -1;            // MINFER_B200_GEMM_PAIR=0 keeps the one-CTA kernel
+    if (pair_mode < 0) { const char* ev = getenv("MINFER_B200_GEMM_PAIR"); pair_mode = ev ? atoi(ev) : 1; }
+    return pair_mode;
+}
+
+// Number of column groups (`parts`) whose sums of squares a residual-completing product of these
+// sizes writes, or 0 if no kernel folds the next norm in at these sizes (the caller then adds
+// the product in the ordinary way and runs the norm as a kernel).
+extern "C" int mf_gemm_tc_prep_parts(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    int nt, splits;
+    mf_gemm_tc_plan(M, N, K, EPI_ACCUM, &nt, &splits);
+    const int kblocks = (K + TILE_K - 1) / TILE_K;
+    if (pair_mode_on() && M >= 256 && splits == 1) return (N + TILE_N - 1) / TILE_N;
+    if (nt <= 64 && splits > 1 && kblocks >= CSPLIT) return ((N + TILE_N - 1) / TILE_N) * CSPLIT;
+    return 0;
+}
+
+static int gemm_tc_impl(const void* x, long long ldx, const void* w, long long ldw,
+                        const float* bias, void* out, long long ldo, int out_dtype, int M, int N,
+                        int K, int epi, float* workspace, int* deferred, unsigned* status,
+                        const FusedNorm* f, cudaStream_t stream) {
     if (deferred) *deferred = 0;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return MF_ERR_UNSUPPORTED;
@@ -768,33 +1152,45 @@ extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long
     if (epi == EPI_ACCUM && out_dtype != MF_DTYPE_F32) return MF_ERR_UNSUPPORTED;
     if (epi == EPI_SWIGLU && (out_dtype != MF_DTYPE_BF16 || N % 2 != 0)) return MF_ERR_UNSUPPORTED;
     if (epi < EPI_STORE || epi > EPI_SWIGLU) return MF_ERR_ARGUMENT;
+    const bool prep = f != nullptr && f->prep_x != nullptr;
+    if (prep && (epi != EPI_ACCUM || f->prep_g == nullptr || f->prep_ssq == nullptr)) return MF_ERR_ARGUMENT;
+    if (f != nullptr && f->row_ssq != nullptr && (f->ssq_parts <= 0 || f->ssq_width <= 0)) return MF_ERR_ARGUMENT;
+    if (prep && mf_gemm_tc_prep_parts(M, N, K) == 0) return MF_ERR_UNSUPPORTED;
     int nt, splits;
     mf_gemm_tc_plan(M, N, K, epi, &nt, &splits);
-    if (splits > 1 && workspace == nullptr) return MF_ERR_ARGUMENT;
+    if (splits > 1 && workspace == nullptr && !prep) return MF_ERR_ARGUMENT;
     CUtensorMap mw, mx;
     if (int e = weight_map(&mw, w, N, K, ldw)) return e;
-    static int pair_mode = -1;            // MINFER_B200_GEMM_PAIR=0 keeps the one-CTA kernel
-    if (pair_mode < 0) { const char* ev = getenv("MINFER_B200_GEMM_PAIR"); pair_mode = ev ? atoi(ev) : 1; }
-    if (pair_mode && M >= 256 && splits == 1) {
+    GemmArgs a = {};
+    a.out = out; a.partial = nullptr; a.bias = bias; a.status = status; a.ldo = ldo;
+    a.M = M; a.N = N; a.K = K; a.out_dtype = out_dtype; a.kblocks_per_split = 0; a.epi = epi;
+    if (f != nullptr) {
+        a.row_ssq = f->row_ssq; a.ssq_parts = f->ssq_parts; a.ssq_width = f->ssq_width; a.ssq_eps = f->ssq_eps;
+        a.prep_x = f->prep_x; a.ldp = f->ldp; a.prep_g = f->prep_g; a.prep_ssq = f->prep_ssq;
+    }
+    if (pair_mode_on() && M >= 256 && splits == 1) {
         const int pnt = pair_token_tile(M, N);
         if (int e = make_map(&mx, x, M, K, ldx, pnt / 2)) return e;
-        GemmArgs pa;
-        pa.out = out; pa.partial = nullptr; pa.bias = bias; pa.status = status; pa.ldo = ldo;
-        pa.M = M; pa.N = N; pa.K = K; pa.out_dtype = out_dtype; pa.kblocks_per_split = 0;
-        pa.epi = epi;
         switch (pnt) {
-            case 224: return launch_pair<224, 6>(mw, mx, pa, stream);
-            case 208: return launch_pair<208, 6>(mw, mx, pa, stream);
-            case 192: return launch_pair<192, 6>(mw, mx, pa, stream);
-            case 160: return launch_pair<160, 6>(mw, mx, pa, stream);
-            default: return launch_pair<256, 6>(mw, mx, pa, stream);
+            case 224: return launch_pair<224, 6>(mw, mx, a, stream);
+            case 208: return launch_pair<208, 6>(mw, mx, a, stream);
+            case 192: return launch_pair<192, 6>(mw, mx, a, stream);
+            case 160: return launch_pair<160, 6>(mw, mx, a, stream);
+            default: return launch_pair<256, 6>(mw, mx, a, stream);
         }
     }
     if (int e = make_map(&mx, x, M, K, ldx, nt)) return e;
     const int kblocks = (K + TILE_K - 1) / TILE_K;
-    GemmArgs a;
-    a.out = out; a.partial = workspace; a.bias = bias; a.status = status; a.ldo = ldo;
-    a.M = M; a.N = N; a.K = K; a.out_dtype = out_dtype;
+    if (prep) {
+        // few tokens, the residual completed inside the product: K split over a cluster
+        a.kblocks_per_split = (kblocks + CSPLIT - 1) / CSPLIT;
+        switch (nt) {
+            case 16: return launch_cluster<16, 6>(mw, mx, a, stream);
+            case 32: return launch_cluster<32, 5>(mw, mx, a, stream);
+            default: return launch_cluster<64, 4>(mw, mx, a, stream);
+        }
+    }
+    a.partial = workspace;
     a.kblocks_per_split = (kblocks + splits - 1) / splits;
     splits = (kblocks + a.kblocks_per_split - 1) / a.kblocks_per_split;   // no empty split
     a.epi = splits > 1 ? EPI_PARTIAL : epi;
@@ -823,6 +1219,40 @@ extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long
         mf_launch(splitk_reduce_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, 
             workspace, bias, (__nv_bfloat16*)out, ldo, M, N, splits, 0);
     return MF_LAUNCH_CHECK();
+}
+
+// out[M][N] (+)= x[M][K] * w[N][K]^T (+ bias).  x, w bfloat16; for EPI_SWIGLU the rows of w
+// alternate gate,up and out is [M][N/2] bfloat16.  `workspace` must hold
+// mf_gemm_tc_workspace_floats floats when that is not zero.
+// `deferred` (may be null): if the product is split along K, the partial sums are LEFT in
+// `workspace` as [splits][M][N], nothing is written to `out`, and *deferred receives the number
+// of splits, so that the caller's next kernel can add them (and the bias) itself; otherwise
+// *deferred is 0 and `out` is complete.
+extern "C" int mf_gemm_tc(const void* x, long long ldx, const void* w, long long ldw,
+                          const float* bias, void* out, long long ldo, int out_dtype, int M, int N,
+                          int K, int epi, float* workspace, int* deferred, unsigned* status,
+                          cudaStream_t stream) {
+    return gemm_tc_impl(x, ldx, w, ldw, bias, out, ldo, out_dtype, M, N, K, epi, workspace, deferred,
+                        status, nullptr, stream);
+}
+
+// The same product with a norm folded in on either side (see the head of this file):
+// `row_ssq` [ssq_parts][M] (may be null): x is the x' = h * g of a norm over `ssq_width` columns
+// with `ssq_eps`; the accumulators of token t are multiplied by its 1 / rms before anything else.
+// `prep_x` (may be null; EPI_ACCUM only; sizes for which mf_gemm_tc_prep_parts is not 0): `out`
+// is complete when the call returns (no deferred sums), prep_x [M][N] (ldp between rows) holds
+// bfloat16(out * prep_g) and prep_ssq [parts][M] the sums of out^2 per column group.
+extern "C" int mf_gemm_tc_fused(const void* x, long long ldx, const void* w, long long ldw,
+                                const float* bias, void* out, long long ldo, int out_dtype, int M,
+                                int N, int K, int epi, float* workspace, int* deferred,
+                                const float* row_ssq, int ssq_parts, int ssq_width, float ssq_eps,
+                                void* prep_x, long long ldp, const float* prep_g, float* prep_ssq,
+                                unsigned* status, cudaStream_t stream) {
+    FusedNorm f;
+    f.row_ssq = row_ssq; f.ssq_parts = ssq_parts; f.ssq_width = ssq_width; f.ssq_eps = ssq_eps;
+    f.prep_x = (__nv_bfloat16*)prep_x; f.ldp = ldp; f.prep_g = prep_g; f.prep_ssq = prep_ssq;
+    return gemm_tc_impl(x, ldx, w, ldw, bias, out, ldo, out_dtype, M, N, K, epi, workspace, deferred,
+                        status, &f, stream);
 }
 
 // out (+)= bias + sum over the K splits left in `partial` ([splits][M][N]) by a deferred

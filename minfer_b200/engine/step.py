@@ -440,6 +440,9 @@ class Engine:
             takes_pending = getattr(block, "accepts_pending", False)
             if not takes_pending:
                 settle_pending(ctx, h)
+                ctx.extras.pop("prepared", None)     # h is complete: the block norms it itself
+            # rows of h are dropped between the last mixer and its feed-forward unless all are wanted
+            ctx.extras["rows_stay"] = i != last or all_rows
             block.mix(h, ctx, bindings[i])
             if not takes_pending or (i == last and not all_rows):
                 settle_pending(ctx, h)
@@ -448,11 +451,22 @@ class Engine:
                     return torch.empty((0, plan.vocab_size), dtype=torch.float32,
                                        device=self.device)
                 if not all_rows:
+                    ctx.extras.pop("prepared", None)
                     picked = torch.empty((n_want, plan.hidden_size), dtype=torch.float32,
                                          device=self.device)
                     K.gather_rows(h, want_rows, picked)
                     h = picked
+            # the norm that reads h after this block's feed-forward: the next block's first, if
+            # it can take its input prepared, or the model's last (the head applies the scale)
+            if i < last:
+                ctx.extras["next_norm"] = model.blocks[plan.schedule[i + 1].layer].entry_norm()
+            else:
+                ctx.extras["next_norm"] = (model.final_norm if model.head.takes_row_scale()
+                                           and model.final_norm.foldable() is not None else None)
             block.feed(h, ctx)
+        prepared = ctx.extras.pop("prepared", None)
+        if prepared is not None and prepared.norm is model.final_norm:
+            return model.head.forward(prepared.x, torch.float32, row_scale=prepared.scale)
         pending = ctx.extras.pop("pending", None)
         if pending is not None:
             x = model.final_norm.forward_settling(h, pending, self.dtype)

@@ -136,6 +136,11 @@ def _sig_gemm_tc(lib: ctypes.CDLL) -> None:
     lib.mf_gemm_tc_workspace_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mf_gemm_tc_workspace_floats.restype = c_longlong
     lib.mf_gemm_tc_plan.argtypes = [c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+    lib.mf_gemm_tc_fused.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
+                                     c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                     c_void_p, c_int, c_int, c_float, c_void_p, c_longlong, c_void_p,
+                                     c_void_p, c_void_p, c_void_p]
+    lib.mf_gemm_tc_prep_parts.argtypes = [c_int, c_int, c_int]
     lib.mf_wait_probe.argtypes = [c_void_p, ctypes.c_uint, c_ulonglong, c_void_p, c_void_p]
 
 
@@ -348,6 +353,94 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
                           out.data_ptr(), out.stride(0), dtype_code(out.dtype), m, n, k, epi,
                           _ptr(ws, "workspace"), None, _i32(status, "status"), _stream()),
            "gemm_tc", 2 if need else 1)
+
+
+class RowScale:
+    """A norm whose 1/rms is still to be applied to the rows of an activation: the rows hold
+    x' = h * g (g: the norm's weight), ``ssq`` [parts, rows] the sums of h^2 per group of
+    columns, as the product before left them.  The product that reads x' multiplies row t's
+    results by ``rsqrt(ssq[:, t].sum() / width + eps)``."""
+
+    __slots__ = ("ssq", "width", "eps")
+
+    def __init__(self, ssq: torch.Tensor, width: int, eps: float):
+        self.ssq, self.width, self.eps = ssq, int(width), float(eps)
+
+
+_PREP_PARTS: dict = {}
+
+
+def gemm_tc_prep_parts(m: int, n: int, k: int) -> int:
+    """Column groups whose sums of squares a residual-completing product of these sizes writes
+    (the first dimension of its ``ssq``), or 0 if no kernel folds the next norm in at these
+    sizes."""
+    key = (m, n, k)
+    got = _PREP_PARTS.get(key)
+    if got is None:
+        got = int(_lib("gemm_tc").mf_gemm_tc_prep_parts(m, n, k))
+        _PREP_PARTS[key] = got
+    return got
+
+
+def gemm_tc_fused(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                  epi: int, status: torch.Tensor, row_scale: Optional[RowScale] = None,
+                  prep_x: Optional[torch.Tensor] = None, prep_weight: Optional[torch.Tensor] = None,
+                  prep_ssq: Optional[torch.Tensor] = None, defer: bool = False) -> Optional[torch.Tensor]:
+    """``gemm_tc`` with a norm folded in on either side.  ``row_scale``: ``x`` holds x' = h * g
+    of a norm and row t's results are multiplied by its 1/rms.  ``prep_x`` [M, N] bfloat16,
+    ``prep_weight`` [N] float32 and ``prep_ssq`` [gemm_tc_prep_parts(M, N, K), M] float32
+    (EPI_ACCUM only): ``out`` is complete when the call returns and the three hold what the
+    norm that reads ``out`` next needs.  ``defer``: if the product is split along K, returns the
+    float32 partial sums [splits, M, N] (``out`` untouched, may be None) instead of adding them."""
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise KernelError(f"gemm: shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    if not gemm_tc_supported(x, w):
+        raise KernelError("gemm_tc: operands must be bfloat16 with 16-byte aligned rows")
+    want_cols = n // 2 if epi == EPI_SWIGLU else n
+    if out is not None and (out.shape != (m, want_cols) or out.stride(1) != 1):
+        raise KernelError(f"gemm: out has shape {tuple(out.shape)}, expected {(m, want_cols)}")
+    if bias is not None and bias.numel() != n:
+        raise KernelError("gemm: bias has the wrong length")
+    if row_scale is not None and (row_scale.ssq.dim() != 2 or row_scale.ssq.shape[1] != m):
+        raise KernelError("gemm: the sums of squares must be [parts, rows]")
+    if prep_x is not None:
+        parts = gemm_tc_prep_parts(m, n, k)
+        if parts == 0:
+            raise KernelError("gemm: no kernel folds the next norm in at these sizes")
+        if (prep_x.shape != (m, n) or prep_x.dtype != torch.bfloat16 or prep_x.stride(1) != 1
+                or prep_weight is None or prep_weight.numel() != n or prep_ssq is None
+                or prep_ssq.shape != (parts, m)):
+            raise KernelError("gemm: the next norm's tensors have the wrong shapes")
+    lib = _lib("gemm_tc")
+    need = _gemm_tc_shape(m, n, k, epi)[2]
+    ws = None
+    if need and prep_x is None:
+        ws = torch.empty(need, dtype=torch.float32, device=x.device)
+    splits = ctypes.c_int(0)
+    if defer:
+        if ws is None:
+            return None
+        target, ldo, code = ws, n, F32
+    else:
+        target, ldo, code = out, out.stride(0), dtype_code(out.dtype)
+    _check(lib.mf_gemm_tc_fused(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), _f32(bias, "bias") if not defer else None,
+        target.data_ptr(), ldo, code, m, n, k, epi, _ptr(ws, "workspace"),
+        ctypes.addressof(splits) if defer else None,
+        _f32(row_scale.ssq, "ssq") if row_scale is not None else None,
+        row_scale.ssq.shape[0] if row_scale is not None else 0,
+        row_scale.width if row_scale is not None else 0,
+        row_scale.eps if row_scale is not None else 0.0,
+        _ptr(prep_x, "prep_x"), prep_x.stride(0) if prep_x is not None else 0,
+        _f32(prep_weight, "prep_weight"), _f32(prep_ssq, "prep_ssq"), _i32(status, "status"),
+        _stream()), "gemm_tc", 2 if (need and prep_x is None and not defer) else 1)
+    if defer:
+        if splits.value < 1:
+            raise KernelError("gemm_tc: a split product reported no splits")
+        return ws[:splits.value * m * n].view(splits.value, m, n)
+    return None
 
 
 def gemm_tc_partial_sums(x: torch.Tensor, w: torch.Tensor,

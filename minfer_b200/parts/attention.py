@@ -135,6 +135,8 @@ class Attention(Mixer):
         self.qkv = Linear(w, b)
         self.out = Linear(weights[f"{p}o_proj.weight"],
                           weights[f"{p}o_proj.bias"] if self.out_bias else None)
+        # the projection of q|k|v can apply a norm's 1/rms itself (bfloat16 on tensor cores)
+        self.accepts_row_scale = self.qkv.takes_row_scale()
         if self.position is not None:
             self.position.load(p, weights)
 
@@ -165,12 +167,13 @@ class Attention(Mixer):
         dev, act = x.device, ctx.act_dtype
         inv_freq, rotary_dim, style = None, 0, 0
         fused = self.position.fused_rotary(dev) if self.position is not None else (None, 0, 0)
+        rs = ctx.input_scale                       # the norm's 1/rms, if this product is to apply it
         # the K splits of a small projection are added by the rotary kernel itself
-        split = self.qkv.partial_sums(x) if fused is not None else None
+        split = self.qkv.partial_sums(x, row_scale=rs) if fused is not None else None
         if split is not None:
             qkv, n_partials, qkv_bias = split.partial, split.partial.shape[0], split.bias
         else:
-            qkv, n_partials, qkv_bias = self.qkv.forward(x, torch.float32), 0, None
+            qkv, n_partials, qkv_bias = self.qkv.forward(x, torch.float32, row_scale=rs), 0, None
         if fused is None:
             self.position.apply(qkv, ctx, nh, nk, hd)
         else:
@@ -245,6 +248,14 @@ class Attention(Mixer):
         self._project_out(o, ctx, residual)
 
     def _project_out(self, o: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
+        target = ctx.extras.pop("prepare_for", None)
+        if target is not None:
+            # the product completes the residual and prepares the next norm's input
+            settle_pending(ctx, residual)
+            prepared = self.out.accumulate_prepared(o, residual, target)
+            if prepared is not None:
+                ctx.extras["prepared"] = prepared
+                return
         pending = self.out.partial_sums(o)
         if pending is None:
             self.out.forward(o, torch.float32, out=residual, accumulate=True)

@@ -85,6 +85,18 @@ class Pending:
         K.splitk_reduce(self.partial, self.bias, h, accumulate=True)
 
 
+@dataclass
+class Prepared:
+    """What a product that completed the residual stream left for the norm that reads it next
+    (``norm``): ``x`` = bfloat16(h * weight of that norm) and the sums of h^2 that give each
+    row's 1/rms (``scale``, a ``kernels.api.RowScale``).  ``h`` itself is complete in memory, so
+    anyone who cannot use this simply ignores it and norms ``h``."""
+
+    x: torch.Tensor
+    scale: Any
+    norm: Any
+
+
 def settle_pending(ctx: "StepContext", h: torch.Tensor) -> None:
     """Adds what a part left pending into ``h``."""
     pending = ctx.extras.pop("pending", None)
@@ -115,6 +127,10 @@ class StepContext:
     status: torch.Tensor            # int32 [1] error bits set by kernels
     host_slots: Sequence[int] = ()
     extras: Dict[str, Any] = field(default_factory=dict)
+    # set by a block around a call of a mixer or feed-forward that says ``accepts_row_scale``:
+    # the rows of ``x`` still lack their norm's 1/rms (a ``kernels.api.RowScale``), which the
+    # part's first product applies
+    input_scale: Any = None
 
 
 class Part:
@@ -148,6 +164,12 @@ class Norm(Part):
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
+    def foldable(self) -> Optional[Tuple[torch.Tensor, float, int]]:
+        """(weight float32 [size], eps, size) if this norm is y = x / rms(x) * weight, so that
+        the product before it can prepare its input and the product after it apply 1/rms
+        (``Prepared``); None for any other norm."""
+        return None
+
     def forward_settling(self, h: torch.Tensor, pending: "Pending",
                          out_dtype: torch.dtype) -> torch.Tensor:
         """Adds ``pending`` into ``h`` and norms the result.  Norms that can do both in one
@@ -169,6 +191,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True: ``forward_add`` looks at ``ctx.input_scale`` and lets its first product apply it;
+    # ``ctx.extras["prepare_for"]`` (a norm), if set, may be answered with a ``Prepared`` in
+    # ``ctx.extras["prepared"]`` by the product that adds into the residual
+    accepts_row_scale = False
+
     def cache_request(self) -> Optional[CacheRequest]:
         return None
 
@@ -181,12 +208,19 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_row_scale = False      # as for ``Mixer``
+
     def forward_add(self, x: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
         raise NotImplementedError
 
 
 class Block(Part):
     mixer: Mixer
+
+    def entry_norm(self) -> Optional[Norm]:
+        """The norm that reads the residual stream first in ``mix``, if the block can take that
+        norm's input prepared by the product before it (``Prepared``); else None."""
+        return None
 
     def parts(self) -> Sequence[Part]:
         """Every part this block runs, whatever it calls them; the engine asks each whether it

@@ -42,17 +42,47 @@ class PreNormBlock(Block):
 
     accepts_pending = True     # its norms add a pending projection output while reading h
 
+    def entry_norm(self):
+        if self.mixer_norm.foldable() is not None and getattr(self.mixer, "accepts_row_scale", False):
+            return self.mixer_norm
+        return None
+
     @staticmethod
-    def _normed(norm, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    def _normed(norm, h: torch.Tensor, ctx: StepContext, consumer):
+        """The norm's output for ``consumer``, as (x, row scale): a prepared input if the product
+        before left one for this very norm and the consumer can apply the scale, else the norm
+        as a kernel (which also adds a pending projection output into ``h``)."""
+        prepared = ctx.extras.pop("prepared", None)
+        if (prepared is not None and prepared.norm is norm
+                and getattr(consumer, "accepts_row_scale", False)):
+            return prepared.x, prepared.scale
         pending = ctx.extras.pop("pending", None)
         if pending is not None:
-            return norm.forward_settling(h, pending, ctx.act_dtype)
-        return norm.forward(h, ctx.act_dtype)
+            return norm.forward_settling(h, pending, ctx.act_dtype), None
+        return norm.forward(h, ctx.act_dtype), None
+
+    def _call(self, part, x, scale, ctx, target, *args) -> None:
+        ctx.input_scale = scale
+        if target is not None and getattr(part, "accepts_row_scale", False):
+            ctx.extras["prepare_for"] = target
+        try:
+            part.forward_add(x, ctx, *args)
+        finally:
+            ctx.input_scale = None
+            ctx.extras.pop("prepare_for", None)
 
     def mix(self, h: torch.Tensor, ctx: StepContext, binding: CallBinding) -> None:
-        x = self._normed(self.mixer_norm, h, ctx)
-        self.mixer.forward_add(x, ctx, binding, h)
+        x, scale = self._normed(self.mixer_norm, h, ctx, self.mixer)
+        # the mixer's last product may prepare the input of the norm before the feed-forward,
+        # unless the engine drops rows of h between the two
+        target = None
+        if (ctx.extras.get("rows_stay", True) and self.feed_forward_norm.foldable() is not None
+                and getattr(self.feed_forward, "accepts_row_scale", False)):
+            target = self.feed_forward_norm
+        self._call(self.mixer, x, scale, ctx, target, binding, h)
 
     def feed(self, h: torch.Tensor, ctx: StepContext) -> None:
-        x = self._normed(self.feed_forward_norm, h, ctx)
-        self.feed_forward.forward_add(x, ctx, h)
+        x, scale = self._normed(self.feed_forward_norm, h, ctx, self.feed_forward)
+        # the feed-forward's last product may prepare the input of the norm that reads h next
+        # (the next block's first, or the model's last), which the engine names
+        self._call(self.feed_forward, x, scale, ctx, ctx.extras.get("next_norm"), h)

@@ -60,6 +60,7 @@ class GatedMlp(FeedForward):
             packed = torch.cat([g, u], dim=0)
         self.gate_up = Linear(packed.contiguous())
         self.down = Linear(weights[f"{p}down_proj.weight"])
+        self.accepts_row_scale = self.interleaved and self.gate_up.takes_row_scale()
 
     def export(self, prefix: str) -> Dict[str, torch.Tensor]:
         p = f"{prefix}mlp."
@@ -77,12 +78,25 @@ class GatedMlp(FeedForward):
         act = torch.empty((x.shape[0], self.intermediate_size), dtype=ctx.act_dtype,
                           device=x.device)
         w = self.gate_up.weight
+        rs = ctx.input_scale                       # the norm's 1/rms, if this product is to apply it
         if (self.interleaved and x.shape[0] > 0 and gemm.use_tensor_cores()
                 and K.gemm_tc_supported(x, w)):
-            K.gemm_tc(x, w, None, act, K.EPI_SWIGLU, gemm.status_word(x.device))
+            if rs is not None:
+                K.gemm_tc_fused(x, w, None, act, K.EPI_SWIGLU, gemm.status_word(x.device), row_scale=rs)
+            else:
+                K.gemm_tc(x, w, None, act, K.EPI_SWIGLU, gemm.status_word(x.device))
         else:
+            if rs is not None:
+                raise K.KernelError("a row scale needs the tensor-core product")
             gu = self.gate_up.forward(x, ctx.act_dtype)
             K.swiglu(gu, act, self.interleaved)
+        target = ctx.extras.pop("prepare_for", None)
+        if target is not None:
+            settle_pending(ctx, residual)
+            prepared = self.down.accumulate_prepared(act, residual, target)
+            if prepared is not None:
+                ctx.extras["prepared"] = prepared
+                return
         pending = self.down.partial_sums(act)
         if pending is None:
             self.down.forward(act, torch.float32, out=residual, accumulate=True)

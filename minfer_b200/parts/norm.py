@@ -34,6 +34,9 @@ class RmsNorm(Norm):
     def export(self, prefix: str) -> Dict[str, torch.Tensor]:
         return {f"{prefix}{self.name}.weight": self.weight}
 
+    def foldable(self):
+        return (self.weight, self.eps, self.size)
+
     def forward(self, x32: torch.Tensor, out_dtype: torch.dtype,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         n = x32.shape[0] if rows is None else rows.numel()

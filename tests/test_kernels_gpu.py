@@ -689,3 +689,64 @@ def test_deferred_split_sums_feed_the_next_kernel():
     for a, b in zip(outs[0], outs[1]):
         assert torch.equal(a, b)
     assert int(st) == 0
+
+
+def _norm_ref(h, g, eps):
+    h = h.double()
+    return h / torch.sqrt((h * h).mean(-1, keepdim=True) + eps) * g.double()
+
+
+@pytest.mark.parametrize("m", [1, 8, 17, 64, 300, 700])
+@pytest.mark.parametrize("n,k", [(3584, 3584), (896, 4864), (200, 1024), (64, 128), (384, 264)])
+def test_product_that_completes_the_residual_and_prepares_the_next_norm(m, n, k):
+    """EPI_ACCUM with the next norm folded in (K split over a cluster for few tokens, the
+    CTA-pair kernel's epilogue for many): the residual, x' = bfloat16(h * g) and the sums of
+    squares against float64; then a product that reads x' with the row scale against
+    norm-then-product in float64."""
+    from minfer_b200.kernels import api as K
+    g0 = torch.Generator().manual_seed(m + n + k)
+    x = (torch.randn(m, k, generator=g0) * 0.5).bfloat16().cuda()
+    w = (torch.randn(n, k, generator=g0) * 0.05).bfloat16().cuda()
+    h0 = torch.randn(m, n, generator=g0).cuda()
+    gw = (1 + 0.1 * torch.randn(n, generator=g0)).cuda()
+    bias = (torch.randn(n, generator=g0) * 0.1).cuda()
+    parts = K.gemm_tc_prep_parts(m, n, k)
+    if parts == 0:
+        # nothing folds the norm in at these sizes: the call says so instead of computing
+        with pytest.raises(K.KernelError):
+            K.gemm_tc_fused(x, w, None, h0.clone(), K.EPI_ACCUM, status(),
+                            prep_x=torch.empty(m, n, dtype=torch.bfloat16, device="cuda"),
+                            prep_weight=gw, prep_ssq=torch.empty(1, m, device="cuda"))
+        return
+    h = h0.clone()
+    xp = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    # guards behind the sums of squares: nothing may be written past the parts that exist
+    ssq_all = torch.full((parts + 2, m), float("nan"), device="cuda")
+    ssq = ssq_all[:parts]
+    st = status()
+    K.gemm_tc_fused(x, w, bias, h, K.EPI_ACCUM, st, prep_x=xp, prep_weight=gw, prep_ssq=ssq)
+    assert int(st.item()) == 0
+    assert torch.isnan(ssq_all[parts:]).all() and not torch.isnan(ssq).any()
+    want_h = h0.double() + x.double() @ w.double().t() + bias.double()
+    close(h, want_h, torch.float32)                     # exact bfloat16 products, float32 sums
+    close(xp, h.double() * gw.double(), torch.bfloat16)
+    close(ssq.sum(0), (h.double() ** 2).sum(-1), torch.float32, scale=float((h.double() ** 2).sum(-1).max()) * 10)
+    # the consumer: a second product reads x' and applies 1/rms in its epilogue
+    n2 = 256
+    w2 = (torch.randn(n2, n, generator=g0) * 0.05).bfloat16().cuda()
+    b2 = torch.randn(n2, generator=g0).cuda()
+    eps = 1e-5
+    want = _norm_ref(h, gw, eps) @ w2.double().t() + b2.double()
+    rs = K.RowScale(ssq, n, eps)
+    out = torch.empty(m, n2, device="cuda")
+    K.gemm_tc_fused(xp, w2, b2, out, K.EPI_STORE, st, row_scale=rs)
+    close(out, want, torch.bfloat16)
+    part = K.gemm_tc_fused(xp, w2, None, None, K.EPI_STORE, st, row_scale=rs, defer=True)
+    if part is not None:                               # split along K: the splits carry the scale
+        close(part.sum(0) + b2, want, torch.bfloat16)
+    # and SwiGLU over interleaved gate/up rows
+    act = torch.empty(m, n2 // 2, dtype=torch.bfloat16, device="cuda")
+    K.gemm_tc_fused(xp, w2, None, act, K.EPI_SWIGLU, st, row_scale=rs)
+    y = _norm_ref(h, gw, eps) @ w2.double().t()
+    close(act, torch.nn.functional.silu(y[:, 0::2]) * y[:, 1::2], torch.bfloat16)
+    assert int(st.item()) == 0
