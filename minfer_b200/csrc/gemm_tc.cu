@@ -22,9 +22,10 @@
 // of every token (`prep_ssq`).  The product that follows takes x' as its token operand and
 // multiplies token t's accumulators by 1 / sqrt(sum_parts ssq[.][t] / width + eps) in its
 // epilogue (`row_ssq`): the same numbers as norm, then product, up to the place of one
-// rounding.  Few tokens: the product that completes the residual is split along K over a
-// CLUSTER of CTAs, which add their partial tiles in rank order through distributed shared
-// memory (no atomics: reproducible), each finishing 128 / splits columns.
+// rounding.  This is done for few tokens (decoding), where a norm as a kernel of its own is a
+// link in a chain of dependent launches: there the product that completes the residual is split
+// along K over a CLUSTER of CTAs, which add their partial tiles in rank order through
+// distributed shared memory (no atomics: reproducible), each finishing some of the tokens.
 //
 // Every wait on an mbarrier is bounded: when it runs out the kernel sets
 // MF_STATUS_WAIT_TIMEOUT in the status word, stops issuing work, lets its copies land,
@@ -72,25 +73,17 @@ struct GemmArgs {
     long long ldp;            // elements between consecutive tokens of prep_x
 };
 
-// 1 / rms of the token rows [m0, m0 + n_tok) into `out` (shared memory), by one warp: every lane
-// adds the parts p = lane, lane + 32, .. of up to 16 tokens at a time (all loads in flight
-// together), then the lanes' sums are added in a fixed order.
-__device__ __forceinline__ void row_scales_by_warp(const GemmArgs& a, int m0, int n_tok, float* out, int lane) {
-    for (int t0 = 0; t0 < n_tok; t0 += 16) {
-        float acc[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
-        for (int p = lane; p < a.ssq_parts; p += 32) {
-            const float* row = a.row_ssq + (size_t)p * a.M + m0 + t0;
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                if (t0 + j < n_tok && m0 + t0 + j < a.M) acc[j] += row[j];
+// 1 / rms of the token rows m0 + t, t = first, first + step, .. < n_tok, into out[t] (shared
+// memory): a thread adds a token's parts in order, all of its loads in flight together.
+__device__ __forceinline__ void row_scales(const GemmArgs& a, int m0, int n_tok, float* out, int first, int step) {
+    for (int t = first; t < n_tok; t += step) {
+        float sum = 0.0f;
+        if (m0 + t < a.M) {
+            const float* col = a.row_ssq + m0 + t;
+#pragma unroll 8
+            for (int p = 0; p < a.ssq_parts; ++p) sum += col[(size_t)p * a.M];
         }
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-            const float sum = warp_sum(acc[j]);
-            if (lane == 0 && t0 + j < n_tok) out[t0 + j] = rsqrtf(sum / (float)a.ssq_width + a.ssq_eps);
-        }
+        out[t] = rsqrtf(sum / (float)a.ssq_width + a.ssq_eps);
     }
 }
 
@@ -335,8 +328,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         pdl_wait();          // every other thread: nothing below may run ahead of the kernel before
     }
     // the tokens' 1 / rms, by the two warps that have nothing to do while the weights stream
-    if (a.row_ssq != nullptr && warp >= 2)
-        row_scales_by_warp(a, m0 + (warp - 2) * (NT / 2), NT / 2, scale_s + (warp - 2) * (NT / 2), lane);
+    if (a.row_ssq != nullptr && warp >= 2) row_scales(a, m0, NT, scale_s, tid - 64, 64);
     if (warp == 1 && lane == 0) {
         // ---- MMA issuer --------------------------------------------------------------
         constexpr uint32_t idesc = umma_idesc(NT);
@@ -399,18 +391,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 // Few tokens, the product that completes the residual stream (out += x W^T): split along K
 // over a CLUSTER of CSPLIT CTAs (grid z = cluster z), whose partial tiles never leave the
 // chip.  Main loop as in gemm_tc_kernel.  Then, by distributed shared memory:
-//   1. every CTA's accumulator is complete and its operand ring idle: cluster barrier
-//   2. CTA r sends, for each of the CSPLIT column groups (128 / CSPLIT columns each), its
-//      partial sums of that group to the CTA that owns the group (rank = group), into that
-//      CTA's idle ring: cluster barrier
-//   3. every CTA adds the CSPLIT partial sums of its group in rank order (reproducible), adds
-//      them (and the bias) into `out`, and, if asked, writes the next norm's x' = h * g and the
-//      sums of h^2 of its columns (see the head of this file).
+//   1. as soon as its accumulator is complete, CTA r sends its partial sums of token t (all
+//      128 columns of the tile) to the CTA that owns the token (rank t mod CSPLIT), into a
+//      buffer of that CTA's shared memory that nothing else uses; meanwhile it fetches the old
+//      residual values of its own tokens, the bias and the norm's weights: then one cluster
+//      barrier
+//   2. every CTA adds the CSPLIT partial sums of its tokens in rank order (reproducible), adds
+//      them (and the bias) into `out`, and, if asked, writes the next norm's x' = h * g and each
+//      token's sum of h^2 over the tile's 128 columns (see the head of this file).
 // No partial sums in global memory, no kernel to add them, and the norm that follows is left
 // with a scale that the next product applies.
 // ------------------------------------------------------------------------------------------
 #define CSPLIT 8
-#define CGROUP (TILE_N / CSPLIT)          // columns a CTA finishes
 
 __device__ __forceinline__ uint32_t rank_in_cluster() {
     uint32_t r;
@@ -422,9 +414,8 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t ran
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
     return r;
 }
-__device__ __forceinline__ void st_cluster_v4(uint32_t addr, float a, float b, float c, float d) {
-    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};"
-                 ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float a) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
 }
 __device__ __forceinline__ void cluster_barrier() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -438,10 +429,13 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     constexpr int B_BYTES = NT * TILE_K * 2;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr int TMEM_COLS = TmemCols<NT>::value;
-    static_assert(CSPLIT * CGROUP * NT * 4 <= STAGES * STAGE_BYTES, "the partial sums fit the idle ring");
+    constexpr int TPO = NT / CSPLIT;                             // tokens a CTA owns: rank, rank + CSPLIT, ..
+    constexpr int PART_BYTES = CSPLIT * TILE_N * TPO * 4;        // the partial sums sent to this CTA
+    static_assert(TPO >= 2 && TPO % 2 == 0, "a token tile of at least 16 tokens");
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);   // full[S], empty[S], acc
+    float* part = (float*)(smem + STAGES * STAGE_BYTES);         // [src rank][owned token][column]
+    uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES + PART_BYTES);   // full[S], empty[S], acc
     uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     float* scale_s = (float*)(tmem_slot + 2);        // [NT] 1 / rms of this tile's tokens
@@ -507,8 +501,7 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     } else {
         pdl_wait();
     }
-    if (a.row_ssq != nullptr && warp >= 2)
-        row_scales_by_warp(a, m0 + (warp - 2) * (NT / 2), NT / 2, scale_s + (warp - 2) * (NT / 2), lane);
+    if (a.row_ssq != nullptr && warp >= 2) row_scales(a, m0, NT, scale_s, tid - 64, 64);
     if (warp == 1 && lane == 0) {
         // ---- MMA issuer ---------------------------------------------------------------------
         constexpr uint32_t idesc = umma_idesc(NT);
@@ -531,21 +524,27 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     }
     __syncwarp();
 
-    // ---- 1. this CTA's accumulator is complete (every MMA has read its operands: the ring is idle)
+    // what this CTA's own tokens need besides the sums: asked for now, used after the barrier.
+    // A thread is a column of the tile in both halves of the epilogue.
+    const int n_local = warp * 32 + lane;
+    const int n = n0 + n_local;
+    const bool n_ok = n < a.N;
+    const float bias = (a.bias != nullptr && n_ok) ? a.bias[n] : 0.0f;
+    const float g = (a.prep_x != nullptr && n_ok) ? a.prep_g[n] : 0.0f;
+    float old[TPO];
+#pragma unroll
+    for (int i = 0; i < TPO; ++i) {
+        const int tok = m0 + (int)rank + i * CSPLIT;
+        old[i] = (a.epi == EPI_ACCUM && tok < a.M && n_ok) ? ((const float*)a.out)[(size_t)tok * a.ldo + n] : 0.0f;
+    }
+
+    // ---- 1. the accumulator is complete: token t's partial sums go to CTA t mod CSPLIT -------------
     const bool acc_ok = n_iter > 0 ? mbar_wait(smem_u32(&bars[2 * STAGES]), 0u, abort_flag) : true;
     tc_fence_after();
-    __syncthreads();                                  // also: the scales are in shared memory
-    // Every thread of every CTA of the cluster comes here, whatever happened above (a wait that
-    // ran out only sets the abort flag): the cluster's barriers cannot be left waiting.
-    cluster_barrier();
-
-    // ---- 2. the partial sums go to the owners of their column groups --------------------------
-    // ring of the owner: part[src rank][column of the group][token], float32
-    float* part = (float*)smem;
     {
-        const int n_local = warp * 32 + lane;         // this thread's accumulator row = column of W
-        const uint32_t owner = (uint32_t)(n_local / CGROUP);
-        const uint32_t dst0 = map_to_rank(smem_u32(part + ((size_t)rank * CGROUP + (n_local % CGROUP)) * NT), owner);
+        // in the owner: part[(src rank * TPO + t / CSPLIT) * 128 + column]: the 32 lanes of a warp
+        // write 128 consecutive bytes
+        const uint32_t mine = smem_u32(part + (size_t)rank * TPO * TILE_N + n_local);
 #pragma unroll 1
         for (int c0 = 0; c0 < NT; c0 += 16) {
             if (m0 + c0 >= a.M) break;
@@ -557,48 +556,49 @@ gemm_tc_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 #pragma unroll
                 for (int j = 0; j < 16; ++j) r[j] = 0u;
             }
+            // tokens c0 + o and c0 + o + 8 belong to owner o, as its tokens c0 / 8 and c0 / 8 + 1
 #pragma unroll
-            for (int j = 0; j < 16; j += 4)
-                st_cluster_v4(dst0 + (uint32_t)((c0 + j) * 4), __uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                              __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            for (int o = 0; o < CSPLIT; ++o) {
+                const uint32_t dst = map_to_rank(mine, (uint32_t)o) + (uint32_t)((c0 / CSPLIT) * TILE_N * 4);
+                st_cluster_f32(dst, __uint_as_float(r[o]));
+                st_cluster_f32(dst + TILE_N * 4, __uint_as_float(r[o + 8]));
+            }
         }
     }
+    // Every thread of every CTA of the cluster comes here, whatever happened above (a wait that
+    // ran out only sets the abort flag): the cluster's barrier cannot be left waiting.  It also
+    // orders the scales in this CTA's shared memory before their use below.
     cluster_barrier();
 
-    // ---- 3. this CTA's column group: sums in rank order, residual, the next norm's input ---------
-    {
-        const int c = tid % CGROUP;                   // column of the group
-        const int tg = tid / CGROUP;                  // tokens tg, tg + 128 / CGROUP, ..
-        constexpr int TSTEP = 128 / CGROUP;
-        const int n = n0 + (int)rank * CGROUP + c;
-        const bool n_ok = n < a.N;
-        const float bias = (a.bias != nullptr && n_ok) ? a.bias[n] : 0.0f;
-        const float g = (a.prep_x != nullptr && n_ok) ? a.prep_g[n] : 0.0f;
-#pragma unroll 1
-        for (int t = tg; t < NT; t += TSTEP) {
-            const int tok = m0 + t;
-            float sq = 0.0f;
-            if (tok < a.M && n_ok) {
-                float v = 0.0f;
+    // ---- 2. this CTA's tokens: sums in rank order, residual, the next norm's input -----------------
+    float* sq_s = scale_s + NT;                       // [4 warps][TPO]
 #pragma unroll
-                for (int s = 0; s < CSPLIT; ++s) v += part[((size_t)s * CGROUP + c) * NT + t];
-                if (a.row_ssq != nullptr) v *= scale_s[t];
-                float* o = (float*)a.out + (size_t)tok * a.ldo + n;
-                const float hn = (a.epi == EPI_ACCUM ? *o : 0.0f) + v + bias;
-                *o = hn;
-                if (a.prep_x != nullptr) {
-                    a.prep_x[(size_t)tok * a.ldp + n] = __float2bfloat16_rn(hn * g);
-                    sq = hn * hn;
-                }
-            }
+    for (int i = 0; i < TPO; ++i) {
+        const int t = (int)rank + i * CSPLIT;
+        const int tok = m0 + t;
+        float sq = 0.0f;
+        if (tok < a.M && n_ok) {
+            float v = 0.0f;
+#pragma unroll
+            for (int s = 0; s < CSPLIT; ++s) v += part[((size_t)s * TPO + i) * TILE_N + n_local];
+            if (a.row_ssq != nullptr) v *= scale_s[t];
+            const float hn = old[i] + v + bias;
+            ((float*)a.out)[(size_t)tok * a.ldo + n] = hn;
             if (a.prep_x != nullptr) {
-                // the CGROUP lanes that hold this token's columns are neighbours in the warp
-#pragma unroll
-                for (int o = CGROUP / 2; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-                if (c == 0 && tok < a.M)
-                    a.prep_ssq[((size_t)blockIdx.y * CSPLIT + rank) * a.M + tok] = sq;
+                a.prep_x[(size_t)tok * a.ldp + n] = __float2bfloat16_rn(hn * g);
+                sq = hn * hn;
             }
         }
+        if (a.prep_x != nullptr) {
+            sq = warp_sum(sq);
+            if (lane == 0) sq_s[warp * TPO + i] = sq;
+        }
+    }
+    if (a.prep_x != nullptr) {
+        __syncthreads();
+        if (tid < TPO && m0 + (int)rank + tid * CSPLIT < a.M)
+            a.prep_ssq[(size_t)blockIdx.y * a.M + m0 + (int)rank + tid * CSPLIT] =
+                (sq_s[tid] + sq_s[TPO + tid]) + (sq_s[2 * TPO + tid] + sq_s[3 * TPO + tid]);
     }
     tc_fence_before();
     __syncthreads();
@@ -746,7 +746,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& 
 template <int NT, int STAGES>
 static int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
                           cudaStream_t stream) {
-    constexpr int smem = STAGES * (A_BYTES + NT * TILE_K * 2) + 1024 + 256 + NT * 4;
+    constexpr int smem = STAGES * (A_BYTES + NT * TILE_K * 2) + TILE_N * NT * 4 + 1024 + 256 + NT * 4 + NT * 2;
     static bool configured[64] = {false};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MF_ERR_UNSUPPORTED;
@@ -849,8 +849,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     uint64_t* acc_empty = acc_full + 2;       // [2]       leader's are used
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
-    float* scale_s = (float*)(tmem_slot + 2);                 // [2][NT] 1 / rms of a tile's tokens
-    float* sq_s = scale_s + 2 * NT;                           // [2][4][NT] sums of squares by warp
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = cluster_ctarank();
@@ -941,66 +939,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             const int n = n0 + (int)rank * TILE_N + q * 32 + lane;
             const bool n_ok = n < a.N;
             const float bias = (a.bias != nullptr && n_ok) ? a.bias[n] : 0.0f;
-            float* scale_b = scale_s + b * NT;
-            if (a.row_ssq != nullptr) {
-                // 1 / rms of this tile's tokens: each epilogue warp a quarter of them, into the
-                // buffer of this accumulator (the other one may still be read for the last tile)
-                constexpr int QUARTER = (NT / 4 + 15) / 16 * 16;
-                const int t_lo = q * QUARTER;
-                if (t_lo < NT)
-                    row_scales_by_warp(a, m0 + t_lo, min(QUARTER, NT - t_lo), scale_b + t_lo, lane);
-                asm volatile("bar.sync 1, 128;" ::: "memory");        // the four epilogue warps
-            }
-            if (a.epi == EPI_ACCUM && a.prep_x != nullptr) {
-                // the residual is complete after this product: write it, the next norm's
-                // x' = h * g, and the sums of h^2 over this CTA's 128 columns
-                float* sq_b = sq_s + (b * 4 + q) * NT;
-                const float g = n_ok ? a.prep_g[n] : 0.0f;
 #pragma unroll 1
-                for (int c0 = 0; c0 < NT; c0 += 16) {
-                    if (m0 + c0 >= a.M) break;
-                    uint32_t r[16];
-                    tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * NT + c0), r);
-                    tc_wait_ld();
-                    float old[16];
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int tok = m0 + c0 + j;
-                        old[j] = (tok < a.M && n_ok) ? ((const float*)a.out)[(size_t)tok * a.ldo + n] : 0.0f;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int tok = m0 + c0 + j;
-                        float sq = 0.0f;
-                        if (tok < a.M && n_ok) {
-                            const float hn = old[j] + __uint_as_float(r[j]) + bias;
-                            ((float*)a.out)[(size_t)tok * a.ldo + n] = hn;
-                            a.prep_x[(size_t)tok * a.ldp + n] = __float2bfloat16_rn(hn * g);
-                            sq = hn * hn;
-                        }
-                        sq = warp_sum(sq);
-                        if (lane == 0) sq_b[c0 + j] = sq;
-                    }
-                }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                // (this CTA's 128 columns may lie beyond N altogether: then it has no part to write)
-                const int part = (n0 >> 7) + (int)rank;
-                for (int t = (warp - 2) * 32 + lane; t < NT; t += 128) {
-                    if (m0 + t < a.M && n0 + (int)rank * TILE_N < a.N) {
-                        const float* sq0 = sq_s + (size_t)(b * 4) * NT + t;
-                        a.prep_ssq[(size_t)part * a.M + m0 + t] = (sq0[0] + sq0[NT]) + (sq0[2 * NT] + sq0[3 * NT]);
-                    }
-                }
-            } else {
-#pragma unroll 1
-                for (int c0 = 0; c0 < NT; c0 += 16) {
-                    if (m0 + c0 >= a.M) break;
-                    uint32_t r[16];
-                    tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * NT + c0), r);
-                    tc_wait_ld();
-                    store_chunk(a, r, n, n_ok, bias, m0 + c0, lane, 0,
-                                a.row_ssq != nullptr ? scale_b + c0 : nullptr);
-                }
+            for (int c0 = 0; c0 < NT; c0 += 16) {
+                if (m0 + c0 >= a.M) break;
+                uint32_t r[16];
+                tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * NT + c0), r);
+                tc_wait_ld();
+                store_chunk(a, r, n, n_ok, bias, m0 + c0, lane, 0);
             }
             tc_fence_before();
             __syncwarp();
@@ -1027,7 +972,7 @@ static int sm_count();
 template <int NT, int STAGES>
 static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
                        cudaStream_t stream) {
-    constexpr int smem = STAGES * (A_BYTES + (NT / 2) * TILE_K * 2) + 1024 + 256 + 10 * NT * 4;
+    constexpr int smem = STAGES * (A_BYTES + (NT / 2) * TILE_K * 2) + 1024 + 256;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<NT, STAGES>,
@@ -1136,8 +1081,13 @@ extern "C" int mf_gemm_tc_prep_parts(int M, int N, int K) {
     int nt, splits;
     mf_gemm_tc_plan(M, N, K, EPI_ACCUM, &nt, &splits);
     const int kblocks = (K + TILE_K - 1) / TILE_K;
-    if (pair_mode_on() && M >= 256 && splits == 1) return (N + TILE_N - 1) / TILE_N;
-    if (nt <= 64 && splits > 1 && kblocks >= CSPLIT) return ((N + TILE_N - 1) / TILE_N) * CSPLIT;
+    // (Folded into the CTA-pair kernel of whole prompts as well it lost: the two norms of a layer
+    // cost 19 us at 2,048 tokens, the longer epilogues of the four products 36 us.)
+    // Every cluster has to be on the GPU at once, two CTAs to an SM: more column tiles than that
+    // allows (hidden 5,120: 40 tiles, 320 CTAs) would run in two rounds, and lost (7.49 -> 7.58 ms
+    // a step at the 14B shape); such sizes keep the split with partial sums in memory.
+    const int tiles_n = (N + TILE_N - 1) / TILE_N;
+    if (nt <= 64 && splits > 1 && kblocks >= CSPLIT && tiles_n * CSPLIT <= 2 * sm_count()) return tiles_n;
     return 0;
 }
 
@@ -1169,6 +1119,7 @@ static int gemm_tc_impl(const void* x, long long ldx, const void* w, long long l
         a.prep_x = f->prep_x; a.ldp = f->ldp; a.prep_g = f->prep_g; a.prep_ssq = f->prep_ssq;
     }
     if (pair_mode_on() && M >= 256 && splits == 1) {
+        if (a.row_ssq != nullptr) return MF_ERR_UNSUPPORTED;     // the CTA-pair kernel applies no row scale
         const int pnt = pair_token_tile(M, N);
         if (int e = make_map(&mx, x, M, K, ldx, pnt / 2)) return e;
         switch (pnt) {
@@ -1185,9 +1136,11 @@ static int gemm_tc_impl(const void* x, long long ldx, const void* w, long long l
         // few tokens, the residual completed inside the product: K split over a cluster
         a.kblocks_per_split = (kblocks + CSPLIT - 1) / CSPLIT;
         switch (nt) {
-            case 16: return launch_cluster<16, 6>(mw, mx, a, stream);
-            case 32: return launch_cluster<32, 5>(mw, mx, a, stream);
-            default: return launch_cluster<64, 4>(mw, mx, a, stream);
+            // (a stage fewer than the kernel without a cluster: the buffer for the partial sums
+            // takes its place, two CTAs still share an SM)
+            case 16: return launch_cluster<16, 5>(mw, mx, a, stream);
+            case 32: return launch_cluster<32, 4>(mw, mx, a, stream);
+            default: return launch_cluster<64, 3>(mw, mx, a, stream);
         }
     }
     a.partial = workspace;

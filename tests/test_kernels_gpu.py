@@ -699,10 +699,10 @@ def _norm_ref(h, g, eps):
 @pytest.mark.parametrize("m", [1, 8, 17, 64, 300, 700])
 @pytest.mark.parametrize("n,k", [(3584, 3584), (896, 4864), (200, 1024), (64, 128), (384, 264)])
 def test_product_that_completes_the_residual_and_prepares_the_next_norm(m, n, k):
-    """EPI_ACCUM with the next norm folded in (K split over a cluster for few tokens, the
-    CTA-pair kernel's epilogue for many): the residual, x' = bfloat16(h * g) and the sums of
-    squares against float64; then a product that reads x' with the row scale against
-    norm-then-product in float64."""
+    """EPI_ACCUM with the next norm folded in (few tokens: K split over a cluster of CTAs that add
+    their tiles through distributed shared memory; many tokens: refused, the norm stays a
+    kernel): the residual, x' = bfloat16(h * g) and the sums of squares against float64; then a
+    product that reads x' with the row scale against norm-then-product in float64."""
     from minfer_b200.kernels import api as K
     g0 = torch.Generator().manual_seed(m + n + k)
     x = (torch.randn(m, k, generator=g0) * 0.5).bfloat16().cuda()
