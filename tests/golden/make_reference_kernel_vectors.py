@@ -1,7 +1,12 @@
 """Makes ``reference_kernels.npz``: outputs of the reference's own float32 CUDA kernels
 (src/cuda_kernels.cu of yusiwen/minfer: rms_norm_f32, rope_f32, swiglu_f32, gqa_attn_f32 with
-store_kv_f32) on small seeded inputs, against which ``tests/test_plain.py`` checks the plain
-implementation's functions.  The reference's model code is Rust and cannot be built here; its
+store_kv_f32, add_bias_f32, add_f32) on small seeded inputs, against which
+``tests/test_plain.py`` checks the plain implementation's functions, and one whole layer
+chained through those launchers in the order of the reference's graph
+(src/models/qwen2/graph.rs:63-176: norm, projections, bias, rotation of q and k, cache store,
+attention, output projection, residual, norm, SwiGLU, residual; the matrix products, which the
+reference does with quantized kernels, are float64 products on the host), against which it
+checks the plain model's composition.  The reference's model code is Rust and cannot be built here; its
 CUDA kernels are plain C and can.
 
     nvcc -shared -Xcompiler -fPIC -gencode arch=compute_100a,code=sm_100a -O2 \\
@@ -32,7 +37,74 @@ def inputs():
     # attention: one sequence of 70 tokens at positions 0..69, 6 heads on 2 key/value heads of 32
     cases["attention"] = {"q": torch.randn(70, 6, 32, generator=g), "k": torch.randn(70, 2, 32, generator=g),
                           "v": torch.randn(70, 2, 32, generator=g), "scale": 1.0 / 32 ** 0.5}
+    cases["layer"] = layer_case(g)
     return cases
+
+
+LAYER = {"hidden": 64, "heads": 4, "kv_heads": 2, "head_dim": 16, "ffn": 96, "tokens": 20,
+         "theta": 10000.0, "eps": 1e-6}
+
+
+def layer_case(g):
+    """One layer's weights and input rows (float32, seeded)."""
+    c = LAYER
+    ne, nh, nk, hd, nf, T = c["hidden"], c["heads"], c["kv_heads"], c["head_dim"], c["ffn"], c["tokens"]
+
+    def r(*shape, std=0.3):
+        return torch.randn(*shape, generator=g) * std
+    return {"h0": r(T, ne, std=1.0), "ln1": 1.0 + r(ne, std=0.1), "ln2": 1.0 + r(ne, std=0.1),
+            "final": 1.0 + r(ne, std=0.1),
+            "wq": r(nh * hd, ne), "bq": r(nh * hd), "wk": r(nk * hd, ne), "bk": r(nk * hd),
+            "wv": r(nk * hd, ne), "bv": r(nk * hd), "wo": r(ne, nh * hd),
+            "wg": r(nf, ne), "wu": r(nf, ne), "wd": r(ne, nf)}
+
+
+def host_product(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x W^T in float64 on the host, rounded once to float32 (the same on every machine)."""
+    return (x.double().cpu() @ w.double().cpu().t()).float()
+
+
+def run_layer(lib, c, dev, stream):
+    """The layer through the reference's launchers; returns the normed output rows [T, hidden]."""
+    L = LAYER
+    ne, nh, nk, hd, nf, T = L["hidden"], L["heads"], L["kv_heads"], L["head_dim"], L["ffn"], L["tokens"]
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    h0 = c["h0"].to(dev)
+
+    def norm(x, w):
+        y = torch.empty_like(x)
+        lib.launch_rms_norm_f32(x.data_ptr(), w.to(dev).data_ptr(), y.data_ptr(), ne, L["eps"], T, stream)
+        torch.cuda.synchronize()
+        return y
+
+    def biased(x, w, b):
+        y = host_product(x, w).to(dev).contiguous()
+        lib.launch_add_bias_f32(y.data_ptr(), b.to(dev).data_ptr(), y.shape[1], T, stream)
+        return y
+    x = norm(h0, c["ln1"])
+    q, k, v = biased(x, c["wq"], c["bq"]), biased(x, c["wk"], c["bk"]), biased(x, c["wv"], c["bv"])
+    lib.launch_rope_f32(q.data_ptr(), nh, hd, T, L["theta"], 1.0, pos.data_ptr(), stream)
+    lib.launch_rope_f32(k.data_ptr(), nk, hd, T, L["theta"], 1.0, pos.data_ptr(), stream)
+    kc = torch.zeros(32, nk * hd, device=dev)
+    vc = torch.zeros_like(kc)
+    lib.launch_store_kv_f32(k.data_ptr(), kc.data_ptr(), nk * hd, T, pos.data_ptr(), stream)
+    lib.launch_store_kv_f32(v.data_ptr(), vc.data_ptr(), nk * hd, T, pos.data_ptr(), stream)
+    o = torch.empty(T, nh * hd, device=dev)
+    lib.launch_gqa_attn_f32(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), o.data_ptr(), pos.data_ptr(),
+                            nh, nk, hd, 1.0 / hd ** 0.5, T, stream)
+    torch.cuda.synchronize()
+    a = host_product(o, c["wo"]).to(dev).contiguous()
+    h1 = torch.empty_like(h0)
+    lib.launch_add_f32(h0.data_ptr(), a.data_ptr(), h1.data_ptr(), h0.numel(), stream)
+    x2 = norm(h1, c["ln2"])
+    gate, up = host_product(x2, c["wg"]).to(dev).contiguous(), host_product(x2, c["wu"]).to(dev).contiguous()
+    act = torch.empty_like(gate)
+    lib.launch_swiglu_f32(gate.data_ptr(), up.data_ptr(), act.data_ptr(), gate.numel(), stream)
+    torch.cuda.synchronize()
+    d = host_product(act, c["wd"]).to(dev).contiguous()
+    h2 = torch.empty_like(h0)
+    lib.launch_add_f32(h1.data_ptr(), d.data_ptr(), h2.data_ptr(), h1.numel(), stream)
+    return o.cpu().numpy(), h2.cpu().numpy(), norm(h2, c["final"]).cpu().numpy()
 
 
 def main(lib_path: str, out_path: str) -> int:
@@ -43,6 +115,8 @@ def main(lib_path: str, out_path: str) -> int:
     lib.launch_swiglu_f32.argtypes = [vp, vp, vp, ci, vp]
     lib.launch_store_kv_f32.argtypes = [vp, vp, ci, ci, vp, vp]
     lib.launch_gqa_attn_f32.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, cf, ci, vp]
+    lib.launch_add_bias_f32.argtypes = [vp, vp, ci, ci, vp]
+    lib.launch_add_f32.argtypes = [vp, vp, vp, ci, vp]
     c = inputs()
     out = {}
     dev = "cuda:0"
@@ -80,6 +154,7 @@ def main(lib_path: str, out_path: str) -> int:
                             nh, nk, hd, a["scale"], T, stream)
     torch.cuda.synchronize()
     out["attention"] = o.cpu().numpy()
+    out["layer_attention"], out["layer_residual"], out["layer_normed"] = run_layer(lib, c["layer"], dev, stream)
     np.savez_compressed(out_path, **out)
     print("wrote", out_path)
     return 0

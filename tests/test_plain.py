@@ -136,3 +136,50 @@ def test_parts_agree_with_the_references_own_cuda_kernels():
     assert err(g / (1.0 + torch.exp(-g)) * u, "swiglu") < 1e-6
     c = cases["attention"]
     assert err(P.attention(c["q"].double(), c["k"].double(), c["v"].double(), c["scale"]), "attention") < 2e-6
+
+
+def test_a_whole_layer_agrees_with_the_references_kernels_chained_in_its_order():
+    """The plain model's composition (bias before the rotation, q and k rotated but not v, keys
+    and values read back by position, attention, output projection added to the layer's input,
+    second norm, SwiGLU, second residual, final norm) against the reference's own CUDA kernels
+    launched in the order of its graph (src/models/qwen2/graph.rs:63-176) on one seeded layer.
+    The plain side sees the layer as a one-layer model whose embedding rows are the layer's
+    input rows and whose head is the identity, so its logits are the normed output rows."""
+    import importlib.util
+    import os
+
+    import numpy as np
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location(
+        "make_reference_kernel_vectors", os.path.join(here, "golden", "make_reference_kernel_vectors.py"))
+    maker = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(maker)
+    c = {k: v.double() for k, v in maker.inputs()["layer"].items()}
+    gold = np.load(os.path.join(here, "golden", "reference_kernels.npz"))
+    L = maker.LAYER
+    T, ne = L["tokens"], L["hidden"]
+    cfg = {"num_hidden_layers": 1, "hidden_size": ne, "num_attention_heads": L["heads"],
+           "num_key_value_heads": L["kv_heads"], "intermediate_size": L["ffn"], "vocab_size": T,
+           "rope_theta": L["theta"], "rms_norm_eps": L["eps"], "tie_word_embeddings": False}
+    p = "model.layers.0."
+    w = {"model.embed_tokens.weight": c["h0"], "lm_head.weight": torch.eye(ne, dtype=torch.float64),
+         "model.norm.weight": c["final"], p + "input_layernorm.weight": c["ln1"],
+         p + "post_attention_layernorm.weight": c["ln2"],
+         p + "self_attn.q_proj.weight": c["wq"], p + "self_attn.q_proj.bias": c["bq"],
+         p + "self_attn.k_proj.weight": c["wk"], p + "self_attn.k_proj.bias": c["bk"],
+         p + "self_attn.v_proj.weight": c["wv"], p + "self_attn.v_proj.bias": c["bv"],
+         p + "self_attn.o_proj.weight": c["wo"], p + "mlp.gate_proj.weight": c["wg"],
+         p + "mlp.up_proj.weight": c["wu"], p + "mlp.down_proj.weight": c["wd"]}
+    got = P.forward(cfg, w, list(range(T)))
+    want = torch.from_numpy(gold["layer_normed"]).double()
+    assert got.shape == want.shape
+    assert float((got - want).abs().max() / want.abs().max()) < 5e-6
+    # and the attention output alone (before the output projection)
+    x = P.rms_norm(c["h0"], c["ln1"], L["eps"])
+    hd = L["head_dim"]
+    q = P.rope_neox(P.linear(x, c["wq"], c["bq"]).reshape(T, L["heads"], hd), range(T), L["theta"])
+    k = P.rope_neox(P.linear(x, c["wk"], c["bk"]).reshape(T, L["kv_heads"], hd), range(T), L["theta"])
+    v = P.linear(x, c["wv"], c["bv"]).reshape(T, L["kv_heads"], hd)
+    o = P.attention(q, k, v, 1.0 / hd ** 0.5).reshape(T, -1)
+    want_o = torch.from_numpy(gold["layer_attention"]).double()
+    assert float((o - want_o).abs().max() / want_o.abs().max()) < 5e-6
