@@ -95,6 +95,70 @@ def gemm_prefill_down(reps):
     _gemm(2048, NE, NF, K.EPI_ACCUM, reps)
 
 
+def _gemm_cluster(m, n, k, reps):
+    """A product that completes the residual and prepares the next norm (K split over a
+    cluster), then the product that applies the norm's 1/rms, as a decode step chains them."""
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    x = (torch.randn(m, k, device="cuda") * 0.5).bfloat16()
+    n_w = max(2, min(8, int(1.2e9 // (n * k * 2))))
+    ws = [(torch.randn(n, k, device="cuda") * 0.05).bfloat16() for _ in range(n_w)]
+    h = torch.zeros(m, n, device="cuda")
+    g = torch.ones(n, device="cuda")
+    parts = K.gemm_tc_prep_parts(m, n, k)
+    xp = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+    ssq = torch.empty(max(parts, 1), m, device="cuda")
+    state = {"i": 0}
+
+    def run():
+        K.gemm_tc_fused(x, ws[state["i"] % n_w], None, h, K.EPI_ACCUM, st, prep_x=xp, prep_weight=g,
+                        prep_ssq=ssq)
+        state["i"] += 1
+    us = _time(run, reps)
+    print(f"gemm_tc cluster m={m} n={n} k={k} parts={parts}: {us:.1f} us, "
+          f"{n * k * 2 / us / 1e3:.1f} GB/s of weights")
+
+
+def gemm_decode_cluster(reps):
+    """The down projection for 8 tokens, K split over clusters of 8 CTAs that add their tiles
+    through distributed shared memory, residual and next norm's input in the epilogue."""
+    _gemm_cluster(8, NE, NF, reps)
+
+
+def gemm_decode_cluster_o(reps):
+    """The output projection for 8 tokens in the same form (25.7 MB of weights)."""
+    _gemm_cluster(8, NE, NE, reps)
+
+
+def gemm_decode_cluster_m64(reps):
+    """The down projection for 64 tokens in the same form."""
+    _gemm_cluster(64, NE, NF, reps)
+
+
+def attention_portion(reps, old=2048, new=2048, heads=NH, kv=NK):
+    """Attention of a 2,048-token portion that goes on from 2,048 cached positions, on tcgen05
+    over the cache's pages (key tiles of two pages by TMA): 90 GFLOP."""
+    end = old + new
+    pages = (end + 63) // 64
+    kc = torch.randn(pages, kv, 64, HD, device="cuda").bfloat16()
+    vc = torch.randn(pages, kv, 64, HD, device="cuda").bfloat16()
+    table = torch.randperm(pages, device="cuda").to(torch.int32).reshape(1, pages)
+    q = torch.randn(new, heads, HD, device="cuda").bfloat16()
+    cu = torch.tensor([0, new], dtype=torch.int32, device="cuda")
+    seq_end = torch.tensor([end], dtype=torch.int32, device="cuda")
+    out = torch.empty(new, heads * HD, dtype=torch.bfloat16, device="cuda")
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    us = _time(lambda: K.attention_prefill_tc_paged(q, kc, vc, cu, seq_end, table, pages, 0, out, 1, new,
+                                                    heads, kv, HD, 0, 1 / math.sqrt(HD), st), reps)
+    flops = heads * 4 * HD * (new * old + new * (new + 1) / 2)
+    print(f"attention of a portion (tcgen05, paged) old={old} new={new} heads={heads}: {us:.1f} us, "
+          f"{flops / us / 1e6:.1f} TFLOP/s")
+
+
+def attention_portion_512_on_8k(reps):
+    """A 512-token portion onto 8,192 cached positions, 40 heads / 8 KV heads (the 14B shape)."""
+    attention_portion(reps, old=8192, new=512, heads=40, kv=8)
+
+
 def attention_decode(reps, batch=64, ctx=2048):
     """Decode attention of 64 sequences at 2,048 cached positions: reads 268 MB of K and V."""
     pos = torch.full((batch,), ctx, dtype=torch.int32, device="cuda")
@@ -201,6 +265,53 @@ def step_prefill(reps, layers=4):
     print(f"prefill step, {layers} layers, 2048 tokens: {us / 1e3:.2f} ms")
 
 
+def step_prefill_timeline(reps, layers=4):
+    """The kernels of one 2,048-token prompt step through 4 layers with their start and end
+    times, from CUPTI activity records."""
+    from torch.profiler import ProfilerActivity, profile
+    eng, cfg = _engine(layers)
+    ids = torch.randint(0, VOCAB, (2048,)).tolist()
+
+    def run():
+        s = eng.acquire()
+        eng.step([s], [ids])
+        eng.release(s)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        run()
+        torch.cuda.synchronize()
+    evs = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    evs.sort(key=lambda e: e.time_range.start)
+    t0, prev = evs[0].time_range.start, evs[0].time_range.start
+    print(f"{'kernel':46s} {'start':>8s} {'end':>8s} {'after the one before':>21s}")
+    for e in evs:
+        print(f"{e.name[:46]:46s} {e.time_range.start - t0:8.1f} {e.time_range.end - t0:8.1f} "
+              f"{e.time_range.end - max(prev, t0):21.1f}")
+        prev = max(prev, e.time_range.end)
+    print(f"step: {prev - t0:.1f} us")
+
+
+def step_portions(reps, layers=4):
+    """A 4,096-token prompt in two portions of 2,048 through 4 layers plus the head: the second
+    portion attends over the cache (tcgen05 over pages) where the first attends over itself."""
+    eng, cfg = _engine(layers)
+    ids = torch.randint(0, VOCAB, (4096,)).tolist()
+    times = {}
+    for name, cuts in (("whole", [4096]), ("two portions", [2048, 2048])):
+        def run():
+            s = eng.acquire()
+            at = 0
+            for n in cuts:
+                eng.step([s], [ids[at:at + n]])
+                at += n
+            eng.release(s)
+        times[name] = _time(run, reps, graph=False)
+    print(f"4,096-token prompt, {layers} layers: whole {times['whole'] / 1e3:.2f} ms, "
+          f"in two portions {times['two portions'] / 1e3:.2f} ms")
+
+
 def step_decode(reps, layers=4, batch=8):
     """Decode steps of 8 sequences at 2,048 positions through 4 layers plus the head."""
     eng, cfg = _engine(layers, max_tokens=batch * 2304, max_seqs=batch)
@@ -270,10 +381,12 @@ def step_decode_small(reps, layers=24):
 
 
 CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_decode_m64, gemm_decode_split_m64, gemm_prefill, gemm_prefill_down,
+                                 gemm_decode_cluster, gemm_decode_cluster_o, gemm_decode_cluster_m64,
                                  attention_decode, attention_decode_b8, attention_decode_long, attention_prefill,
                                  attention_prefill_tc, attention_prefill_tc_8k, attention_prefill_8k,
-                                 step_prefill, step_decode, step_decode_timeline, step_decode_timeline_b64, step_decode_b64,
-                                 step_decode_small)}
+                                 attention_portion, attention_portion_512_on_8k,
+                                 step_prefill, step_prefill_timeline, step_portions, step_decode, step_decode_timeline,
+                                 step_decode_timeline_b64, step_decode_b64, step_decode_small)}
 
 
 def main(argv=None) -> int:
