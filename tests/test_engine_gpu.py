@@ -353,3 +353,25 @@ def test_step_refusals():
     eng.check_status()
     with pytest.raises(CacheError, match="not held"):
         eng.release(b), eng.release(b)
+
+
+def test_whole_prompts_through_the_mma_twin_of_the_prompt_kernel(monkeypatch):
+    """``MINFER_B200_PROMPT_ATTENTION=mma`` puts whole prompts on the mma.sync kernel instead of
+    the tcgen05 one (both are held to float64 kernel by kernel); here the engine runs with it:
+    the same logits within bfloat16's tolerance, window and unequal batch included."""
+    import minfer_b200.parts.attention as attention_part
+    folder = make_folder("D")
+    cfg, w = P.load_folder(folder)
+    prompts = [random_ids(n, cfg["vocab_size"], 50 + n) for n in (300, 65, 1)]
+    want = torch.cat([P.forward(cfg, w, ids) for ids in prompts])
+    outs = {}
+    for kind in ("tcgen05", "mma"):
+        monkeypatch.setattr(attention_part, "PROMPT_ATTENTION", kind)
+        eng = _engine(folder, "bfloat16")
+        slots = [eng.acquire() for _ in prompts]
+        outs[kind] = eng.step(slots, prompts, [list(range(len(p))) for p in prompts])
+        eng.check_status()
+    for kind, got in outs.items():
+        err, bound = logits_err(got, want, "bfloat16")
+        assert err < bound, (kind, err)
+    assert not torch.equal(outs["mma"], outs["tcgen05"])       # two kernels really ran
