@@ -375,3 +375,58 @@ def test_whole_prompts_through_the_mma_twin_of_the_prompt_kernel(monkeypatch):
         err, bound = logits_err(got, want, "bfloat16")
         assert err < bound, (kind, err)
     assert not torch.equal(outs["mma"], outs["tcgen05"])       # two kernels really ran
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,seed", [("B", 1), ("D", 2), ("C", 3), ("F", 4)])
+def test_random_schedules_of_any_cut(name, seed, dtype):
+    """Seeded random schedules: up to five requests live at once, each fed in random portions
+    (1 to 90 tokens, often 1), requests starting in steps where others go on, ending at different
+    steps, their slots and pages taken by later ones; every step's wanted places (a random
+    subset, in random order) against the plain implementation.  Rings of the windowed
+    configurations are short here (one page of slack), so long portions also run in passes."""
+    import random
+    from minfer_b200.engine.step import Engine
+    from minfer_b200.model import Model
+    rng = random.Random(seed)
+    folder = make_folder(name)
+    cfg, w = P.load_folder(folder)
+    V = cfg["vocab_size"]
+    eng = Engine(Model.from_folder(folder, dtype, "cuda:0"), max_tokens=2048, max_seqs=5,
+                 ring_step_tokens=40)
+    requests = []
+    for i in range(9):
+        ids = random_ids(rng.choice([1, 3, 40, 64, 65, 130, 200, 257]), V, 1000 * seed + i)
+        requests.append({"ids": ids, "plain": P.forward(cfg, w, ids), "at": 0, "slot": None})
+    waiting, live, worst = list(range(len(requests))), [], 0.0
+    while waiting or live:
+        while waiting and len(live) < 5 and (not live or rng.random() < 0.5):
+            r = waiting.pop(0)
+            requests[r]["slot"] = eng.acquire()
+            live.append(r)
+        rows = [r for r in live if rng.random() < 0.8] or live[:1]
+        rng.shuffle(rows)
+        tokens, want, expect = [], [], []
+        for r in rows:
+            q = requests[r]
+            left = len(q["ids"]) - q["at"]
+            n = min(left, 1 if rng.random() < 0.4 else rng.randint(1, 90))
+            tokens.append(q["ids"][q["at"]:q["at"] + n])
+            places = rng.sample(range(n), rng.randint(0, min(n, 4)))
+            want.append(places)
+            expect += [q["plain"][q["at"] + p] for p in places]
+            q["at"] += n
+        out = eng.step([requests[r]["slot"] for r in rows], tokens, want)
+        assert out.shape[0] == len(expect)
+        if expect:
+            err, bound = logits_err(out, torch.stack(expect), dtype)
+            assert err < bound, (name, dtype, err, [len(t) for t in tokens])
+            worst = max(worst, err)
+        for r in list(live):
+            if requests[r]["at"] == len(requests[r]["ids"]):
+                eng.release(requests[r]["slot"])
+                live.remove(r)
+    assert all(n == g.n_pages for n, g in zip(eng.cache.free_pages(), eng.cache.groups))
+    assert eng.cache.slots.n_free() == 5
+    eng.check_status()
+    eng.cache.check_canaries()
