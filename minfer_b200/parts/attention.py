@@ -44,8 +44,11 @@ def decode_ctas(device: Optional[torch.device] = None) -> int:
 FORCE_GENERIC_ATTENTION = os.environ.get("MINFER_B200_GENERIC_ATTENTION", "0") == "1"
 # a step that is neither whole prompts nor one token a row runs the tcgen05 kernel over the
 # cache's pages from this many tokens on; below, every token is a row of the decode kernel
-# (a query tile of 128 rows for a handful of tokens wastes the tensor cores' time)
-PAGED_PROMPT_MIN_TOKENS = int(os.environ.get("MINFER_B200_PAGED_PROMPT_MIN_TOKENS", "1"))
+# (a query tile of 128 rows for a handful of tokens wastes the tensor cores' time, and few
+# rows give that kernel few CTAs).  Measured at 2,048 cached positions, 4 layers of the 7B
+# shape: 8 rows x 16 tokens 1.17 ms against 1.06 with the decode kernel, 8 x 32 1.46 against
+# 1.76, 7 rows of one token beside one of 512 2.17 against 2.98.
+PAGED_PROMPT_MIN_TOKENS = int(os.environ.get("MINFER_B200_PAGED_PROMPT_MIN_TOKENS", "160"))
 # "tcgen05" (tensor memory, the default) or "mma" (the mma.sync twin) for whole prompts in bfloat16
 PROMPT_ATTENTION = os.environ.get("MINFER_B200_PROMPT_ATTENTION", "tcgen05")
 

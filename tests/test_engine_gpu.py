@@ -238,6 +238,28 @@ def test_prompt_in_portions(tiny_cuts, dtype, sizes):
     eng.check_status()
 
 
+@pytest.mark.parametrize("min_tokens", [1, 10 ** 9])
+def test_portions_through_either_attention_kernel(tiny_cuts, min_tokens, monkeypatch):
+    """A bfloat16 step over the cache runs the tcgen05 kernel over pages from some number of
+    tokens on and the decode kernel (a row per token) below; here each of them takes all
+    portions, small and large, and the mixed step."""
+    import minfer_b200.parts.attention as attention_part
+    monkeypatch.setattr(attention_part, "PAGED_PROMPT_MIN_TOKENS", min_tokens)
+    eng = _engine(tiny_cuts["folder"], "bfloat16")
+    for ids, want in zip(tiny_cuts["prompts"], tiny_cuts["plain"]):
+        for sizes in ([7], [100, 3, 64]):
+            got = _in_portions(eng, ids, sizes)
+            assert _close(got, want, "bfloat16"), (tiny_cuts["name"], len(ids), sizes, min_tokens)
+    p, plain = tiny_cuts["prompts"], tiny_cuts["plain"]
+    a, b = eng.acquire(), eng.acquire()
+    eng.step([a], [p[1][:200]])
+    out = eng.step([a, b], [[p[1][200]], p[0][:90]], [[0], [89, 5]])
+    assert _close(out, torch.stack([plain[1][200], plain[0][89], plain[0][5]]), "bfloat16")
+    out = eng.step([b, a], [p[0][90:130], p[1][201:204]], [[39], [2]])
+    assert _close(out, torch.stack([plain[0][129], plain[1][203]]), "bfloat16")
+    eng.check_status()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_short_rings_run_long_portions_in_passes(tiny_cuts, dtype):
     """Rings no longer than the window's pages: a portion longer than a ring takes is run in
