@@ -81,6 +81,10 @@ class ModelPlan:
     schedule: Sequence[LayerCall]
     max_positions: int
     stop_token_ids: Sequence[int] = ()
+    # what some architectures do around the blocks (this one does neither): a factor on the
+    # embedding rows as they enter the residual stream, a bias added to the logits
+    embedding_scale: float = 1.0
+    head_bias_name: Optional[str] = None
 
     def validate(self) -> None:
         if self.vocab_size <= 0 or self.hidden_size <= 0:

@@ -10,11 +10,12 @@
 #include "common.cuh"
 
 // ------------------------------------------------------------------------------------
-// embedding: out[t][:] = table[ids[t]][:]  (float32 out: the residual stream is float32)
+// embedding: out[t][:] = table[ids[t]][:] * scale  (float32 out: the residual stream is
+// float32; scale is 1 for architectures that do not multiply their embeddings)
 // ------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                             float* __restrict__ out, int width, int vocab,
+                             float* __restrict__ out, int width, int vocab, float scale,
                              unsigned* __restrict__ status) {
     pdl_prologue();
     const int t = blockIdx.x;
@@ -26,20 +27,20 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
         return;
     }
     const T* row = table + (size_t)id * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32(row[i]);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
 }
 
 extern "C" int mf_embed(const void* table, int table_dtype, const int* ids, float* out,
-                        int n_tokens, int width, int vocab, unsigned* status,
+                        int n_tokens, int width, int vocab, float scale, unsigned* status,
                         cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     if (table_dtype == MF_DTYPE_F32)
         mf_launch(embed_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, ids, out, width,
-                                                             vocab, status);
+                                                             vocab, scale, status);
     else if (table_dtype == MF_DTYPE_BF16)
         mf_launch(embed_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, 
-            (const __nv_bfloat16*)table, ids, out, width, vocab, status);
+            (const __nv_bfloat16*)table, ids, out, width, vocab, scale, status);
     else
         return MF_ERR_UNSUPPORTED;
     return MF_LAUNCH_CHECK();

@@ -430,7 +430,7 @@ class Engine:
         model, plan = self.model, self.model.plan
         gemm.use_status_word(self.status)           # this engine's products report into its word
         h = torch.empty((ctx.n_tokens, plan.hidden_size), dtype=torch.float32, device=self.device)
-        K.embed(model.embedding, ctx.token_ids, h, self.status)
+        K.embed(model.embedding, ctx.token_ids, h, self.status, plan.embedding_scale)
         bindings = self._bindings(ctx)
         last = len(plan.schedule) - 1
         n_want = 0 if want_rows is None else want_rows.numel()

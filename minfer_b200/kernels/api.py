@@ -94,8 +94,8 @@ def _lib(name: str) -> ctypes.CDLL:
 
 
 def _sig_ops(lib: ctypes.CDLL) -> None:
-    lib.mf_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
-                             c_void_p]
+    lib.mf_embed.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
+                             c_void_p, c_void_p]
     lib.mf_rmsnorm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float,
                                c_void_p]
     lib.mf_rope_kvstore.argtypes = ([c_void_p, c_int, c_void_p] + [c_void_p] * 10 + [c_int] * 9 +
@@ -162,14 +162,16 @@ _SIGNATURES = {"attention_prefill_tc": _sig_attention_prefill_tc,
 # ---------------------------------------------------------------------------------------
 # row-wise ops
 # ---------------------------------------------------------------------------------------
-def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+def embed(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor,
+          scale: float = 1.0) -> None:
+    """out[t] = table[ids[t]] * scale in float32; an id outside the table sets status bit 1."""
     n, width = out.shape
     vocab = table.shape[0]
     if table.shape[1] != width or ids.numel() != n:
         raise KernelError("embed: shapes do not fit")
     _check(_lib("ops").mf_embed(_ptr(table, "table"), dtype_code(table.dtype), _i32(ids, "ids"),
-                                _f32(out, "out"), n, width, vocab, _i32(status, "status"),
-                                _stream()), "embed")
+                                _f32(out, "out"), n, width, vocab, float(scale),
+                                _i32(status, "status"), _stream()), "embed")
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,

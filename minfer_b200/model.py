@@ -22,7 +22,7 @@ from .parts.linear import Linear
 from .registry import build_part, plan_from_config, read_config
 from .weights.loader import held_dtype, load_weights
 from .weights.random_init import random_tensor, write_model_folder
-from .weights.spec import MATRIX, Init, TensorSpec
+from .weights.spec import MATRIX, VECTOR, Init, TensorSpec
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
           "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -58,6 +58,8 @@ class Model:
         if p.head_name is not None:
             specs.append(TensorSpec(p.head_name, (p.vocab_size, p.hidden_size), MATRIX,
                                     Init(0.0, 0.02)))
+        if p.head_bias_name is not None:
+            specs.append(TensorSpec(p.head_bias_name, (p.vocab_size,), VECTOR, Init(0.0, 0.02)))
         names = [s.name for s in specs]
         if len(set(names)) != len(names):
             dup = sorted({n for n in names if names.count(n) > 1})
@@ -79,7 +81,7 @@ class Model:
             block.load("", weights)
         self.final_norm.load(p.final_norm_prefix, weights)
         head_w = self.embedding if p.head_name is None else weights[p.head_name]
-        self.head = Linear(head_w)
+        self.head = Linear(head_w, weights[p.head_bias_name] if p.head_bias_name is not None else None)
         return self
 
     @classmethod
@@ -154,6 +156,8 @@ class Model:
         out.update(self.final_norm.export(p.final_norm_prefix))
         if p.head_name is not None:
             out[p.head_name] = self.head.weight
+        if p.head_bias_name is not None:
+            out[p.head_bias_name] = self.head.bias
         return out
 
     # ---- sizes ----------------------------------------------------------------------------

@@ -35,6 +35,8 @@ def test_embed_and_bad_token_flag():
         st = status()
         K.embed(table, ids, out, st)
         assert torch.equal(out, table.float()[ids.long()]) and int(st) == 0
+        K.embed(table, ids, out, st, scale=2.5)
+        assert torch.equal(out, table.float()[ids.long()] * 2.5) and int(st) == 0
     bad = torch.tensor([3, 131], dtype=torch.int32, device="cuda")
     out = torch.full((2, 72), 9.0, device="cuda")
     K.embed(table, bad, out, st)

@@ -102,9 +102,12 @@ def _register():
                        else PartSpec("gated_mlp", dict(hidden_size=self.width, intermediate_size=40)))
                 layers.append(LayerSpec(f"toy.{l}.", PartSpec("pre_norm", {}), mixer,
                                         norm.with_params(name="n1"), ffn, norm.with_params(name="n2")))
+            # the embedding rows are multiplied by 3 on their way in and the logits get a bias:
+            # hooks of the plan that the shipped architecture leaves at their defaults
             return ModelPlan("ToyStateLM", self.vocab, self.width, "toy.embed", None,
                              norm.with_params(name="final"), "toy.", layers,
-                             default_schedule(self.layers), 4096, ())
+                             default_schedule(self.layers), 4096, (), embedding_scale=3.0,
+                             head_bias_name="toy.head_bias")
 
     registry.register_part("mixer", "toy_decay", DecayMixer, replace=True)
     registry.register_part("feed_forward", "toy_square", SquareFeedForward, replace=True)
@@ -120,7 +123,7 @@ def _reference(w, ids):
     """The toy model in float64, whole sequence."""
     def norm(x, wt):
         return x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5) * wt
-    h = w["toy.embed"][torch.tensor(ids)]
+    h = w["toy.embed"][torch.tensor(ids)] * 3.0
     T = len(ids)
     for l in range(3):
         p = f"toy.{l}."
@@ -150,7 +153,7 @@ def _reference(w, ids):
         else:
             g, u = x @ w[p + "mlp.gate_proj.weight"].t(), x @ w[p + "mlp.up_proj.weight"].t()
             h = h + (torch.nn.functional.silu(g) * u) @ w[p + "mlp.down_proj.weight"].t()
-    return norm(h, w["toy.final.weight"]) @ w["toy.embed"].t()
+    return norm(h, w["toy.final.weight"]) @ w["toy.embed"].t() + w["toy.head_bias"]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
