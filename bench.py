@@ -323,7 +323,10 @@ def point_long(engine, torch, K, pk, cfg, context=32000, steps=32):
 
 
 REF_KERNELS = os.path.join(ROOT, "baseline", "_ref", "libref_kernels.so")
-REF_SOURCE = "/root/reference/src/cuda_kernels.cu"
+# the reference's checkout, if it sits beside this repository (or where MINFER_REFERENCE_DIR says)
+REF_SOURCE = os.path.join(os.environ.get("MINFER_REFERENCE_DIR",
+                                         os.path.join(os.path.dirname(ROOT), "reference")),
+                          "src", "cuda_kernels.cu")
 
 
 def reference_kernel_times(torch, K):
