@@ -396,7 +396,8 @@ def test_whole_prompts_through_the_mma_twin_of_the_prompt_kernel(monkeypatch):
     for kind, got in outs.items():
         err, bound = logits_err(got, want, "bfloat16")
         assert err < bound, (kind, err)
-    assert not torch.equal(outs["mma"], outs["tcgen05"])       # two kernels really ran
+    if not attention_part.FORCE_GENERIC_ATTENTION:
+        assert not torch.equal(outs["mma"], outs["tcgen05"])   # two kernels really ran
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
