@@ -265,10 +265,12 @@ class Engine:
         return logits
 
     # ---- metadata -----------------------------------------------------------------------
-    def _host_fields(self, slots, tokens, counts, starts, want, widths):
+    def _host_fields(self, slots, tokens, counts, starts, want, widths, order=None):
         """The step's integers, field by field: tokens, positions, batch row of each token,
         cu_seqlens, lengths after the step, slots, wanted rows, then one page table per cache
-        group (``widths[g]`` entries a row, -1 where a sequence has no page)."""
+        group (``widths[g]`` entries a row, -1 where a sequence has no page).  ``order``: the
+        rows are given in another order than the caller's; ``order[i]`` is the row here that
+        was the caller's row ``i``, and the wanted rows are listed in the caller's order."""
         n_rows = len(slots)
         if all(c == 1 for c in counts) and all(len(w) == 1 and w[0] == 0 for w in want):
             # one token a row, each row's logits wanted (decoding): no loop over the rows' tokens
@@ -278,14 +280,16 @@ class Engine:
             for g, width in zip(self.cache.groups, widths):
                 fields.append(g.table_flat(slots, width))
             return fields
-        flat_tokens, positions, token_row, cu, want_rows = [], [], [], [0], []
-        for b in range(n_rows):
-            base = cu[-1]
+        flat_tokens, positions, token_row, cu, base_of = [], [], [], [0], {}
+        for b in range(n_rows):                       # (rows may have been reordered by the caller)
+            base_of[b] = cu[-1]
             flat_tokens.extend(int(t) for t in tokens[b])
             positions.extend(range(starts[b], starts[b] + counts[b]))
             token_row.extend([b] * counts[b])
-            cu.append(base + counts[b])
-            want_rows.extend(base + int(w) for w in want[b])
+            cu.append(cu[-1] + counts[b])
+        want_rows = []
+        for b in (order if order is not None else range(n_rows)):
+            want_rows.extend(base_of[b] + int(w) for w in want[b])
         seq_end = [starts[b] + counts[b] for b in range(n_rows)]
         fields = [flat_tokens, positions, token_row, cu, seq_end, list(slots), want_rows]
         for g, width in zip(self.cache.groups, widths):
@@ -312,8 +316,24 @@ class Engine:
         return ctx
 
     def _context(self, slots, tokens, counts, starts, want, from_start, single):
+        # A step in which some rows bring one token and others more: the one-token rows go first,
+        # so that a mixer can hand them to its decode kernel as one contiguous stretch of tokens
+        # and the others to its kernel for portions.  Rows are independent, so their order in
+        # the step is the engine's to choose; the logits still come back in the caller's order.
+        order, n_single = None, 0
+        if not from_start and not single:
+            n_single = sum(1 for c in counts if c == 1)
+            if 0 < n_single < len(slots):
+                perm = sorted(range(len(slots)), key=lambda b: counts[b] != 1)      # stable
+                order = [0] * len(slots)
+                for here, b in enumerate(perm):
+                    order[b] = here
+                slots, tokens, counts, starts, want = ([x[b] for b in perm] for x in
+                                                       (slots, tokens, counts, starts, want))
+            else:
+                n_single = 0
         widths = [max(1, g.max_pages_of(slots)) for g in self.cache.groups]
-        fields = self._host_fields(slots, tokens, counts, starts, want, widths)
+        fields = self._host_fields(slots, tokens, counts, starts, want, widths, order)
         sizes = [len(f) for f in fields]
         host = torch.tensor([x for f in fields for x in f], dtype=torch.int32).pin_memory()
         dev = host.to(self.device, non_blocking=True)
@@ -323,6 +343,7 @@ class Engine:
                              max(starts[b] + counts[b] for b in range(len(slots))))
         # every row wanted, in order (decoding): the last layer needs no row selection
         ctx.extras["want_is_identity"] = fields[6] == list(range(sum(counts)))
+        ctx.extras["single_rows"] = n_single          # rows of one token, first in the batch
         return ctx, (views[6] if sizes[6] else None)
 
     # ---- decode steps replayed as CUDA graphs -------------------------------------------------

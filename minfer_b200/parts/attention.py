@@ -227,28 +227,44 @@ class Attention(Mixer):
                     f"a sequence brings {ctx.max_row_tokens} tokens, but a ring of {cache.ring} "
                     f"positions with a window of {self.window} takes "
                     f"{cache.ring - self.window + 1} a step (the engine runs longer rows in portions)")
+            n_one = int(ctx.extras.get("single_rows", 0))      # rows of one token, first in the batch
             if (not ctx.single_token and PROMPT_ATTENTION != "mma" and not FORCE_GENERIC_ATTENTION
                     and K.attention_prefill_supported(q, nh, nk, hd)
-                    and ctx.n_tokens >= PAGED_PROMPT_MIN_TOKENS):
-                # several tokens a row: query tiles of the step's rows over the cache's pages
-                K.attention_prefill_tc_paged(q, cache.k, cache.v, ctx.cu_seqlens, ctx.seq_end,
-                                             cache.page_table, cache.table_stride, cache.ring, o,
-                                             ctx.n_rows, ctx.max_row_tokens, nh, nk, hd,
-                                             self.window, self.scale, ctx.status)
+                    and ctx.n_tokens - n_one >= PAGED_PROMPT_MIN_TOKENS):
+                # rows of several tokens: query tiles of the step's rows over the cache's pages
+                stride = cache.table_stride
+                K.attention_prefill_tc_paged(q, cache.k, cache.v, ctx.cu_seqlens[n_one:],
+                                             ctx.seq_end[n_one:], cache.page_table[n_one * stride:],
+                                             stride, cache.ring, o, ctx.n_rows - n_one,
+                                             ctx.max_row_tokens, nh, nk, hd, self.window, self.scale,
+                                             ctx.status)
+                if n_one:
+                    # the rows of one token beside them: the decode kernel, a row per token (each
+                    # is its sequence's only new token, so its older keys were there before the step)
+                    self._over_cache(q[:n_one], o[:n_one], ctx.token_row[:n_one], ctx.positions[:n_one],
+                                     cache, ctx, final=True)
                 self._project_out(o, ctx, residual)
                 return
-            chunk, n_chunks = decode_chunks(n * nk, ctx.max_end, tensor_cores=(
-                act == torch.bfloat16 and hd in (64, 128) and nh // nk <= 16
-                and not FORCE_GENERIC_ATTENTION))
-            partial = None
-            if n_chunks > 1 or act == torch.bfloat16:
-                partial = torch.empty((n * nh * n_chunks * (hd + 2),), dtype=torch.float32,
-                                      device=dev)
-            K.attention_paged(q, cache.k, cache.v, ctx.token_row, ctx.positions, cache.page_table,
-                              cache.table_stride, cache.ring, o, partial, nh, nk, hd, self.window,
-                              chunk, n_chunks, self.scale, force_generic=FORCE_GENERIC_ATTENTION,
-                              status=ctx.status, old_keys_final=ctx.single_token)
+            self._over_cache(q, o, ctx.token_row, ctx.positions, cache, ctx, final=ctx.single_token)
         self._project_out(o, ctx, residual)
+
+    def _over_cache(self, q: torch.Tensor, o: torch.Tensor, token_row: torch.Tensor,
+                    positions: torch.Tensor, cache, ctx: StepContext, final: bool) -> None:
+        """Every token of ``q`` a query at its position over the paged cache (key chunks and
+        their merge).  ``final``: each is its sequence's only new token in this step."""
+        n, act = q.shape[0], q.dtype
+        nh, nk, hd = self.n_heads, self.n_kv_heads, self.head_dim
+        chunk, n_chunks = decode_chunks(n * nk, ctx.max_end, tensor_cores=(
+            act == torch.bfloat16 and hd in (64, 128) and nh // nk <= 16
+            and not FORCE_GENERIC_ATTENTION))
+        partial = None
+        if n_chunks > 1 or act == torch.bfloat16:
+            partial = torch.empty((n * nh * n_chunks * (hd + 2),), dtype=torch.float32,
+                                  device=q.device)
+        K.attention_paged(q, cache.k, cache.v, token_row, positions, cache.page_table,
+                          cache.table_stride, cache.ring, o, partial, nh, nk, hd, self.window,
+                          chunk, n_chunks, self.scale, force_generic=FORCE_GENERIC_ATTENTION,
+                          status=ctx.status, old_keys_final=final)
 
     def _project_out(self, o: torch.Tensor, ctx: StepContext, residual: torch.Tensor) -> None:
         target = ctx.extras.pop("prepare_for", None)
