@@ -108,7 +108,10 @@ def settle_pending(ctx: "StepContext", h: torch.Tensor) -> None:
 class StepContext:
     """The batch of one step, as device tensors plus the few host numbers kernels need for
     their launch shape.  Row ``b`` of the batch is one sequence; tokens are packed row
-    after row."""
+    after row.  The engine may order the rows as it likes (logits go back in the caller's
+    order): in a step where some rows bring one token and others more, the one-token rows come
+    first and ``extras["single_rows"]`` says how many they are, so that a mixer can treat that
+    stretch of tokens with its kernel for single tokens."""
 
     device: torch.device
     act_dtype: torch.dtype
