@@ -323,6 +323,40 @@ def step_decode(reps, layers=4, batch=8):
     print(f"decode step, {layers} layers, batch {batch}: {us:.1f} us")
 
 
+def step_decode_sweep(reps, layers=28):
+    """Decode steps of the whole Qwen2.5-7B shape (28 layers) over batch sizes 1 to 128 and
+    contexts of 512 to 8,192 cached positions: time of a replayed step (median of `reps`, CUDA
+    events) and the bytes it has to read (weights once, the cache of the live rows) over that
+    time."""
+    import statistics
+    eng, cfg = _engine(layers, max_tokens=128 * 8192 + 128 * 512, max_seqs=128)
+    weights = eng.model.parameter_bytes() - eng.model.embedding.numel() * 2
+    kv_per_pos = layers * 2 * NK * HD * 2
+    print(f"{'batch':>6s} {'context':>8s} {'ms/step':>9s} {'tokens/s':>10s} {'GB/s':>8s}")
+    for ctx_len in (512, 2048, 8192):
+        for batch in (1, 4, 8, 16, 32, 64, 128):
+            slots = [eng.acquire() for _ in range(batch)]
+            for i in range(0, batch, 8):        # prompts of 8 sequences at a time
+                part = slots[i:i + 8]
+                eng.step(part, [torch.randint(0, VOCAB, (ctx_len,)).tolist() for _ in part])
+            tokens = torch.randint(0, VOCAB, (batch,), dtype=torch.int32, device="cuda")
+            for _ in range(4):
+                eng.decode_on_device(slots, tokens)
+            torch.cuda.synchronize()
+            marks = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+            marks[0].record()
+            for i in range(reps):
+                eng.decode_on_device(slots, tokens)
+                marks[i + 1].record()
+            torch.cuda.synchronize()
+            ms = statistics.median(marks[i].elapsed_time(marks[i + 1]) for i in range(reps))
+            nbytes = weights + batch * (ctx_len + 4 + reps / 2) * kv_per_pos
+            print(f"{batch:6d} {ctx_len:8d} {ms:9.3f} {batch / ms * 1e3:10.0f} {nbytes / ms / 1e6:8.0f}")
+            for s_ in slots:
+                eng.release(s_)
+    eng.check_status()
+
+
 def step_decode_timeline(reps, layers=4, batch=8):
     """The kernels of one replayed decode step (8 sequences at 2,048 positions, 4 layers) with
     their start and end times inside the graph, from CUPTI activity records."""
@@ -385,7 +419,7 @@ CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_decode_m64
                                  attention_decode, attention_decode_b8, attention_decode_long, attention_prefill,
                                  attention_prefill_tc, attention_prefill_tc_8k, attention_prefill_8k,
                                  attention_portion, attention_portion_512_on_8k,
-                                 step_prefill, step_prefill_timeline, step_portions, step_decode, step_decode_timeline,
+                                 step_prefill, step_prefill_timeline, step_portions, step_decode, step_decode_sweep, step_decode_timeline,
                                  step_decode_timeline_b64, step_decode_b64, step_decode_small)}
 
 
