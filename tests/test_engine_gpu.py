@@ -453,3 +453,27 @@ def test_random_schedules_of_any_cut(name, seed, dtype):
     assert eng.cache.slots.n_free() == 5
     eng.check_status()
     eng.cache.check_canaries()
+
+
+def test_matrices_stored_in_32_bit_stay_so_in_the_bfloat16_engine(capfd):
+    """A folder whose matrices are stored in float32: the bfloat16 engine keeps them as stored
+    (their products then run on the FP32 pipe with bfloat16 activations), says so once when it
+    loads them, and still gives the plain implementation's logits, whole and in portions."""
+    from minfer_b200.engine.step import Engine
+    from minfer_b200.model import Model
+    folder = make_folder("D", store_dtype="float32")
+    cfg, w = P.load_folder(folder)
+    model = Model.from_folder(folder, "bfloat16", "cuda:0")
+    err = capfd.readouterr().err
+    assert "stored in 32-bit" in err and "FP32 pipe" in err
+    assert model.blocks[0].mixer.qkv.weight.dtype == torch.float32
+    assert model.blocks[0].mixer.accepts_row_scale is False        # no tensor-core product to fold into
+    eng = Engine(model, max_tokens=1024)
+    ids = random_ids(150, cfg["vocab_size"], 77)
+    want = P.forward(cfg, w, ids)
+    s = eng.acquire()
+    got = torch.cat([eng.step([s], [ids[:100]], [list(range(100))]),
+                     eng.step([s], [ids[100:140]], [list(range(40))])] +
+                    [eng.step([s], [[t]]) for t in ids[140:]])
+    assert _close(got, want, "bfloat16")
+    eng.check_status()
