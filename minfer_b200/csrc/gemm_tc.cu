@@ -169,7 +169,6 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
 __device__ __forceinline__ void tc_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
-
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte
 // swizzle: 8-row groups 1024 bytes apart (SBO), version 1, layout type 2.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
@@ -213,6 +212,17 @@ __device__ __forceinline__ void store_chunk(const GemmArgs& a, const uint32_t* r
             const int tok = tok0 + 2 * jj + (even ? 0 : 1);
             if (tok < a.M && n_ok)
                 o[(size_t)(2 * jj) * a.ldo] = __float2bfloat16_rn(__fdividef(g * u, 1.0f + __expf(-g)));
+        }
+    } else if (a.epi == EPI_ACCUM && a.bias == nullptr) {
+        // out += acc as a reduction at the memory side: nothing comes back, so a chunk does not
+        // wait a round trip for the old values (each element gets exactly one add: same bits)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int tok = tok0 + j;
+            if (tok < a.M && n_ok)
+                asm volatile("red.global.add.f32 [%0], %1;"
+                             ::"l"((float*)a.out + (size_t)tok * a.ldo + n), "f"(__uint_as_float(r[j]))
+                             : "memory");
         }
     } else if (a.epi == EPI_ACCUM) {
         // all loads of the chunk first, so that they are in flight together
@@ -786,11 +796,23 @@ static int launch_cluster(const CUtensorMap& mw, const CUtensorMap& mx, const Ge
 //                        LEADER's (rank 0) "full" barrier, which the leader arms for both
 //   warp 1, one thread   MMA issuer, leader CTA only; tcgen05.commit multicasts to both CTAs'
 //                        "empty" barriers (stage free) and "accumulator full" barriers
-//   warps 2-5            epilogue of the CTA's own 128 accumulator rows; when done they arrive
-//                        on the leader's "accumulator empty" barrier (remote for rank 1)
+//   warps 2-9            epilogue of the CTA's own 128 accumulator rows: two groups of four warps
+//                        (a warp reads the 32 tensor-memory lanes of its index mod 4) that take
+//                        alternate 16-token chunks, each loading its next chunk from tensor memory
+//                        while it stores the one before; when done they arrive on the leader's
+//                        "accumulator empty" barrier (remote for rank 1)
 // No load is multicast: each CTA fetches its own tiles.
+//
+// DUAL: a pair takes two neighbouring token tiles of one weight tile at once.  A stage then
+// holds the 128 weight rows once and both token halves, every k-block feeds both accumulators,
+// and the operand bytes a pair pulls per flop fall by a quarter (256 + 2 NT rows instead of
+// 2 (256 + NT)).  The two accumulators are then both in use, so a tile's epilogue no longer
+// hides behind the next tile's main loop: the form is for products whose tiles make one or two
+// rounds over the pairs.  An element's sum is the same in either form (k ascending, one
+// accumulator).
 // ------------------------------------------------------------------------------------------
-#define PAIR_THREADS 192
+#define PAIR_THREADS 320
+#define PAIR_EPI_WARPS 8
 #define PEER_BIT_MASK 0xFEFFFFFFu      // clears the CTA-rank bit of a shared::cluster address
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -831,14 +853,16 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t cta_ra
         ::"r"(bar), "r"(cta_rank) : "memory");
 }
 
-template <int NT, int STAGES>
+template <int NT, int STAGES, bool DUAL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  const GemmArgs a, int tiles_m, int total_tiles) {
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int B_BYTES = (NT / 2) * TILE_K * 2;           // this CTA's half of the tokens
+    constexpr int HALF_B = (NT / 2) * TILE_K * 2;            // this CTA's half of one token tile
+    constexpr int B_BYTES = (DUAL ? 2 : 1) * HALF_B;
     constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int M_STEP = (DUAL ? 2 : 1) * NT;              // tokens a pair takes per tile of its walk
     constexpr int TMEM_COLS = 2 * NT <= 256 ? 256 : 512;      // two accumulators of NT columns (a power of two is allocated)
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -862,7 +886,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&acc_full[b]), 1);
-            mbar_init(smem_u32(&acc_empty[b]), 8);            // 4 epilogue warps of each CTA
+            mbar_init(smem_u32(&acc_empty[b]), 2 * PAIR_EPI_WARPS);   // the epilogue warps of both CTAs
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -884,17 +908,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         int it = 0;
         bool ok = true;
         for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
-            const int m0 = (tile % tiles_m) * NT, n0 = (tile / tiles_m) * 256;
+            const int m0 = (tile % tiles_m) * M_STEP, n0 = (tile / tiles_m) * 256;
+            const bool two = DUAL && m0 + NT < a.M;           // the second token tile has tokens
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (uint32_t)(it / STAGES) & 1u;
                 if (!mbar_wait(smem_u32(&empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
                 const uint32_t leader_full = smem_u32(&full[s]) & PEER_BIT_MASK;
-                if (rank == 0) mbar_expect_tx(smem_u32(&full[s]), 2 * STAGE_BYTES);
+                if (rank == 0)
+                    mbar_expect_tx(smem_u32(&full[s]), 2 * (A_BYTES + (two ? 2 : 1) * HALF_B));
                 const uint32_t dst = smem_u32(smem + s * STAGE_BYTES);
                 tma_load_2d_pair(dst, &map_w, kb * TILE_K, n0 + (int)rank * TILE_N, leader_full);
                 tma_load_2d_pair(dst + A_BYTES, &map_x, kb * TILE_K, m0 + (int)rank * (NT / 2),
                                  leader_full);
+                if (two)
+                    tma_load_2d_pair(dst + A_BYTES + HALF_B, &map_x, kb * TILE_K,
+                                     m0 + NT + (int)rank * (NT / 2), leader_full);
             }
         }
     } else if (warp == 1 && lane == 0 && rank == 0) {
@@ -904,8 +933,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         int it = 0, tile_i = 0;
         bool ok = true;
         for (int tile = pair; tile < total_tiles && ok; tile += n_pairs, ++tile_i) {
-            const int b = tile_i & 1;
-            const uint32_t u = (uint32_t)(tile_i >> 1);
+            // DUAL: both accumulators belong to this tile (barrier 0 stands for the two)
+            const int b = DUAL ? 0 : tile_i & 1;
+            const uint32_t u = (uint32_t)(DUAL ? tile_i : tile_i >> 1);
+            const bool two = DUAL && (tile % tiles_m) * M_STEP + NT < a.M;
             ok = mbar_wait(smem_u32(&acc_empty[b]), (u & 1u) ^ 1u, abort_flag);
             if (!ok) break;
             tc_fence_after();
@@ -918,10 +949,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 tc_fence_after();
                 const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
                 const uint64_t da = umma_desc(sa), db = umma_desc(sa + A_BYTES);
+                const uint64_t db2 = umma_desc(sa + A_BYTES + HALF_B);
 #pragma unroll
-                for (int k = 0; k < TILE_K / 16; ++k)
+                for (int k = 0; k < TILE_K / 16; ++k) {
                     tc_mma_pair(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc,
                                 (kb > 0 || k > 0) ? 1u : 0u);
+                    if (two)
+                        tc_mma_pair(tmem_d + (uint32_t)NT, da + (uint64_t)(2 * k),
+                                    db2 + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                }
                 tc_commit_pair(smem_u32(&empty[s]));
             }
             if (ok) tc_commit_pair(smem_u32(&acc_full[b]));
@@ -929,23 +965,34 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     } else if (warp >= 2) {
         // ---- epilogue: this CTA's 128 rows; warp w reads TMEM lanes 32*(w%4) .. ------------
         const int q = warp & 3;
+        const int group = (warp - 2) >> 2;            // 0 or 1
         int tile_i = 0;
         for (int tile = pair; tile < total_tiles; tile += n_pairs, ++tile_i) {
-            const int b = tile_i & 1;
-            const uint32_t u = (uint32_t)(tile_i >> 1);
-            const int m0 = (tile % tiles_m) * NT, n0 = (tile / tiles_m) * 256;
+            const int b = DUAL ? 0 : tile_i & 1;
+            const uint32_t u = (uint32_t)(DUAL ? tile_i : tile_i >> 1);
+            const int m0 = (tile % tiles_m) * M_STEP, n0 = (tile / tiles_m) * 256;
             if (!mbar_wait(smem_u32(&acc_full[b]), u & 1u, abort_flag)) break;
             tc_fence_after();
             const int n = n0 + (int)rank * TILE_N + q * 32 + lane;
             const bool n_ok = n < a.N;
             const float bias = (a.bias != nullptr && n_ok) ? a.bias[n] : 0.0f;
+            // DUAL: columns [0, NT) are the first token tile, [NT, 2 NT) the second.  The groups
+            // take chunks group, group + 2, ...; a chunk is 16 columns = 16 tokens.
+            int n_chunks = (min(a.M - m0, M_STEP) + 15) >> 4;
+            n_chunks = n_chunks > group ? (n_chunks - group + 1) >> 1 : 0;      // this group's share
+            const uint32_t t0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * NT + group * 16);
+            uint32_t ra[16], rb[16];
+            if (n_chunks > 0) tc_ld16(t0, ra);
 #pragma unroll 1
-            for (int c0 = 0; c0 < NT; c0 += 16) {
-                if (m0 + c0 >= a.M) break;
-                uint32_t r[16];
-                tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * NT + c0), r);
+            for (int i = 0; i < n_chunks; i += 2) {
                 tc_wait_ld();
-                store_chunk(a, r, n, n_ok, bias, m0 + c0, lane, 0);
+                if (i + 1 < n_chunks) tc_ld16(t0 + (uint32_t)((i + 1) * 32), rb);
+                store_chunk(a, ra, n, n_ok, bias, m0 + group * 16 + i * 32, lane, 0);
+                if (i + 1 < n_chunks) {
+                    tc_wait_ld();
+                    if (i + 2 < n_chunks) tc_ld16(t0 + (uint32_t)((i + 2) * 32), ra);
+                    store_chunk(a, rb, n, n_ok, bias, m0 + group * 16 + (i + 1) * 32, lane, 0);
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -969,46 +1016,80 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 
 static int sm_count();
 
-template <int NT, int STAGES>
+template <int NT, int STAGES, bool DUAL>
 static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
                        cudaStream_t stream) {
-    constexpr int smem = STAGES * (A_BYTES + (NT / 2) * TILE_K * 2) + 1024 + 256;
+    constexpr int smem = STAGES * (A_BYTES + (DUAL ? 2 : 1) * (NT / 2) * TILE_K * 2) + 1024 + 256;
+    static_assert(smem <= 227 * 1024, "the ring does not fit an SM's shared memory");
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<NT, STAGES>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<NT, STAGES, DUAL>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const int tiles_m = (a.M + NT - 1) / NT, tiles_n = (a.N + 255) / 256;
+    const int step = (DUAL ? 2 : 1) * NT;
+    const int tiles_m = (a.M + step - 1) / step, tiles_n = (a.N + 255) / 256;
     const int total = tiles_m * tiles_n;
     int pairs = sm_count() / 2;
     if (pairs > total) pairs = total;
-    mf_launch(gemm_pair_kernel<NT, STAGES>, dim3(2 * pairs), dim3(PAIR_THREADS), smem, stream, mw, mx,
+    mf_launch(gemm_pair_kernel<NT, STAGES, DUAL>, dim3(2 * pairs), dim3(PAIR_THREADS), smem, stream, mw, mx,
               a, tiles_m, total);
     return MF_LAUNCH_CHECK();
 }
 
 static int sm_count() { return mf_sm_count(); }
 
-// The token tile of the CTA-pair kernel: the one whose tiles fill the fewest, shortest rounds
-// over the pairs (14 weight tiles x 8 token tiles of 256 are 112 tiles for 74 pairs: the second
-// round runs half empty; 10 token tiles of 208 are 140 tiles and two rounds of 208).  A tile's
-// time follows the operand bytes it pulls through L2, 256 weight rows plus its tokens per
-// k-block (measured: a 208-token tile takes 0.96 of a 256-token one).  An element's sum does
-// not depend on the tile (k ascending, one accumulator), so the choice changes no bits.
-static int pair_token_tile(int M, int N) {
+// How the CTA-pair kernel cuts a product: the token tile and whether a pair takes two token
+// tiles at once (DUAL).  A model of the kernel's time picks them; its figures are measured on
+// this kernel (2,048 to 8,192 tokens, K 1,792 to 18,944):
+//   * operand bytes: every k-block a pair pulls 256 weight rows and its tokens' rows, 128 bytes
+//     each, through L2, and all pairs together get 11.8 TB/s (a 208-token tile takes 0.905 of a
+//     256-token one: the ratio of the bytes, not of the flops);
+//   * tensor cores: 23.4 TFLOP/s a pair with every pair at work (the clock under load);
+//   * rounds: the pairs walk the tiles in step, so the last round counts in full
+//     (14 weight tiles x 8 token tiles of 256 are 112 tiles for 74 pairs; 10 token tiles of 208
+//     are 140 tiles and two full rounds);
+//   * what is not hidden: the last tile's epilogue, and with DUAL every tile's (both
+//     accumulators are in use, so none is free for the next tile's main loop).
+// DUAL therefore wins where the tiles make one or two rounds, the more the longer K is (the
+// down projection of a 2,048-token prompt: 181 against 217 us; the O projection: 44 against 50);
+// it is not considered beyond two rounds.  An element's sum does not depend
+// on the cut (k ascending, one accumulator), so the choice changes no bits.
+struct PairPlan { int nt; int dual; };
+static int g_pair_dual = -1;              // 0 never, 1 where the model says so, 2 always
+// MINFER_B200_PAIR_DUAL or this call (tests compare the two forms bit for bit) sets the mode.
+extern "C" void mf_gemm_pair_dual_mode(int mode) { g_pair_dual = mode; }
+static PairPlan pair_plan(int M, int N, int K) {
     static const int candidates[] = {256, 224, 208, 192, 160};
-    const int pairs = sm_count() / 2, tiles_n = (N + 255) / 256;
-    int best = 256;
-    long long best_cost = -1;
-    for (int nt : candidates) {
-        const long long tiles = (long long)((M + nt - 1) / nt) * tiles_n;
-        const long long rounds = (tiles + pairs - 1) / pairs;
-        const long long cost = rounds * (nt + 256);
-        if (best_cost < 0 || cost < best_cost) { best = nt; best_cost = cost; }
-    }
+    if (g_pair_dual < 0) { const char* ev = getenv("MINFER_B200_PAIR_DUAL"); g_pair_dual = ev ? atoi(ev) : 1; }
+    const int allow_dual = g_pair_dual;
+    const double pairs = sm_count() / 2, tiles_n = (N + 255) / 256, kb = (K + TILE_K - 1) / TILE_K;
+    const double l2_bytes_per_ns = 11800.0 * (pairs / 74.0), pair_flops_per_ns = 23400.0;
+    PairPlan best = {256, 0};
+    double best_cost = -1.0;
+    for (int dual = allow_dual == 2 ? 1 : 0; dual <= (allow_dual ? 1 : 0); ++dual)
+        for (int nt : candidates) {
+            const int step = (dual ? 2 : 1) * nt;
+            const double tiles = (double)((M + step - 1) / step) * tiles_n;
+            const double rounds = (double)(long long)((tiles + pairs - 1) / pairs);
+            const double bytes = 128.0 * (256 + step), flops = 2.0 * 256 * step * TILE_K;
+            const double l2 = tiles * kb * bytes / l2_bytes_per_ns;
+            const double tc = rounds * kb * flops / pair_flops_per_ns;
+            const double epilogue = (dual ? rounds * 11600.0 : 4000.0) * nt / 256.0;
+            double cost = (l2 > tc ? l2 : tc) + epilogue;
+            if (dual && rounds > 2) continue;     // measured for one and two rounds only
+            if (best_cost < 0 || cost < best_cost) { best = {nt, dual}; best_cost = cost; }
+        }
     return best;
+}
+
+// The cut of the CTA-pair kernel for these sizes (it runs products of 256 tokens and more).
+extern "C" int mf_gemm_pair_plan(int M, int N, int K, int* token_tile, int* dual) {
+    const PairPlan pp = pair_plan(M, N, K);
+    *token_tile = pp.nt;
+    *dual = pp.dual;
+    return 0;
 }
 
 // How a product of these sizes is cut: the token tile and the number of K splits.  A
@@ -1120,14 +1201,23 @@ static int gemm_tc_impl(const void* x, long long ldx, const void* w, long long l
     }
     if (pair_mode_on() && M >= 256 && splits == 1) {
         if (a.row_ssq != nullptr) return MF_ERR_UNSUPPORTED;     // the CTA-pair kernel applies no row scale
-        const int pnt = pair_token_tile(M, N);
+        const PairPlan pp = pair_plan(M, N, K);
+        const int pnt = pp.nt, dual = pp.dual;
         if (int e = make_map(&mx, x, M, K, ldx, pnt / 2)) return e;
+        if (dual)
+            switch (pnt) {
+                case 224: return launch_pair<224, 5, true>(mw, mx, a, stream);
+                case 208: return launch_pair<208, 5, true>(mw, mx, a, stream);
+                case 192: return launch_pair<192, 5, true>(mw, mx, a, stream);
+                case 160: return launch_pair<160, 6, true>(mw, mx, a, stream);
+                default: return launch_pair<256, 4, true>(mw, mx, a, stream);
+            }
         switch (pnt) {
-            case 224: return launch_pair<224, 6>(mw, mx, a, stream);
-            case 208: return launch_pair<208, 6>(mw, mx, a, stream);
-            case 192: return launch_pair<192, 6>(mw, mx, a, stream);
-            case 160: return launch_pair<160, 6>(mw, mx, a, stream);
-            default: return launch_pair<256, 6>(mw, mx, a, stream);
+            case 224: return launch_pair<224, 6, false>(mw, mx, a, stream);
+            case 208: return launch_pair<208, 6, false>(mw, mx, a, stream);
+            case 192: return launch_pair<192, 6, false>(mw, mx, a, stream);
+            case 160: return launch_pair<160, 6, false>(mw, mx, a, stream);
+            default: return launch_pair<256, 6, false>(mw, mx, a, stream);
         }
     }
     if (int e = make_map(&mx, x, M, K, ldx, nt)) return e;

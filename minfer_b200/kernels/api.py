@@ -136,6 +136,9 @@ def _sig_gemm_tc(lib: ctypes.CDLL) -> None:
     lib.mf_gemm_tc_workspace_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mf_gemm_tc_workspace_floats.restype = c_longlong
     lib.mf_gemm_tc_plan.argtypes = [c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+    lib.mf_gemm_pair_plan.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p]
+    lib.mf_gemm_pair_dual_mode.argtypes = [c_int]
+    lib.mf_gemm_pair_dual_mode.restype = None
     lib.mf_gemm_tc_fused.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
                                      c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_float, c_void_p, c_longlong, c_void_p,
@@ -318,6 +321,20 @@ def gemm_tc_plan(m: int, n: int, k: int, epi: int = EPI_STORE) -> tuple[int, int
     """(token tile, K splits) the kernel uses for these sizes (a function of the sizes only:
     asked once per shape)."""
     return _gemm_tc_shape(m, n, k, epi)[:2]
+
+
+def gemm_pair_plan(m: int, n: int, k: int) -> tuple[int, bool]:
+    """(token tile, two token tiles a pair at once) of the CTA-pair kernel, which runs products
+    of 256 tokens and more."""
+    nt, dual = ctypes.c_int(0), ctypes.c_int(0)
+    _lib("gemm_tc").mf_gemm_pair_plan(m, n, k, ctypes.addressof(nt), ctypes.addressof(dual))
+    return nt.value, bool(dual.value)
+
+
+def gemm_pair_dual_mode(mode: int) -> None:
+    """0: a pair never takes two token tiles at once; 1: where the kernel's cost model says so
+    (the default); 2: always.  The result's bits are the same in every mode."""
+    _lib("gemm_tc").mf_gemm_pair_dual_mode(int(mode))
 
 
 def _gemm_tc_shape(m: int, n: int, k: int, epi: int) -> tuple[int, int, int]:

@@ -375,6 +375,64 @@ def test_gemm_tensor_core_against_float64(m, n, k):
     assert torch.equal(again, out)
 
 
+@pytest.mark.parametrize("m,n,k", [(300, 640, 328), (2048, 512, 200), (777, 1000, 520),
+                                   (256, 256, 64), (1300, 768, 1024), (3000, 300, 136)])
+def test_gemm_pair_kernel_two_token_tiles_at_once(m, n, k):
+    """The CTA-pair kernel with two token tiles a pair (forced on: the cost model picks it only
+    for long K): one token tile alone, a second one with a few tokens, an odd number of token
+    tiles, ragged edges, every epilogue.  Against float64, and bit for bit against the form
+    with one token tile a pair."""
+    from minfer_b200.kernels import api as K
+    g = torch.Generator().manual_seed(m * 3 + n + k)
+    x = (torch.randn(m, k, generator=g) * 0.5).bfloat16().cuda()
+    w = (torch.randn(n, k, generator=g) * 0.5).bfloat16().cuda()
+    bias = torch.randn(n, generator=g).cuda()
+    start = torch.randn(m, n, generator=g).cuda()
+    st = status()
+    want = x.double() @ w.double().t()
+    results = {}
+    try:
+        for mode in (2, 0):
+            K.gemm_pair_dual_mode(mode)
+            assert K.gemm_pair_plan(m, n, k)[1] == (mode == 2)
+            out = torch.zeros(m, n, device="cuda")
+            K.gemm_tc(x, w, bias, out, K.EPI_STORE, st)
+            acc = start.clone()
+            K.gemm_tc(x, w, None, acc, K.EPI_ACCUM, st)
+            accb = start.clone()
+            K.gemm_tc(x, w, bias, accb, K.EPI_ACCUM, st)
+            act = torch.zeros(m, n // 2, dtype=torch.bfloat16, device="cuda")
+            K.gemm_tc(x, w, None, act, K.EPI_SWIGLU, st)
+            results[mode] = (out, acc, accb, act)
+    finally:
+        K.gemm_pair_dual_mode(1)
+    out, acc, accb, act = results[2]
+    close(out, want + bias.double(), torch.float32)
+    close(acc, start.double() + want, torch.float32)
+    close(accb, start.double() + want + bias.double(), torch.float32)
+    close(act, torch.nn.functional.silu(want[:, 0::2]) * want[:, 1::2], torch.bfloat16)
+    for a, b in zip(results[2], results[0]):
+        assert torch.equal(a, b)
+    assert int(st) == 0
+
+
+def test_gemm_pair_plan_takes_two_token_tiles_for_a_long_k():
+    """The cost model's choices at the sizes it was measured on: the down projection of a
+    2,048-token prompt (K 18,944, 14 weight tiles) takes two token tiles a pair, the gate|up
+    projection (16 rounds of tiles, whose epilogues hide behind the next tile) does not, and
+    neither does a product with fewer tiles than pairs."""
+    from minfer_b200.kernels import api as K
+    K.gemm_pair_dual_mode(1)
+    assert K.gemm_pair_plan(2048, 3584, 18944) == (208, True)
+    assert K.gemm_pair_plan(4096, 3584, 18944) == (208, True)
+    assert K.gemm_pair_plan(2048, 37888, 3584) == (256, False)
+    assert K.gemm_pair_plan(2048, 4608, 3584) == (256, False)
+    assert K.gemm_pair_plan(512, 3584, 18944)[1] is False
+    assert K.gemm_pair_plan(8192, 5120, 5120) == (256, False)
+    assert K.gemm_pair_plan(2048, 3584, 3584) == (208, True)
+    assert K.gemm_pair_plan(8192, 5120, 13824)[1] is False
+
+
 def test_gemm_tensor_core_refuses_unaligned_rows():
     from minfer_b200.kernels import api as K
     x = torch.zeros(4, 20, dtype=torch.bfloat16, device="cuda")
