@@ -853,10 +853,26 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t bar, uint32_t cta_ra
         ::"r"(bar), "r"(cta_rank) : "memory");
 }
 
+// The order in which the pairs walk the tiles.  Tiles that run side by side fetch what they share
+// once (they stream along K in step, so L2 serves the others); what a later round needs again
+// comes from memory again.  With few token tiles all of them run beside each other for a weight
+// tile.  With many (8,192 tokens and more) that order would fetch every token row once per weight
+// tile, gigabytes for a down projection; the token tiles are therefore taken in groups of
+// `group_m`, and within a group the weight tiles change slowest, so that a round of tiles is a
+// block of about as many weight tiles as token tiles.
+__device__ __forceinline__ void pair_tile_at(int tile, int tiles_m, int tiles_n, int group_m,
+                                             int& mi, int& ni) {
+    const int per_group = group_m * tiles_n;
+    const int g = tile / per_group, r = tile - g * per_group;
+    const int width = min(group_m, tiles_m - g * group_m);     // the last group may be narrower
+    ni = r / width;
+    mi = g * group_m + (r - ni * width);
+}
+
 template <int NT, int STAGES, bool DUAL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                 const GemmArgs a, int tiles_m, int total_tiles) {
+                 const GemmArgs a, int tiles_m, int tiles_n, int group_m, int total_tiles) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr int HALF_B = (NT / 2) * TILE_K * 2;            // this CTA's half of one token tile
@@ -908,7 +924,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         int it = 0;
         bool ok = true;
         for (int tile = pair; tile < total_tiles && ok; tile += n_pairs) {
-            const int m0 = (tile % tiles_m) * M_STEP, n0 = (tile / tiles_m) * 256;
+            int mi, ni;
+            pair_tile_at(tile, tiles_m, tiles_n, group_m, mi, ni);
+            const int m0 = mi * M_STEP, n0 = ni * 256;
             const bool two = DUAL && m0 + NT < a.M;           // the second token tile has tokens
             for (int kb = 0; kb < kblocks; ++kb, ++it) {
                 const int s = it % STAGES;
@@ -936,7 +954,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             // DUAL: both accumulators belong to this tile (barrier 0 stands for the two)
             const int b = DUAL ? 0 : tile_i & 1;
             const uint32_t u = (uint32_t)(DUAL ? tile_i : tile_i >> 1);
-            const bool two = DUAL && (tile % tiles_m) * M_STEP + NT < a.M;
+            int mi, ni;
+            pair_tile_at(tile, tiles_m, tiles_n, group_m, mi, ni);
+            const bool two = DUAL && mi * M_STEP + NT < a.M;
             ok = mbar_wait(smem_u32(&acc_empty[b]), (u & 1u) ^ 1u, abort_flag);
             if (!ok) break;
             tc_fence_after();
@@ -970,7 +990,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         for (int tile = pair; tile < total_tiles; tile += n_pairs, ++tile_i) {
             const int b = DUAL ? 0 : tile_i & 1;
             const uint32_t u = (uint32_t)(DUAL ? tile_i : tile_i >> 1);
-            const int m0 = (tile % tiles_m) * M_STEP, n0 = (tile / tiles_m) * 256;
+            int mi, ni;
+            pair_tile_at(tile, tiles_m, tiles_n, group_m, mi, ni);
+            const int m0 = mi * M_STEP, n0 = ni * 256;
             if (!mbar_wait(smem_u32(&acc_full[b]), u & 1u, abort_flag)) break;
             tc_fence_after();
             const int n = n0 + (int)rank * TILE_N + q * 32 + lane;
@@ -1016,6 +1038,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 
 static int sm_count();
 
+static int g_pair_group_m = 0;            // > 0: the width of a group of token tiles (tests, measurement)
+extern "C" void mf_gemm_pair_group_m(int group_m) { g_pair_group_m = group_m; }
+
 template <int NT, int STAGES, bool DUAL>
 static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& a,
                        cudaStream_t stream) {
@@ -1032,9 +1057,18 @@ static int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, const GemmA
     const int tiles_m = (a.M + step - 1) / step, tiles_n = (a.N + 255) / 256;
     const int total = tiles_m * tiles_n;
     int pairs = sm_count() / 2;
+    // groups of token tiles such that a round of tiles is about square (as many weight tiles
+    // as token tiles, 9 x 9 for 74 pairs), all groups equally wide
+    int side = 1;
+    while ((side + 1) * (side + 1) <= pairs) ++side;
+    const int across = tiles_n < side ? tiles_n : side;
+    const int want_m = (pairs + across - 1) / across;
+    const int groups = (tiles_m + want_m - 1) / want_m;
+    int group_m = (tiles_m + groups - 1) / groups;
+    if (g_pair_group_m > 0) group_m = g_pair_group_m < tiles_m ? g_pair_group_m : tiles_m;
     if (pairs > total) pairs = total;
     mf_launch(gemm_pair_kernel<NT, STAGES, DUAL>, dim3(2 * pairs), dim3(PAIR_THREADS), smem, stream, mw, mx,
-              a, tiles_m, total);
+              a, tiles_m, tiles_n, group_m, total);
     return MF_LAUNCH_CHECK();
 }
 

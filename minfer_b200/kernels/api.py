@@ -139,6 +139,8 @@ def _sig_gemm_tc(lib: ctypes.CDLL) -> None:
     lib.mf_gemm_pair_plan.argtypes = [c_int, c_int, c_int, c_void_p, c_void_p]
     lib.mf_gemm_pair_dual_mode.argtypes = [c_int]
     lib.mf_gemm_pair_dual_mode.restype = None
+    lib.mf_gemm_pair_group_m.argtypes = [c_int]
+    lib.mf_gemm_pair_group_m.restype = None
     lib.mf_gemm_tc_fused.argtypes = [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p,
                                      c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p, c_int, c_int, c_float, c_void_p, c_longlong, c_void_p,
@@ -335,6 +337,12 @@ def gemm_pair_dual_mode(mode: int) -> None:
     """0: a pair never takes two token tiles at once; 1: where the kernel's cost model says so
     (the default); 2: always.  The result's bits are the same in every mode."""
     _lib("gemm_tc").mf_gemm_pair_dual_mode(int(mode))
+
+
+def gemm_pair_group_m(group_m: int) -> None:
+    """The CTA-pair kernel walks the token tiles in groups of this many (0: chosen from the sizes,
+    the default).  The order of the tiles changes no bits."""
+    _lib("gemm_tc").mf_gemm_pair_group_m(int(group_m))
 
 
 def _gemm_tc_shape(m: int, n: int, k: int, epi: int) -> tuple[int, int, int]:

@@ -357,6 +357,45 @@ def step_decode_sweep(reps, layers=28):
     eng.check_status()
 
 
+def step_prefill_sweep(reps, layers=28):
+    """Whole-prompt steps of the whole Qwen2.5-7B shape (28 layers) over prompt lengths of 256 to
+    32,000 tokens and batches of 2,048-token prompts: the first prompt's time after a pause (the
+    clock of an idle GPU) and the median of `reps` back to back (the clock under the power cap),
+    with the step's flops (products, causal attention, the head on the wanted row) over them."""
+    import statistics
+    import time
+    eng, cfg = _engine(layers, max_tokens=8 * 4096 + 64, max_seqs=8)
+    matrix_flops = 2.0 * layers * (NE * (NH + 2 * NK) * HD + NH * HD * NE + 3 * NE * NF)
+
+    def flops(lens):
+        attn = sum(4.0 * layers * NH * HD * (n * (n + 1) / 2) for n in lens)
+        return sum(lens) * matrix_flops + attn + 2.0 * len(lens) * NE * VOCAB
+
+    print(f"{'prompts':>8s} {'tokens':>7s} {'first ms':>9s} {'PFLOP/s':>8s} {'median ms':>10s} {'PFLOP/s':>8s} {'tokens/s':>10s}")
+    for lens in ([256], [512], [1024], [2048], [4096], [8192], [16384], [32000], [2048] * 4, [2048] * 8,
+                 [300, 700, 1500, 2048, 40, 1000, 1900, 64]):
+        ids = [torch.randint(0, VOCAB, (n,)).tolist() for n in lens]
+        times = []
+        for i in range(reps + 2):
+            slots = [eng.acquire() for _ in lens]
+            if i == 1:
+                torch.cuda.synchronize()
+                time.sleep(1.0)                       # the first timed step starts from an idle clock
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            eng.step(slots, ids)
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+            for s_ in slots:
+                eng.release(s_)
+        first, med = times[1], statistics.median(times[2:])
+        f = flops(lens)
+        print(f"{len(lens):8d} {sum(lens):7d} {first:9.2f} {f / first / 1e12:8.3f} {med:10.2f} "
+              f"{f / med / 1e12:8.3f} {sum(lens) / med * 1e3:10.0f}")
+    eng.check_status()
+
+
 def step_decode_timeline(reps, layers=4, batch=8):
     """The kernels of one replayed decode step (8 sequences at 2,048 positions, 4 layers) with
     their start and end times inside the graph, from CUPTI activity records."""
@@ -419,7 +458,7 @@ CASES = {f.__name__: f for f in (gemm_decode, gemm_decode_split, gemm_decode_m64
                                  attention_decode, attention_decode_b8, attention_decode_long, attention_prefill,
                                  attention_prefill_tc, attention_prefill_tc_8k, attention_prefill_8k,
                                  attention_portion, attention_portion_512_on_8k,
-                                 step_prefill, step_prefill_timeline, step_portions, step_decode, step_decode_sweep, step_decode_timeline,
+                                 step_prefill, step_prefill_timeline, step_portions, step_decode, step_decode_sweep, step_prefill_sweep, step_decode_timeline,
                                  step_decode_timeline_b64, step_decode_b64, step_decode_small)}
 
 

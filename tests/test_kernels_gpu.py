@@ -416,6 +416,37 @@ def test_gemm_pair_kernel_two_token_tiles_at_once(m, n, k):
     assert int(st) == 0
 
 
+@pytest.mark.parametrize("m,n,k", [(3000, 600, 136), (5000, 300, 72)])
+def test_gemm_pair_kernel_walks_the_tiles_in_groups(m, n, k):
+    """The CTA-pair kernel takes the token tiles in groups (within a group the weight tiles
+    change slowest), so that prompts of many thousand tokens do not fetch every token row once
+    per weight tile.  Every group width, a last group that is narrower, one and two token
+    tiles a pair: the same bits as the ungrouped order, and right against float64."""
+    from minfer_b200.kernels import api as K
+    g = torch.Generator().manual_seed(m + n + k)
+    x = (torch.randn(m, k, generator=g) * 0.5).bfloat16().cuda()
+    w = (torch.randn(n, k, generator=g) * 0.5).bfloat16().cuda()
+    start = torch.randn(m, n, generator=g).cuda()
+    st = status()
+    want = start.double() + x.double() @ w.double().t()
+    try:
+        for dual in (0, 2):
+            K.gemm_pair_dual_mode(dual)
+            K.gemm_pair_group_m(1 << 20)                   # one group: all token tiles side by side
+            base = start.clone()
+            K.gemm_tc(x, w, None, base, K.EPI_ACCUM, st)
+            close(base, want, torch.float32)
+            for group in (0, 1, 3, 5, 7):
+                K.gemm_pair_group_m(group)
+                acc = start.clone()
+                K.gemm_tc(x, w, None, acc, K.EPI_ACCUM, st)
+                assert torch.equal(acc, base), (dual, group)
+    finally:
+        K.gemm_pair_dual_mode(1)
+        K.gemm_pair_group_m(0)
+    assert int(st) == 0
+
+
 def test_gemm_pair_plan_takes_two_token_tiles_for_a_long_k():
     """The cost model's choices at the sizes it was measured on: the down projection of a
     2,048-token prompt (K 18,944, 14 weight tiles) takes two token tiles a pair, the gate|up
