@@ -361,7 +361,9 @@ def step_prefill_sweep(reps, layers=28):
     """Whole-prompt steps of the whole Qwen2.5-7B shape (28 layers) over prompt lengths of 256 to
     32,000 tokens and batches of 2,048-token prompts: the first prompt's time after a pause (the
     clock of an idle GPU) and the median of `reps` back to back (the clock under the power cap),
-    with the step's flops (products, causal attention, the head on the wanted row) over them."""
+    with the step's flops (products, causal attention, the head on the wanted row) over them,
+    and the time the host needs to issue the step's launches (a whole-prompt step is not a
+    graph: below about 512 tokens the device waits for the host)."""
     import statistics
     import time
     eng, cfg = _engine(layers, max_tokens=8 * 4096 + 64, max_seqs=8)
@@ -371,20 +373,22 @@ def step_prefill_sweep(reps, layers=28):
         attn = sum(4.0 * layers * NH * HD * (n * (n + 1) / 2) for n in lens)
         return sum(lens) * matrix_flops + attn + 2.0 * len(lens) * NE * VOCAB
 
-    print(f"{'prompts':>8s} {'tokens':>7s} {'first ms':>9s} {'PFLOP/s':>8s} {'median ms':>10s} {'PFLOP/s':>8s} {'tokens/s':>10s}")
+    print(f"{'prompts':>8s} {'tokens':>7s} {'first ms':>9s} {'PFLOP/s':>8s} {'median ms':>10s} {'PFLOP/s':>8s} {'tokens/s':>10s} {'host ms':>8s}")
     for lens in ([256], [512], [1024], [2048], [4096], [8192], [16384], [32000], [2048] * 4, [2048] * 8,
                  [300, 700, 1500, 2048, 40, 1000, 1900, 64]):
         ids = [torch.randint(0, VOCAB, (n,)).tolist() for n in lens]
-        times = []
+        times, host = [], []
         for i in range(reps + 2):
             slots = [eng.acquire() for _ in lens]
             if i == 1:
                 torch.cuda.synchronize()
                 time.sleep(1.0)                       # the first timed step starts from an idle clock
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            h0 = time.perf_counter()
             a.record()
             eng.step(slots, ids)
             b.record()
+            host.append((time.perf_counter() - h0) * 1e3)     # until the host has issued the step
             torch.cuda.synchronize()
             times.append(a.elapsed_time(b))
             for s_ in slots:
@@ -392,7 +396,7 @@ def step_prefill_sweep(reps, layers=28):
         first, med = times[1], statistics.median(times[2:])
         f = flops(lens)
         print(f"{len(lens):8d} {sum(lens):7d} {first:9.2f} {f / first / 1e12:8.3f} {med:10.2f} "
-              f"{f / med / 1e12:8.3f} {sum(lens) / med * 1e3:10.0f}")
+              f"{f / med / 1e12:8.3f} {sum(lens) / med * 1e3:10.0f} {statistics.median(host[2:]):8.2f}")
     eng.check_status()
 
 
