@@ -24,6 +24,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache.paged import PAGE, Cache, CacheError, GroupKey
@@ -34,6 +35,23 @@ from ..parts.base import CacheView, CallBinding, StepContext, settle_pending
 
 class StepError(RuntimeError):
     pass
+
+
+def _int_array(values, what: str) -> np.ndarray:
+    """A row's integers (token ids, wanted places) as an int64 array; refuses what is no integer."""
+    a = np.asarray(values)
+    if a.ndim != 1:
+        a = a.reshape(-1) if a.size == 0 else a
+    if a.ndim != 1:
+        raise StepError(f"{what} of a row must be a flat sequence of integers")
+    if a.size == 0:
+        return np.zeros(0, dtype=np.int64)
+    if a.dtype.kind not in "iu":
+        as_int = a.astype(np.int64, copy=True) if a.dtype.kind in "fb" else None
+        if as_int is None or not np.array_equal(as_int, a):
+            raise StepError(f"{what} must be integers")
+        return as_int
+    return a.astype(np.int64, copy=False)
 
 
 def padded_rows(n_rows: int) -> int:
@@ -157,21 +175,27 @@ class Engine:
         if min(counts) < 1:
             raise StepError("every sequence of a step brings at least one token")
         starts = [self.cache.length(s) for s in slots]
+        # the rows' tokens as integer arrays from here on (a prompt of thousands of tokens is
+        # checked and laid out without a Python loop over its tokens)
+        tokens = [_int_array(t, "token ids") for t in tokens]
         for b in range(n_rows):
             if starts[b] + counts[b] > plan.max_positions:
                 raise StepError(
                     f"sequence in slot {slots[b]} would reach position "
                     f"{starts[b] + counts[b] - 1}, beyond max_position_embeddings "
                     f"{plan.max_positions}")
-            for t in tokens[b]:
-                if not 0 <= int(t) < plan.vocab_size:
-                    raise StepError(f"token id {t} is outside the vocabulary of {plan.vocab_size}")
+            bad = (tokens[b] < 0) | (tokens[b] >= plan.vocab_size)
+            if bad.any():
+                t = int(tokens[b][int(np.argmax(bad))])
+                raise StepError(f"token id {t} is outside the vocabulary of {plan.vocab_size}")
         if want is None:
             want = [[c - 1] for c in counts]
+        want = [_int_array(w, "wanted places") for w in want]
         for b in range(n_rows):
-            for w in want[b]:
-                if not 0 <= int(w) < counts[b]:
-                    raise StepError(f"wanted place {w} is outside the {counts[b]} tokens given")
+            bad = (want[b] < 0) | (want[b] >= counts[b])
+            if bad.any():
+                w = int(want[b][int(np.argmax(bad))])
+                raise StepError(f"wanted place {w} is outside the {counts[b]} tokens given")
         for b in range(n_rows):
             self.cache.reserve(slots[b], starts[b] + counts[b])
         from_start = all(s == 0 for s in starts)
@@ -280,18 +304,19 @@ class Engine:
             for g, width in zip(self.cache.groups, widths):
                 fields.append(g.table_flat(slots, width))
             return fields
-        flat_tokens, positions, token_row, cu, base_of = [], [], [], [0], {}
-        for b in range(n_rows):                       # (rows may have been reordered by the caller)
-            base_of[b] = cu[-1]
-            flat_tokens.extend(int(t) for t in tokens[b])
-            positions.extend(range(starts[b], starts[b] + counts[b]))
-            token_row.extend([b] * counts[b])
-            cu.append(cu[-1] + counts[b])
-        want_rows = []
-        for b in (order if order is not None else range(n_rows)):
-            want_rows.extend(base_of[b] + int(w) for w in want[b])
-        seq_end = [starts[b] + counts[b] for b in range(n_rows)]
-        fields = [flat_tokens, positions, token_row, cu, seq_end, list(slots), want_rows]
+        counts_a = np.asarray(counts, dtype=np.int64)
+        starts_a = np.asarray(starts, dtype=np.int64)
+        cu = np.zeros(n_rows + 1, dtype=np.int64)           # (rows may have been reordered by the caller)
+        np.cumsum(counts_a, out=cu[1:])
+        flat_tokens = np.concatenate([np.asarray(t, dtype=np.int64) for t in tokens])
+        token_row = np.repeat(np.arange(n_rows, dtype=np.int64), counts_a)
+        # position of a token = its row's start + its place in the row
+        positions = np.arange(int(cu[-1]), dtype=np.int64) - np.repeat(cu[:-1] - starts_a, counts_a)
+        rows = order if order is not None else range(n_rows)
+        want_rows = [cu[b] + np.asarray(want[b], dtype=np.int64) for b in rows]
+        want_rows = np.concatenate(want_rows) if want_rows else np.zeros(0, dtype=np.int64)
+        fields = [flat_tokens, positions, token_row, cu, starts_a + counts_a,
+                  np.asarray(slots, dtype=np.int64), want_rows]
         for g, width in zip(self.cache.groups, widths):
             fields.append(g.table_flat(slots, width))
         return fields
@@ -335,14 +360,17 @@ class Engine:
         widths = [max(1, g.max_pages_of(slots)) for g in self.cache.groups]
         fields = self._host_fields(slots, tokens, counts, starts, want, widths, order)
         sizes = [len(f) for f in fields]
-        host = torch.tensor([x for f in fields for x in f], dtype=torch.int32).pin_memory()
+        host = torch.from_numpy(np.concatenate(
+            [np.asarray(f, dtype=np.int32) for f in fields])).pin_memory()
         dev = host.to(self.device, non_blocking=True)
         self.h2d_bytes += host.numel() * 4
         views = self._views(dev, sizes)
         ctx = self._make_ctx(views, widths, sum(counts), slots, from_start, single, max(counts),
                              max(starts[b] + counts[b] for b in range(len(slots))))
         # every row wanted, in order (decoding): the last layer needs no row selection
-        ctx.extras["want_is_identity"] = fields[6] == list(range(sum(counts)))
+        n_tokens = sum(counts)
+        ctx.extras["want_is_identity"] = (len(fields[6]) == n_tokens and
+                                          bool(np.array_equal(fields[6], np.arange(n_tokens))))
         ctx.extras["single_rows"] = n_single          # rows of one token, first in the batch
         return ctx, (views[6] if sizes[6] else None)
 
