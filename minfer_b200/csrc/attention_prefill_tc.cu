@@ -43,6 +43,7 @@
 #define FA_Q 128              // queries per tile
 #define FA_CTA_Q 256          // a CTA owns two query tiles that share every key tile
 #define FA_KEYS 128           // keys per tile
+#define FA_LAZY_LOG2 8.0f      // the maximum may grow this many binary orders before O is rescaled
 #define FA_THREADS 384        // warp 0 TMA, warp 1 MMA, warps 4-7 and 8-11 softmax of the two query tiles
 #define FA_MAX_SPIN (1u << 24)
 #define FA_MAX_WAIT_NS 2000000000ull
@@ -160,6 +161,32 @@ __device__ __forceinline__ uint64_t fa_desc_kmajor(uint32_t addr) {
 __device__ __forceinline__ uint64_t fa_desc_mnmajor(uint32_t addr, uint32_t lbo) {
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+
+// Two float32 in one 64-bit register, and the packed forms of fma and add (each half is the
+// scalar operation, round to nearest), and the maximum of three.
+__device__ __forceinline__ uint64_t fa_pack2(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void fa_unpack2(uint64_t v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fa_fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t fa_add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float fa_max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
 }
 
 __device__ __forceinline__ uint32_t fa_pack(float lo, float hi) {
@@ -400,20 +427,27 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     if (!vis) sr[i] = 0xff800000u;            // -inf
                 }
             }
-            // the maximum with four independent chains
+            // the maximum with four independent chains of three-input maxima
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < FA_KEYS; i += 4) {
-                mx0 = fmaxf(mx0, __uint_as_float(sr[i]));
-                mx1 = fmaxf(mx1, __uint_as_float(sr[i + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(sr[i + 2]));
-                mx3 = fmaxf(mx3, __uint_as_float(sr[i + 3]));
+            for (int i = 0; i < FA_KEYS; i += 8) {
+                mx0 = fa_max3(mx0, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+                mx1 = fa_max3(mx1, __uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3]));
+                mx2 = fa_max3(mx2, __uint_as_float(sr[i + 4]), __uint_as_float(sr[i + 5]));
+                mx3 = fa_max3(mx3, __uint_as_float(sr[i + 6]), __uint_as_float(sr[i + 7]));
             }
             const float m_tile = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-            const float m_new = fmaxf(m, m_tile);
+            // The reference point of the exponentials moves only when the maximum has grown by more
+            // than FA_LAZY_LOG2 binary orders (softmax does not depend on the point; until then a
+            // probability is at most 2^FA_LAZY_LOG2 before the division by the sum, far inside
+            // float32 and bfloat16).  The output so far has to be rescaled when the point moves,
+            // a round trip of 128 columns through tensor memory in the middle of the softmax.
+            const bool jump = m == -INFINITY ? m_tile > -INFINITY
+                                             : (m_tile - m) * a.scale_log2 > FA_LAZY_LOG2;
+            const float m_new = jump ? m_tile : m;
             const float m_off = m_new == -INFINITY ? 0.0f : m_new * a.scale_log2;
             const float corr = m == -INFINITY ? 0.0f : exp2f(m * a.scale_log2 - m_off);
-            // the output so far is rescaled only if some row of this warp has a new maximum
+            // the output so far is rescaled only if the point moved for some row of this warp
             const bool grow = m_new > m;
             if (c > 0 && __any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
@@ -429,19 +463,28 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             m = m_new;
             // probabilities (ex2.approx of the scaled difference), their sum with four chains,
             // packed as bfloat16 pairs into the first 64 columns of this S buffer
-            float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+            // (two scores an instruction: the scaled differences and the sums are packed pairs of
+            // float32, the same operations on each half as the scalar forms)
+            uint64_t l01 = 0, l23 = 0;                   // {l0, l1}, {l2, l3} = four zeros
+            const uint64_t scale2 = fa_pack2(a.scale_log2, a.scale_log2), off2 = fa_pack2(-m_off, -m_off);
             uint32_t pk[FA_KEYS / 2];
 #pragma unroll
             for (int i = 0; i < FA_KEYS; i += 4) {
-                float p0, p1, p2, p3;
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(sr[i]), a.scale_log2, -m_off)));
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(sr[i + 1]), a.scale_log2, -m_off)));
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p2) : "f"(fmaf(__uint_as_float(sr[i + 2]), a.scale_log2, -m_off)));
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p3) : "f"(fmaf(__uint_as_float(sr[i + 3]), a.scale_log2, -m_off)));
-                l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+                float x0, x1, x2, x3, p0, p1, p2, p3;
+                fa_unpack2(fa_fma2(fa_pack2(__uint_as_float(sr[i]), __uint_as_float(sr[i + 1])), scale2, off2), x0, x1);
+                fa_unpack2(fa_fma2(fa_pack2(__uint_as_float(sr[i + 2]), __uint_as_float(sr[i + 3])), scale2, off2), x2, x3);
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(x0));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(x1));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p2) : "f"(x2));
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p3) : "f"(x3));
+                l01 = fa_add2(l01, fa_pack2(p0, p1));
+                l23 = fa_add2(l23, fa_pack2(p2, p3));
                 pk[i >> 1] = fa_pack(p0, p1);
                 pk[(i >> 1) + 1] = fa_pack(p2, p3);
             }
+            float l0, l1, l2, l3;
+            fa_unpack2(l01, l0, l1);
+            fa_unpack2(l23, l2, l3);
             l = l * corr + ((l0 + l1) + (l2 + l3));
 #pragma unroll
             for (int c0 = 0; c0 < FA_KEYS / 2; c0 += 32) fa_st32(s_addr + (uint32_t)c0, pk + c0);
