@@ -9,7 +9,8 @@ layers deep, random weights N(0, 0.02) rounded to bfloat16:
   portions;
 * the bfloat16 engine (tcgen05 GEMMs, tensor-core attention, CUDA graphs) under the same
   schedules against the float32 engine on the same weights, for a prompt long enough to take
-  the CTA-pair GEMM.
+  the CTA-pair GEMM, and for a 2,048-token prompt (the sizes at which that kernel takes two
+  token tiles a pair).
 """
 import pytest
 import torch
@@ -76,13 +77,15 @@ def test_all_layers_at_real_sizes():
     prompts = [random_ids(n, V, 31 + n) for n in LENS]
     feed = [random_ids(DECODE, V, 77 + i) for i in range(3)]
     short = random_ids(48, V, 5)
-    outs, short_out = {}, {}
+    long_prompt = random_ids(2048, V, 9)                # products with two token tiles a CTA pair
+    long_want = [0, 255, 256, 1000, 2047]
+    outs, short_out, long_out = {}, {}, {}
     oracle = None
     for dtype in ("float32", "bfloat16"):
         # the same bfloat16-rounded weights in both engines (float32 holds them exactly)
         model = Model.from_config(CONFIG, seed=5, dtype=dtype, device="cuda:0",
                                   store_dtype="bfloat16", make_on="device")
-        eng = Engine(model, max_tokens=1024, max_seqs=4)
+        eng = Engine(model, max_tokens=3072, max_seqs=4)
         if dtype == "float32":
             with torch.no_grad():
                 oracle = P.forward(CONFIG, _AsFloat64(model.export_state_dict()), short).cpu()
@@ -90,6 +93,10 @@ def test_all_layers_at_real_sizes():
         short_out[dtype] = eng.step([s], [short], [list(range(len(short)))]).cpu()
         eng.release(s)
         outs[dtype] = _schedules(eng, prompts, feed)
+        s = eng.acquire()
+        long_out[dtype] = eng.step([s], [long_prompt], [long_want]).cpu()
+        eng.release(s)
+        eng.check_status()
         del eng, model
         torch.cuda.empty_cache()
     # against the plain implementation
@@ -109,6 +116,9 @@ def test_all_layers_at_real_sizes():
     assert outs["bfloat16"].shape == f32.shape
     assert torch.isfinite(outs["bfloat16"]).all()
     assert row_rms_err(outs["bfloat16"], f32) < ROW_RMS_TOL
+    # a 2,048-token prompt: the bfloat16 engine's products run two token tiles a CTA pair (O,
+    # down) and 256-token tiles (q|k|v, gate|up), its attention on tcgen05
+    assert row_rms_err(long_out["bfloat16"], long_out["float32"]) < ROW_RMS_TOL
     # the argmax agrees wherever the float32 margin is larger than the tolerance
     top2 = f32.topk(2, dim=-1).values
     clear = (top2[:, 0] - top2[:, 1]) > 0.05 * f32.abs().max()
