@@ -39,7 +39,12 @@ class StepError(RuntimeError):
 
 def _int_array(values, what: str) -> np.ndarray:
     """A row's integers (token ids, wanted places) as an int64 array; refuses what is no integer."""
-    a = np.asarray(values)
+    if isinstance(values, torch.Tensor):
+        values = values.detach().cpu().numpy()
+    try:
+        a = np.asarray(values)
+    except (TypeError, ValueError) as e:
+        raise StepError(f"{what} of a row must be a flat sequence of integers") from e
     if a.ndim != 1:
         a = a.reshape(-1) if a.size == 0 else a
     if a.ndim != 1:
