@@ -85,6 +85,11 @@ class ModelPlan:
     # embedding rows as they enter the residual stream, a bias added to the logits
     embedding_scale: float = 1.0
     head_bias_name: Optional[str] = None
+    # optional parts of role "model" (``ModelPart``) run on the residual stream right after the
+    # embedding and on the logits right after the head; their tensors take this prefix
+    after_embedding: Optional[PartSpec] = None
+    on_logits: Optional[PartSpec] = None
+    model_part_prefix: str = ""
 
     def validate(self) -> None:
         if self.vocab_size <= 0 or self.hidden_size <= 0:

@@ -121,7 +121,7 @@ class Engine:
             self._call_state.append(tensors)
         from ..kernels import build
         # every part of the model, asked of the blocks themselves
-        parts = [model.final_norm]
+        parts = [model.final_norm] + model.model_parts()
         for block in model.blocks:
             parts.append(block)
             parts.extend(block.parts())
@@ -485,6 +485,8 @@ class Engine:
         gemm.use_status_word(self.status)           # this engine's products report into its word
         h = torch.empty((ctx.n_tokens, plan.hidden_size), dtype=torch.float32, device=self.device)
         K.embed(model.embedding, ctx.token_ids, h, self.status, plan.embedding_scale)
+        if model.after_embedding is not None:
+            model.after_embedding.forward_inplace(h, ctx)
         bindings = self._bindings(ctx)
         last = len(plan.schedule) - 1
         n_want = 0 if want_rows is None else want_rows.numel()
@@ -520,13 +522,17 @@ class Engine:
             block.feed(h, ctx)
         prepared = ctx.extras.pop("prepared", None)
         if prepared is not None and prepared.norm is model.final_norm:
-            return model.head.forward(prepared.x, torch.float32, row_scale=prepared.scale)
-        pending = ctx.extras.pop("pending", None)
-        if pending is not None:
-            x = model.final_norm.forward_settling(h, pending, self.dtype)
+            logits = model.head.forward(prepared.x, torch.float32, row_scale=prepared.scale)
         else:
-            x = model.final_norm.forward(h, self.dtype)
-        return model.head.forward(x, torch.float32)
+            pending = ctx.extras.pop("pending", None)
+            if pending is not None:
+                x = model.final_norm.forward_settling(h, pending, self.dtype)
+            else:
+                x = model.final_norm.forward(h, self.dtype)
+            logits = model.head.forward(x, torch.float32)
+        if model.on_logits is not None:
+            model.on_logits.forward_inplace(logits, ctx)
+        return logits
 
     # ---- marks on the stream, for device times -------------------------------------------------
     def time_mark(self) -> torch.cuda.Event:

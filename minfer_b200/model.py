@@ -44,6 +44,9 @@ class Model:
         self.blocks: List[Block] = [build_part("block", layer.block, layer=layer)
                                     for layer in plan.layers]
         self.final_norm: Norm = build_part("norm", plan.final_norm)
+        self.after_embedding = (build_part("model", plan.after_embedding)
+                                if plan.after_embedding is not None else None)
+        self.on_logits = build_part("model", plan.on_logits) if plan.on_logits is not None else None
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[Linear] = None
         self.device: Optional[torch.device] = None
@@ -55,6 +58,8 @@ class Model:
         for block in self.blocks:
             specs += block.tensor_specs()
         specs += self.final_norm.tensor_specs(p.final_norm_prefix)
+        for part in self.model_parts():
+            specs += part.tensor_specs(p.model_part_prefix)
         if p.head_name is not None:
             specs.append(TensorSpec(p.head_name, (p.vocab_size, p.hidden_size), MATRIX,
                                     Init(0.0, 0.02)))
@@ -65,6 +70,10 @@ class Model:
             dup = sorted({n for n in names if names.count(n) > 1})
             raise ValueError(f"two parts ask for the same tensor: {', '.join(dup)}")
         return specs
+
+    def model_parts(self) -> List[Any]:
+        """The plan's parts around the blocks that this model has."""
+        return [part for part in (self.after_embedding, self.on_logits) if part is not None]
 
     def ignorable_tensors(self) -> List[str]:
         """Names a checkpoint may hold without being used: a separate head beside tied
@@ -80,6 +89,8 @@ class Model:
         for block in self.blocks:
             block.load("", weights)
         self.final_norm.load(p.final_norm_prefix, weights)
+        for part in self.model_parts():
+            part.load(p.model_part_prefix, weights)
         head_w = self.embedding if p.head_name is None else weights[p.head_name]
         self.head = Linear(head_w, weights[p.head_bias_name] if p.head_bias_name is not None else None)
         return self
@@ -154,6 +165,8 @@ class Model:
         for block in self.blocks:
             out.update(block.export(""))
         out.update(self.final_norm.export(p.final_norm_prefix))
+        for part in self.model_parts():
+            out.update(part.export(p.model_part_prefix))
         if p.head_name is not None:
             out[p.head_name] = self.head.weight
         if p.head_bias_name is not None:

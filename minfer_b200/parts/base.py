@@ -162,6 +162,17 @@ class Part:
         return {}
 
 
+class ModelPart(Part):
+    """A part of the model around the blocks (role ``"model"``), named by the plan: after the
+    embedding (``ModelPlan.after_embedding``: learned positions added to the residual stream,
+    for instance) or on the logits (``ModelPlan.on_logits``: a soft cap, for instance).  It
+    changes its tensor in place, row by row: row ``t`` of ``h`` is token ``t`` of the step
+    (``ctx.positions[t]``, ``ctx.token_row[t]``); the rows of the logits are the wanted places."""
+
+    def forward_inplace(self, x: torch.Tensor, ctx: "StepContext") -> None:
+        raise NotImplementedError
+
+
 class Norm(Part):
     def forward(self, x32: torch.Tensor, out_dtype: torch.dtype,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:

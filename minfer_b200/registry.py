@@ -14,7 +14,7 @@ from typing import Any, Callable, Mapping
 
 from .config.base import ConfigError, ModelPlan, PartSpec
 
-PART_ROLES = ("mixer", "feed_forward", "norm", "position", "block")
+PART_ROLES = ("mixer", "feed_forward", "norm", "position", "block", "model")
 
 
 @dataclass(frozen=True)

@@ -18,6 +18,7 @@ from helpers import random_ids, rel_err
 pytestmark = pytest.mark.gpu
 
 VOCAB, WIDTH, INNER = 97, 48, 24
+SOFT_CAP = 4.0
 
 
 def _register():
@@ -25,7 +26,8 @@ def _register():
     from minfer_b200.config.base import (ConfigReader, LayerSpec, ModelPlan, PartSpec,
                                          default_schedule)
     from minfer_b200.kernels import api as K
-    from minfer_b200.parts.base import FeedForward, Mixer, PositionEncoding, StateRequest
+    from minfer_b200.parts.base import (FeedForward, Mixer, ModelPart, PositionEncoding,
+                                        StateRequest)
     from minfer_b200.weights.spec import MATRIX, Init, TensorSpec
 
     class DecayMixer(Mixer):
@@ -82,6 +84,32 @@ def _register():
             n_rot = (n_heads + n_kv_heads) * head_dim
             qkv32[:, :n_rot] += 0.01 * ctx.positions.to(torch.float32)[:, None]
 
+    class LearnedPositions(ModelPart):
+        """A vector per absolute position, added to the residual stream after the embedding."""
+        capturable = True
+
+        def __init__(self, width, positions):
+            self.width, self.positions = width, positions
+
+        def tensor_specs(self, prefix):
+            return [TensorSpec(f"{prefix}positions", (self.positions, self.width), MATRIX, Init(0.0, 0.1))]
+
+        def load(self, prefix, weights):
+            self.table = weights[f"{prefix}positions"]
+
+        def forward_inplace(self, h, ctx):
+            h += self.table[ctx.positions.long()].to(h.dtype)
+
+    class SoftCap(ModelPart):
+        """logits <- cap * tanh(logits / cap)."""
+        capturable = True
+
+        def __init__(self, cap):
+            self.cap = float(cap)
+
+        def forward_inplace(self, logits, ctx):
+            logits.div_(self.cap).tanh_().mul_(self.cap)
+
     class ToyConfig:
         def __init__(self, d):
             r = ConfigReader(d)
@@ -102,16 +130,23 @@ def _register():
                        else PartSpec("gated_mlp", dict(hidden_size=self.width, intermediate_size=40)))
                 layers.append(LayerSpec(f"toy.{l}.", PartSpec("pre_norm", {}), mixer,
                                         norm.with_params(name="n1"), ffn, norm.with_params(name="n2")))
-            # the embedding rows are multiplied by 3 on their way in and the logits get a bias:
+            # the embedding rows are multiplied by 3 on their way in and the logits get a bias;
+            # a vector per position is added after the embedding and the logits are soft-capped:
             # hooks of the plan that the shipped architecture leaves at their defaults
             return ModelPlan("ToyStateLM", self.vocab, self.width, "toy.embed", None,
                              norm.with_params(name="final"), "toy.", layers,
-                             default_schedule(self.layers), 4096, (), embedding_scale=3.0,
-                             head_bias_name="toy.head_bias")
+                             default_schedule(self.layers), 128, (), embedding_scale=3.0,
+                             head_bias_name="toy.head_bias",
+                             after_embedding=PartSpec("toy_learned_positions",
+                                                      dict(width=self.width, positions=128)),
+                             on_logits=PartSpec("toy_soft_cap", dict(cap=SOFT_CAP)),
+                             model_part_prefix="toy.")
 
     registry.register_part("mixer", "toy_decay", DecayMixer, replace=True)
     registry.register_part("feed_forward", "toy_square", SquareFeedForward, replace=True)
     registry.register_part("position", "toy_shift", ShiftPosition, replace=True)
+    registry.register_part("model", "toy_learned_positions", LearnedPositions, replace=True)
+    registry.register_part("model", "toy_soft_cap", SoftCap, replace=True)
     registry.register_architecture("ToyStateLM", lambda d, where: ToyConfig(d), replace=True)
 
 
@@ -123,8 +158,8 @@ def _reference(w, ids):
     """The toy model in float64, whole sequence."""
     def norm(x, wt):
         return x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5) * wt
-    h = w["toy.embed"][torch.tensor(ids)] * 3.0
     T = len(ids)
+    h = w["toy.embed"][torch.tensor(ids)] * 3.0 + w["toy.positions"][:T]
     for l in range(3):
         p = f"toy.{l}."
         x = norm(h, w[p + "n1.weight"])
@@ -153,7 +188,8 @@ def _reference(w, ids):
         else:
             g, u = x @ w[p + "mlp.gate_proj.weight"].t(), x @ w[p + "mlp.up_proj.weight"].t()
             h = h + (torch.nn.functional.silu(g) * u) @ w[p + "mlp.down_proj.weight"].t()
-    return norm(h, w["toy.final.weight"]) @ w["toy.embed"].t() + w["toy.head_bias"]
+    logits = norm(h, w["toy.final.weight"]) @ w["toy.embed"].t() + w["toy.head_bias"]
+    return SOFT_CAP * torch.tanh(logits / SOFT_CAP)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
