@@ -21,7 +21,8 @@ server slot (src/server/slot.rs:15-32), and has one kind of layer only.  Here:
 * ``StatePool`` holds fixed-size state per slot (zeroed when the slot is handed out) for
   parts that ask for it, and for the sampler.
 
-Layout of a group's storage: ``[entry][page][kv_head][64][head_dim]`` for K and for V.
+Layout of a group's storage: ``[entry][page][kv_head][64][head_dim]`` for K and for V (V with
+its own last dimension where a mixer asks for values of another width).
 """
 from __future__ import annotations
 
@@ -156,6 +157,7 @@ class GroupKey:
     n_kv_heads: int
     head_dim: int
     window: int          # 0: linear
+    value_dim: int = 0   # width of a value vector if it differs from head_dim (0: the same)
 
 
 class CacheGroup:
@@ -177,10 +179,11 @@ class CacheGroup:
         self._table = np.full((n_slots + 1, 8), -1, dtype=np.int32)
         self._table[n_slots, 0] = self.spare_page
         shape = (len(self.entries), n_pages + 1, key.n_kv_heads, PAGE, key.head_dim)
+        v_shape = shape[:-1] + (key.value_dim or key.head_dim,)
         # zeros, once: a page's unwritten positions are masked by length but still multiplied
         # by a zero weight in the tensor-core kernels, so they must never hold NaN or Inf
         self._guarded = [Guarded(shape, dtype, device, f"keys of cache group {key}"),
-                         Guarded(shape, dtype, device, f"values of cache group {key}")]
+                         Guarded(v_shape, dtype, device, f"values of cache group {key}")]
         self.k = self._guarded[0].tensor
         self.v = self._guarded[1].tensor
         self._index = {e: i for i, e in enumerate(self.entries)}

@@ -96,7 +96,7 @@ class Engine:
             req = model.blocks[call.layer].mixer.cache_request()
             if req is None:
                 continue
-            key = GroupKey(req.n_kv_heads, req.head_dim, req.window)
+            key = GroupKey(req.n_kv_heads, req.head_dim, req.window, req.value_dim)
             if call.writes_cache:
                 requests[call.cache] = key
             else:
@@ -104,7 +104,7 @@ class Engine:
         for call in plan.schedule:
             req = model.blocks[call.layer].mixer.cache_request()
             if req is not None and not call.writes_cache:
-                want = GroupKey(req.n_kv_heads, req.head_dim, req.window)
+                want = GroupKey(req.n_kv_heads, req.head_dim, req.window, req.value_dim)
                 if requests.get(call.cache) != want:
                     raise StepError(
                         f"a call reads cache entry {call.cache} with {want}, but it is written "

@@ -35,6 +35,7 @@ class CacheRequest:
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    value_dim: int = 0       # width of a value vector if it differs from the keys' (0: head_dim)
 
 
 @dataclass(frozen=True)
@@ -51,7 +52,7 @@ class CacheView:
     """One cache entry as kernels see it."""
 
     k: torch.Tensor                 # [pages, n_kv_heads, 64, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor                 # [pages, n_kv_heads, 64, value_dim or head_dim]
     page_table: torch.Tensor        # int32 [batch rows, table_stride]
     table_stride: int
     ring: int                       # 0 = linear, else ring length in positions

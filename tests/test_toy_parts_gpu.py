@@ -500,3 +500,130 @@ def test_toy_block_with_other_member_names_gets_the_capture_check():
     assert len(eng._graphs) >= 1
     assert rel_err(torch.cat(rows), want) < 2e-5
     eng.check_status()
+
+
+# ---------------------------------------------------------------------------------------------
+# A toy mixer whose values are wider than its keys (keys of 16, values of 40, one head): it asks
+# the cache for both widths, writes its own keys and values into the pages it is given and
+# reads them back by page table.  Plain tensor code on purpose: only the cache's interface is
+# under test here (slots, pages, page tables, reuse), not a kernel.
+# ---------------------------------------------------------------------------------------------
+KEY_DIM, VALUE_DIM = 16, 40
+
+
+def _register_wide_values():
+    from minfer_b200 import registry
+    from minfer_b200.config.base import ConfigReader, LayerSpec, ModelPlan, PartSpec, default_schedule
+    from minfer_b200.parts.base import CacheRequest, Mixer
+    from minfer_b200.weights.spec import MATRIX, Init, TensorSpec
+
+    class WideValueMixer(Mixer):
+        def __init__(self, width):
+            self.width = width
+
+        def tensor_specs(self, prefix):
+            shapes = {"q": (KEY_DIM, self.width), "k": (KEY_DIM, self.width),
+                      "v": (VALUE_DIM, self.width), "o": (self.width, VALUE_DIM)}
+            return [TensorSpec(f"{prefix}wide.{n}", shape, MATRIX, Init(0.0, 0.2))
+                    for n, shape in shapes.items()]
+
+        def load(self, prefix, weights):
+            self.w = {n: weights[f"{prefix}wide.{n}"].float() for n in "qkvo"}
+
+        def cache_request(self):
+            return CacheRequest(1, KEY_DIM, 0, value_dim=VALUE_DIM)
+
+        def forward_add(self, x, ctx, binding, residual):
+            x = x.float()
+            q, k, v = (x @ self.w[n].t() for n in "qkv")
+            cache = binding.cache
+            assert cache.k.shape[-1] == KEY_DIM and cache.v.shape[-1] == VALUE_DIM
+            rows, positions = ctx.token_row.tolist(), ctx.positions.tolist()
+            table = cache.page_table.view(-1, cache.table_stride).tolist()
+            for t, (b, pos) in enumerate(zip(rows, positions)):        # write, then read: the step's
+                page = table[b][pos // 64]                             # own keys are in the cache
+                cache.k[page, 0, pos % 64] = k[t].to(cache.k.dtype)
+                cache.v[page, 0, pos % 64] = v[t].to(cache.v.dtype)
+            out = torch.zeros_like(v)
+            for t, (b, pos) in enumerate(zip(rows, positions)):
+                pages = torch.tensor(table[b][:pos // 64 + 1], device=x.device)
+                keys = cache.k[pages, 0].reshape(-1, KEY_DIM)[:pos + 1].float()
+                values = cache.v[pages, 0].reshape(-1, VALUE_DIM)[:pos + 1].float()
+                out[t] = torch.softmax(keys @ q[t] * 0.25, 0) @ values
+            residual += out @ self.w["o"].t()
+
+    class WideConfig:
+        def __init__(self, d):
+            r = ConfigReader(d)
+            self.vocab, self.width, self.layers = r.integer("vocab"), r.integer("width"), r.integer("layers")
+
+        def plan(self):
+            norm = PartSpec("rms_norm", {"size": self.width, "eps": 1e-5})
+            layers = [LayerSpec(f"w.{l}.", PartSpec("pre_norm", {}),
+                                PartSpec("toy_wide_value", dict(width=self.width)),
+                                norm.with_params(name="n1"),
+                                PartSpec("gated_mlp", dict(hidden_size=self.width, intermediate_size=24)),
+                                norm.with_params(name="n2")) for l in range(self.layers)]
+            return ModelPlan("ToyWideValueLM", self.vocab, self.width, "w.embed", None,
+                             norm.with_params(name="final"), "w.", layers,
+                             default_schedule(self.layers), 512, ())
+
+    registry.register_part("mixer", "toy_wide_value", WideValueMixer, replace=True)
+    registry.register_architecture("ToyWideValueLM", lambda d, where: WideConfig(d), replace=True)
+
+
+def _wide_reference(w, ids, layers):
+    def norm(x, wt):
+        return x / torch.sqrt((x * x).mean(-1, keepdim=True) + 1e-5) * wt
+    h = w["w.embed"][torch.tensor(ids)]
+    T = len(ids)
+    mask = torch.triu(torch.ones(T, T, dtype=torch.bool), 1)
+    for l in range(layers):
+        p = f"w.{l}."
+        x = norm(h, w[p + "n1.weight"])
+        q, k, v = (x @ w[p + f"wide.{n}"].t() for n in "qkv")
+        sc = (q @ k.t() * 0.25).masked_fill(mask, float("-inf"))
+        h = h + (torch.softmax(sc, -1) @ v) @ w[p + "wide.o"].t()
+        x = norm(h, w[p + "n2.weight"])
+        g, u = x @ w[p + "mlp.gate_proj.weight"].t(), x @ w[p + "mlp.up_proj.weight"].t()
+        h = h + (torch.nn.functional.silu(g) * u) @ w[p + "mlp.down_proj.weight"].t()
+    return norm(h, w["w.final.weight"]) @ w["w.embed"].t()
+
+
+def test_toy_mixer_with_values_wider_than_keys_uses_the_cache():
+    _register_wide_values()
+    from minfer_b200.engine.step import Engine
+    from minfer_b200.model import Model
+    from minfer_b200.registry import read_config
+    from minfer_b200.weights.random_init import write_model_folder
+    from minfer_b200.weights.safetensors_io import load_all
+    config = {"architectures": ["ToyWideValueLM"], "vocab": 61, "width": 32, "layers": 2}
+    with tempfile.TemporaryDirectory() as folder:
+        json.dump(config, open(os.path.join(folder, "config.json"), "w"))
+        cfg = read_config(config)
+        write_model_folder(folder, config, Model(cfg.plan(), "float32", cfg).tensor_specs(), 4, "float32")
+        w = {k: v.double() for k, v in load_all(folder).items()}
+        eng = Engine(Model.from_folder(folder, "float32", "cuda:0"), 512, max_seqs=2)
+    group = eng.cache.groups[0]
+    assert group.k.shape[-1] == KEY_DIM and group.v.shape[-1] == VALUE_DIM
+    assert eng.cuda_graphs is False                                   # the mixer reads on the host
+    prompts = [random_ids(n, 61, 40 + n) for n in (150, 70, 90)]
+    want = [_wide_reference(w, p, 2) for p in prompts]
+    # two sequences at a time, the third in the slot and pages the first gives back
+    a, b = eng.acquire(), eng.acquire()
+    got_a = [eng.step([a], [prompts[0][:100]], [list(range(100))])]
+    out = eng.step([a, b], [prompts[0][100:140], prompts[1][:60]], [list(range(40)), list(range(60))])
+    got_a.append(out[:40]); got_b = [out[40:]]
+    for t in range(10):
+        out = eng.step([a, b], [[prompts[0][140 + t]], [prompts[1][60 + t]]])
+        got_a.append(out[0:1]); got_b.append(out[1:2])
+    eng.release(a)
+    c = eng.acquire()
+    assert c == a
+    got_c = [eng.step([c], [prompts[2]], [list(range(90))])]
+    eng.release(b); eng.release(c)
+    for got, ref in ((got_a, want[0]), (got_b, want[1]), (got_c, want[2])):
+        assert rel_err(torch.cat(got), ref) < 2e-5
+    assert all(n == g.n_pages for n, g in zip(eng.cache.free_pages(), eng.cache.groups))
+    eng.check_status()
+    eng.cache.check_canaries()
