@@ -175,17 +175,16 @@ class Model:
 
     # ---- sizes ----------------------------------------------------------------------------
     def parameter_bytes(self) -> int:
+        """Bytes of all weights as held on the device, every storage counted once (a tied head
+        is the embedding's storage; packed projections are one storage under several names).
+        Asked of the parts through ``export_state_dict``, so a part that keeps its weights in
+        any form is counted."""
         seen, total = set(), 0
-        tensors = [self.embedding, self.head.weight]
-        for block in self.blocks:
-            for part in (block.mixer, block.feed_forward):
-                for lin in vars(part).values():
-                    if isinstance(lin, Linear):
-                        tensors.append(lin.weight)
-        for t in tensors:
-            if t is not None and t.data_ptr() not in seen:
-                seen.add(t.data_ptr())
-                total += t.numel() * t.element_size()
+        for t in self.export_state_dict().values():
+            store = t.untyped_storage()
+            if store.data_ptr() not in seen:
+                seen.add(store.data_ptr())
+                total += store.nbytes()
         return total
 
 
