@@ -1112,7 +1112,7 @@ static PairPlan pair_plan(int M, int N, int K) {
             const double tc = rounds * kb * flops / pair_flops_per_ns;
             const double epilogue = (dual ? rounds * 11600.0 : 4000.0) * nt / 256.0;
             double cost = (l2 > tc ? l2 : tc) + epilogue;
-            if (dual && rounds > 2) continue;     // measured for one and two rounds only
+            if (dual && rounds > 2 && allow_dual != 2) continue;   // measured for one and two rounds only
             if (best_cost < 0 || cost < best_cost) { best = {nt, dual}; best_cost = cost; }
         }
     return best;
